@@ -1,0 +1,201 @@
+"""ctypes binding of libf8b200.so (the C-ABI kernel library, `include/f8b200.h`).
+
+There is no fallback: if the library is missing or a call fails the caller gets an
+exception.  Nothing here runs on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libf8b200.so")
+_lib: Optional[ctypes.CDLL] = None
+
+BF16, FP16, FP32 = 0, 1, 2
+E4M3, E5M2 = 0, 1
+
+_HP_CODE = {torch.bfloat16: BF16, torch.float16: FP16, torch.float32: FP32}
+_FP8_CODE = {torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
+FP8_DTYPE = {E4M3: torch.float8_e4m3fn, E5M2: torch.float8_e5m2}
+
+# every symbol include/f8b200.h declares
+EXPORTS = (
+    "f8b200_status_string",
+    "f8b200_device_check",
+    "f8b200_last_cuda_error",
+    "f8b200_amax",
+    "f8b200_multi_amax",
+    "f8b200_amax_to_scale",
+    "f8b200_cast",
+    "f8b200_transpose_u8",
+    "f8b200_delayed_sync",
+    "f8b200_gemm_fp8",
+    "f8b200_read_device_error",
+)
+
+
+class F8B200Error(RuntimeError):
+    pass
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Loads the kernel library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise F8B200Error(
+            f"{_LIB_PATH} is missing: build it with `python -m float8_experimental_b200.csrc.build` "
+            "(there is no CPU or PyTorch fallback for these kernels)"
+        )
+    lib = ctypes.CDLL(_LIB_PATH)
+    vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    lib.f8b200_status_string.restype = ctypes.c_char_p
+    lib.f8b200_status_string.argtypes = [i32]
+    lib.f8b200_last_cuda_error.restype = ctypes.c_char_p
+    lib.f8b200_last_cuda_error.argtypes = []
+    lib.f8b200_device_check.argtypes = []
+    lib.f8b200_amax.argtypes = [vp, i32, i64, vp, vp]
+    lib.f8b200_multi_amax.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(i64), i32, i32, vp, vp]
+    lib.f8b200_amax_to_scale.argtypes = [vp, i64, i32, i32, i32, vp, vp]
+    lib.f8b200_cast.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, vp, i64, vp, i64, vp, i32, vp]
+    lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
+    lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
+    lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
+    lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+    for name in EXPORTS:
+        fn = getattr(lib, name)
+        if fn.restype is not ctypes.c_char_p:
+            fn.restype = i32
+    _lib = lib
+    return lib
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.f8b200_status_string(status).decode()
+    detail = lib.f8b200_last_cuda_error().decode() if status == -4 else ""
+    raise F8B200Error(f"{what}: {msg}" + (f" [{detail}]" if detail else ""))
+
+
+def hp_code(dtype: torch.dtype) -> int:
+    try:
+        return _HP_CODE[dtype]
+    except KeyError:
+        raise F8B200Error(f"unsupported high-precision dtype {dtype}") from None
+
+
+def fp8_code(dtype: torch.dtype) -> int:
+    try:
+        return _FP8_CODE[dtype]
+    except KeyError:
+        raise F8B200Error(f"unsupported float8 dtype {dtype}") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise F8B200Error("f8b200 kernels run on CUDA tensors only (no CPU path exists)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------------------
+# thin tensor-level wrappers (each sets the device of its first argument)
+# ---------------------------------------------------------------------------
+def amax(x: torch.Tensor, out: torch.Tensor) -> None:
+    _require_cuda(x, out)
+    with torch.cuda.device(x.device):
+        _check(load().f8b200_amax(x.data_ptr(), hp_code(x.dtype), x.numel(), out.data_ptr(), _stream(x)), "f8b200_amax")
+
+
+def multi_amax(xs: Sequence[torch.Tensor], out: torch.Tensor) -> None:
+    n = len(xs)
+    if n == 0:
+        return
+    _require_cuda(out, *xs)
+    dt = xs[0].dtype
+    if any(t.dtype != dt for t in xs):
+        raise F8B200Error("multi_amax needs tensors of one dtype")
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in xs])
+    numels = (ctypes.c_int64 * n)(*[t.numel() for t in xs])
+    with torch.cuda.device(out.device):
+        _check(load().f8b200_multi_amax(ptrs, numels, n, hp_code(dt), out.data_ptr(), _stream(out)), "f8b200_multi_amax")
+
+
+def amax_to_scale(amax_t: torch.Tensor, fp8_kind: int, amax_dtype: int, orig_dtype: int, out: torch.Tensor) -> None:
+    _require_cuda(amax_t, out)
+    with torch.cuda.device(out.device):
+        _check(
+            load().f8b200_amax_to_scale(amax_t.data_ptr(), amax_t.numel(), fp8_kind, amax_dtype, orig_dtype,
+                                        out.data_ptr(), _stream(out)),
+            "f8b200_amax_to_scale",
+        )
+
+
+def cast(x: torch.Tensor, rows: int, cols: int, ld_x: int, scale_src: int, scale_in: torch.Tensor,
+         scale_out: Optional[torch.Tensor], product_fp32: bool, fp8_kind: int, out: Optional[torch.Tensor],
+         ld_out: int, out_t: Optional[torch.Tensor], ld_out_t: int, amax_out: Optional[torch.Tensor],
+         reverse: bool) -> None:
+    _require_cuda(x, scale_in, scale_out, out, out_t, amax_out)
+    with torch.cuda.device(x.device):
+        _check(
+            load().f8b200_cast(x.data_ptr(), hp_code(x.dtype), rows, cols, ld_x, scale_src, scale_in.data_ptr(),
+                               _ptr(scale_out), int(product_fp32), fp8_kind, _ptr(out), ld_out, _ptr(out_t),
+                               ld_out_t, _ptr(amax_out), int(reverse), _stream(x)),
+            "f8b200_cast",
+        )
+
+
+def transpose_u8(src: torch.Tensor, rows: int, cols: int, ld_in: int, dst: torch.Tensor, ld_out: int) -> None:
+    _require_cuda(src, dst)
+    with torch.cuda.device(src.device):
+        _check(load().f8b200_transpose_u8(src.data_ptr(), rows, cols, ld_in, dst.data_ptr(), ld_out, _stream(src)),
+               "f8b200_transpose_u8")
+
+
+def delayed_sync(amax_t: torch.Tensor, hist: torch.Tensor, n_e4m3: int, orig_dtype: int, scale_out: torch.Tensor,
+                 hist_out: Optional[torch.Tensor]) -> None:
+    _require_cuda(amax_t, hist, scale_out, hist_out)
+    rows, hist_len = hist.shape
+    with torch.cuda.device(hist.device):
+        _check(
+            load().f8b200_delayed_sync(amax_t.data_ptr(), hist.data_ptr(), hist.stride(0), rows, hist_len, n_e4m3,
+                                       orig_dtype, scale_out.data_ptr(), _ptr(hist_out),
+                                       hist_out.stride(0) if hist_out is not None else 0, _stream(hist)),
+            "f8b200_delayed_sync",
+        )
+
+
+def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor, scale_b: torch.Tensor,
+             bias: Optional[torch.Tensor], out: torch.Tensor, ldo: int, m: int, n: int, k: int,
+             use_fast_accum: bool) -> None:
+    _require_cuda(a, b, scale_a, scale_b, bias, out)
+    with torch.cuda.device(a.device):
+        _check(
+            load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
+                                   scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
+                                   out.data_ptr(), ldo, m, n, k, int(use_fast_accum), _stream(a)),
+            "f8b200_gemm_fp8",
+        )
+
+
+def read_device_error() -> int:
+    v = ctypes.c_uint32(0)
+    _check(load().f8b200_read_device_error(ctypes.byref(v)), "f8b200_read_device_error")
+    return int(v.value)

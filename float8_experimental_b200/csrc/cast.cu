@@ -1,0 +1,555 @@
+// Per-tensor scaling kernels: amax reduction, scale derivation, saturating RNE cast
+// to e4m3fn / e5m2 with the transposed copy emitted from the same read, the fp8
+// transpose, and the batched delayed-scaling bookkeeping.  All of them are bound by
+// HBM bandwidth (or by launch latency for the bookkeeping), so the design rules are:
+// 128-bit / 64-bit coalesced global accesses, enough loads in flight per thread to
+// cover HBM latency, one atomic per CTA, and no re-read of the source.
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace f8b200 {
+
+// ---------------------------------------------------------------------------
+// amax
+// ---------------------------------------------------------------------------
+// |x| bit patterns order like unsigned integers for non-NaN values and every NaN
+// pattern is larger than inf, so an unsigned max both finds the amax and propagates
+// NaN.  2-byte types are reduced two at a time with a packed unsigned max.
+template <int HP>
+struct AbsMax {
+  uint32_t m = 0;
+  __device__ __forceinline__ void add_word(uint32_t w) {
+    if constexpr (HP == F8B200_FP32) {
+      m = max(m, w & 0x7FFFFFFFu);
+    } else {
+      m = __vmaxu2(m, w & 0x7FFF7FFFu);
+    }
+  }
+  __device__ __forceinline__ void add_half(uint16_t h) { m = __vmaxu2(m, (uint32_t)(h & 0x7FFFu)); }
+  // fp32 bit pattern of the running amax
+  __device__ __forceinline__ uint32_t f32_bits() const {
+    if constexpr (HP == F8B200_FP32) {
+      return m;
+    } else {
+      const uint32_t h = max(m & 0xFFFFu, m >> 16);
+      if constexpr (HP == F8B200_BF16) {
+        return h << 16;
+      } else {
+        return __float_as_uint(__half2float(__ushort_as_half((unsigned short)h)));
+      }
+    }
+  }
+};
+
+// CTA-wide max of `v`, then at most one atomic on the global word.
+__device__ __forceinline__ void block_atomic_max(uint32_t v, uint32_t* out, uint32_t* smem) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_max_u32(v);
+  if (lane == 0) smem[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    v = lane < nw ? smem[lane] : 0u;
+    v = warp_max_u32(v);
+    if (lane == 0 && v > *reinterpret_cast<volatile uint32_t*>(out)) atomicMax(out, v);
+  }
+}
+
+template <int HP>
+__device__ __forceinline__ uint32_t amax_flat_body(const char* base, int64_t n, int64_t gtid,
+                                                   int64_t gstride) {
+  constexpr int ES = (HP == F8B200_FP32) ? 4 : 2;
+  constexpr int EPV = 16 / ES;
+  AbsMax<HP> acc;
+  // scalar head up to the first 16-byte boundary, vector body, scalar tail
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(base);
+  int64_t head = (int64_t)(((16 - (addr & 15)) & 15) / ES);
+  if (head > n) head = n;
+  const int64_t nvec = (n - head) / EPV;
+  const int64_t tail0 = head + nvec * EPV;
+  if (gtid < head + (n - tail0)) {
+    const int64_t i = gtid < head ? gtid : tail0 + (gtid - head);
+    if constexpr (ES == 4) {
+      acc.add_word(reinterpret_cast<const uint32_t*>(base)[i]);
+    } else {
+      acc.add_half(reinterpret_cast<const uint16_t*>(base)[i]);
+    }
+  }
+  const uint4* v = reinterpret_cast<const uint4*>(base + head * ES);
+  int64_t i = gtid;
+  for (; i + 3 * gstride < nvec; i += 4 * gstride) {
+    const uint4 a = v[i], b = v[i + gstride], c = v[i + 2 * gstride], d = v[i + 3 * gstride];
+    acc.add_word(a.x); acc.add_word(a.y); acc.add_word(a.z); acc.add_word(a.w);
+    acc.add_word(b.x); acc.add_word(b.y); acc.add_word(b.z); acc.add_word(b.w);
+    acc.add_word(c.x); acc.add_word(c.y); acc.add_word(c.z); acc.add_word(c.w);
+    acc.add_word(d.x); acc.add_word(d.y); acc.add_word(d.z); acc.add_word(d.w);
+  }
+  for (; i < nvec; i += gstride) {
+    const uint4 a = v[i];
+    acc.add_word(a.x); acc.add_word(a.y); acc.add_word(a.z); acc.add_word(a.w);
+  }
+  return acc.f32_bits();
+}
+
+template <int HP>
+__global__ void __launch_bounds__(512) amax_flat_kernel(const void* x, int64_t n, uint32_t* out) {
+  __shared__ uint32_t smem[16];
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t gstride = (int64_t)gridDim.x * blockDim.x;
+  const uint32_t m = amax_flat_body<HP>(static_cast<const char*>(x), n, gtid, gstride);
+  block_atomic_max(m, out, smem);
+}
+
+constexpr int kMultiMax = 128;  // tensors per launch (2 KB of kernel parameters)
+struct MultiAmaxArgs {
+  const void* ptr[kMultiMax];
+  int64_t numel[kMultiMax];
+};
+
+template <int HP>
+__global__ void __launch_bounds__(512) multi_amax_kernel(const MultiAmaxArgs args, uint32_t* out) {
+  __shared__ uint32_t smem[16];
+  const int t = blockIdx.y;
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t gstride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n = args.numel[t];
+  uint32_t m = 0;
+  if (n > 0) m = amax_flat_body<HP>(static_cast<const char*>(args.ptr[t]), n, gtid, gstride);
+  block_atomic_max(m, out + t, smem);
+}
+
+__global__ void amax_to_scale_kernel(const float* amax, int64_t n, float fp8_max, int amax_dtype,
+                                     int clamp_fp16, float* scale) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scale[i] = amax_to_scale_dev(amax[i], fp8_max, amax_dtype, clamp_fp16 != 0);
+}
+
+// ---------------------------------------------------------------------------
+// cast (+ transposed copy, + amax of the same read)
+// ---------------------------------------------------------------------------
+struct CastParams {
+  const void* x;
+  int64_t rows, cols, ld_x;
+  const float* scale_in;
+  float* scale_out;
+  int scale_src;
+  int product_fp32;
+  uint8_t* out;
+  int64_t ld_out;
+  uint8_t* out_t;
+  int64_t ld_out_t;
+  uint32_t* amax_out;
+  int reverse;
+  int64_t tiles_c, ntiles;
+};
+
+template <int HP>
+__device__ __forceinline__ float load_scale(const CastParams& p, float fp8_max) {
+  if (p.scale_src == 1) {
+    const float s = amax_to_scale_dev(*p.scale_in, fp8_max, HP, HP == F8B200_FP16);
+    if (p.scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.scale_out = s;
+    return s;
+  }
+  return *p.scale_in;
+}
+
+// A 128x128 byte tile held as 16 row-words per thread (warp w owns rows 16w..16w+15,
+// lane owns columns 4*lane..4*lane+3) is transposed with byte permutes into one
+// 16-byte vector per owned column, staged through shared memory with an XOR swizzle
+// (conflict-free for both the 16-byte writes and the 16-byte reads) and written out
+// as 128-byte contiguous row segments of the transposed matrix.
+__device__ __forceinline__ void store_transposed_tile(const uint32_t (&rw)[16], uint4* smem_t,
+                                                      uint8_t* out_t, int64_t ld_out_t,
+                                                      int64_t tile_row0, int64_t tile_col0,
+                                                      int64_t rows, int64_t cols) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  uint32_t cw[4][4];  // [column j][row group k]
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t a = rw[4 * k], b = rw[4 * k + 1], c = rw[4 * k + 2], d = rw[4 * k + 3];
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+    cw[0][k] = __byte_perm(t0, t1, 0x5410);
+    cw[1][k] = __byte_perm(t0, t1, 0x7632);
+    cw[2][k] = __byte_perm(t2, t3, 0x5410);
+    cw[3][k] = __byte_perm(t2, t3, 0x7632);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = 4 * lane + j;
+    smem_t[c * 8 + (w ^ (lane & 7))] = make_uint4(cw[j][0], cw[j][1], cw[j][2], cw[j][3]);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = it * 256 + tid;
+    const int c = idx >> 3, chunk = idx & 7;
+    const uint4 val = smem_t[c * 8 + (chunk ^ ((c >> 2) & 7))];
+    const int64_t gc = tile_col0 + c;
+    const int64_t gr = tile_row0 + chunk * 16;
+    if (gc < cols && gr < rows) {
+      uint8_t* dst = out_t + gc * ld_out_t + gr;
+      if (gr + 16 <= rows) {
+        *reinterpret_cast<uint4*>(dst) = val;
+      } else {
+        const uint32_t wv[4] = {val.x, val.y, val.z, val.w};
+        for (int b = 0; b < 16 && gr + b < rows; ++b) dst[b] = (uint8_t)(wv[b >> 2] >> (8 * (b & 3)));
+      }
+    }
+  }
+}
+
+template <int HP, int KIND>
+__global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
+  __shared__ uint4 smem_t[128 * 8];
+  __shared__ uint32_t smem_max[8];
+  constexpr int ES = (HP == F8B200_FP32) ? 4 : 2;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int64_t t = p.reverse ? (p.ntiles - 1 - (int64_t)blockIdx.x) : (int64_t)blockIdx.x;
+  const int64_t tile_row0 = (t / p.tiles_c) * 128, tile_col0 = (t % p.tiles_c) * 128;
+  const int64_t row0 = tile_row0 + w * 16, col = tile_col0 + lane * 4;
+  const bool col_ok = col < p.cols;
+  const float s = load_scale<HP>(p, (KIND == F8B200_E4M3) ? kE4M3Max : kE5M2Max);
+  const char* xb = static_cast<const char*>(p.x);
+
+  uint32_t rw[16];
+  AbsMax<HP> acc;
+  if constexpr (ES == 2) {
+    uint2 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t r = row0 + i;
+      v[i] = make_uint2(0u, 0u);
+      if (col_ok && r < p.rows) v[i] = __ldcs(reinterpret_cast<const uint2*>(xb + (r * p.ld_x + col) * ES));
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      acc.add_word(v[i].x);
+      acc.add_word(v[i].y);
+      float f0, f1, f2, f3;
+      if constexpr (HP == F8B200_BF16) {
+        f0 = __uint_as_float(v[i].x << 16);
+        f1 = __uint_as_float(v[i].x & 0xFFFF0000u);
+        f2 = __uint_as_float(v[i].y << 16);
+        f3 = __uint_as_float(v[i].y & 0xFFFF0000u);
+      } else {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v[i].x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v[i].y));
+        f0 = a.x; f1 = a.y; f2 = b.x; f3 = b.y;
+      }
+      float p0 = __fmul_rn(f0, s), p1 = __fmul_rn(f1, s), p2 = __fmul_rn(f2, s), p3 = __fmul_rn(f3, s);
+      if (!p.product_fp32) {
+        p0 = round_hp<HP>(p0); p1 = round_hp<HP>(p1); p2 = round_hp<HP>(p2); p3 = round_hp<HP>(p3);
+      }
+      rw[i] = cvt_pair<KIND>(p0, p1) | (cvt_pair<KIND>(p2, p3) << 16);
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int64_t r = row0 + h * 8 + i;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (col_ok && r < p.rows) v[i] = __ldcs(reinterpret_cast<const uint4*>(xb + (r * p.ld_x + col) * ES));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc.add_word(v[i].x); acc.add_word(v[i].y); acc.add_word(v[i].z); acc.add_word(v[i].w);
+        const float p0 = __fmul_rn(__uint_as_float(v[i].x), s), p1 = __fmul_rn(__uint_as_float(v[i].y), s);
+        const float p2 = __fmul_rn(__uint_as_float(v[i].z), s), p3 = __fmul_rn(__uint_as_float(v[i].w), s);
+        rw[h * 8 + i] = cvt_pair<KIND>(p0, p1) | (cvt_pair<KIND>(p2, p3) << 16);
+      }
+    }
+  }
+
+  if (p.out != nullptr && col_ok) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t r = row0 + i;
+      if (r < p.rows) *reinterpret_cast<uint32_t*>(p.out + r * p.ld_out + col) = rw[i];
+    }
+  }
+  if (p.out_t != nullptr) {
+    store_transposed_tile(rw, smem_t, p.out_t, p.ld_out_t, tile_row0, tile_col0, p.rows, p.cols);
+  }
+  if (p.amax_out != nullptr) block_atomic_max(acc.f32_bits(), p.amax_out, smem_max);
+}
+
+// Any shape, stride or alignment: one element per thread.  Used only when the tiled
+// kernel's alignment requirements do not hold.
+template <int HP, int KIND>
+__global__ void __launch_bounds__(256) cast_generic_kernel(const CastParams p) {
+  __shared__ uint32_t smem_max[8];
+  const float s = load_scale<HP>(p, (KIND == F8B200_E4M3) ? kE4M3Max : kE5M2Max);
+  const int64_t n = p.rows * p.cols;
+  AbsMax<HP> acc;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / p.cols, c = i % p.cols;
+    float f;
+    if constexpr (HP == F8B200_FP32) {
+      const uint32_t u = static_cast<const uint32_t*>(p.x)[r * p.ld_x + c];
+      acc.add_word(u);
+      f = __uint_as_float(u);
+    } else {
+      const uint16_t u = static_cast<const uint16_t*>(p.x)[r * p.ld_x + c];
+      acc.add_half(u);
+      f = (HP == F8B200_BF16) ? __uint_as_float((uint32_t)u << 16) : __half2float(__ushort_as_half(u));
+    }
+    float pr = __fmul_rn(f, s);
+    if (!p.product_fp32) pr = round_hp<HP>(pr);
+    const uint8_t b = (uint8_t)(cvt_pair<KIND>(pr, 0.0f) & 0xFFu);
+    if (p.out != nullptr) p.out[r * p.ld_out + c] = b;
+    if (p.out_t != nullptr) p.out_t[c * p.ld_out_t + r] = b;
+  }
+  if (p.amax_out != nullptr) block_atomic_max(acc.f32_bits(), p.amax_out, smem_max);
+}
+
+// ---------------------------------------------------------------------------
+// fp8 transpose
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose_u8_tile_kernel(const uint8_t* in, int64_t rows, int64_t cols,
+                                                                int64_t ld_in, uint8_t* out, int64_t ld_out,
+                                                                int64_t tiles_c) {
+  __shared__ uint4 smem_t[128 * 8];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int64_t t = blockIdx.x;
+  const int64_t tile_row0 = (t / tiles_c) * 128, tile_col0 = (t % tiles_c) * 128;
+  const int64_t row0 = tile_row0 + w * 16, col = tile_col0 + lane * 4;
+  uint32_t rw[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = row0 + i;
+    rw[i] = 0u;
+    if (col < cols && r < rows) rw[i] = __ldcs(reinterpret_cast<const uint32_t*>(in + r * ld_in + col));
+  }
+  store_transposed_tile(rw, smem_t, out, ld_out, tile_row0, tile_col0, rows, cols);
+}
+
+__global__ void transpose_u8_generic_kernel(const uint8_t* in, int64_t rows, int64_t cols, int64_t ld_in,
+                                            uint8_t* out, int64_t ld_out) {
+  const int64_t n = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i % cols;
+    out[c * ld_out + r] = in[r * ld_in + c];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// delayed-scaling bookkeeping: one thread per (layer, tensor) row
+// ---------------------------------------------------------------------------
+__global__ void delayed_sync_kernel(const float* amax, const float* hist, int64_t ld_hist, int64_t rows,
+                                    int hist_len, int64_t n_e4m3, int clamp_fp16, float* scale_out,
+                                    float* hist_out, int64_t ld_hist_out) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const float cur = amax[r];
+  const float* h = hist + r * ld_hist;
+  float m = cur;
+  bool has_nan = cur != cur;
+  float prev = cur;  // value moving into slot i
+  for (int i = 0; i < hist_len; ++i) {
+    const float old = h[i];
+    if (i < hist_len - 1) {  // old h[i] survives the roll (lands in slot i+1)
+      has_nan |= (old != old);
+      m = fmaxf(m, old);
+    }
+    if (hist_out != nullptr) hist_out[r * ld_hist_out + i] = prev;
+    prev = old;
+  }
+  if (has_nan) m = __uint_as_float(0x7FC00000u);
+  const float fmax8 = r < n_e4m3 ? kE4M3Max : kE5M2Max;
+  scale_out[r] = amax_to_scale_dev(m, fmax8, F8B200_FP32, clamp_fp16 != 0);
+}
+
+// ---------------------------------------------------------------------------
+// host entry points
+// ---------------------------------------------------------------------------
+static inline bool aligned_to(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+template <typename F>
+static int dispatch_hp(int hp, F&& f) {
+  switch (hp) {
+    case F8B200_BF16: return f(std::integral_constant<int, F8B200_BF16>{});
+    case F8B200_FP16: return f(std::integral_constant<int, F8B200_FP16>{});
+    case F8B200_FP32: return f(std::integral_constant<int, F8B200_FP32>{});
+    default: return F8B200_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace f8b200
+
+using namespace f8b200;
+
+extern "C" int f8b200_amax(const void* x, int hp_dtype, int64_t numel, float* amax_out, void* stream) {
+  if (x == nullptr || amax_out == nullptr || numel <= 0) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2) return F8B200_ERR_BAD_ARG;
+  if (!aligned_to(x, hp_size_of(hp_dtype)) || !aligned_to(amax_out, 4)) return F8B200_ERR_ALIGNMENT;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = record_cuda_error(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+  if (rc != F8B200_OK) return rc;
+  const int64_t nvec = numel / (16 / hp_size_of(hp_dtype));
+  int64_t blocks = (nvec + 512 * 4 - 1) / (512 * 4);
+  const int64_t cap = (int64_t)sm_count() * 4;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return dispatch_hp(hp_dtype, [&](auto hp) {
+    amax_flat_kernel<decltype(hp)::value><<<(unsigned)blocks, 512, 0, st>>>(x, numel, reinterpret_cast<uint32_t*>(amax_out));
+    return check_launch();
+  });
+}
+
+extern "C" int f8b200_multi_amax(const void* const* ptrs, const int64_t* numels, int n, int hp_dtype,
+                                 float* amax_out, void* stream) {
+  if (n < 0 || (n > 0 && (ptrs == nullptr || numels == nullptr || amax_out == nullptr))) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2) return F8B200_ERR_BAD_ARG;
+  if (n == 0) return F8B200_OK;
+  for (int i = 0; i < n; ++i) {
+    if (numels[i] < 0 || (numels[i] > 0 && ptrs[i] == nullptr)) return F8B200_ERR_BAD_ARG;
+    if (numels[i] > 0 && !aligned_to(ptrs[i], hp_size_of(hp_dtype))) return F8B200_ERR_ALIGNMENT;
+  }
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = record_cuda_error(cudaMemsetAsync(amax_out, 0, sizeof(float) * (size_t)n, st));
+  if (rc != F8B200_OK) return rc;
+  for (int base = 0; base < n; base += kMultiMax) {
+    const int cnt = (n - base < kMultiMax) ? (n - base) : kMultiMax;
+    MultiAmaxArgs args;
+    int64_t biggest = 0;
+    for (int i = 0; i < kMultiMax; ++i) {
+      args.ptr[i] = i < cnt ? ptrs[base + i] : nullptr;
+      args.numel[i] = i < cnt ? numels[base + i] : 0;
+      if (args.numel[i] > biggest) biggest = args.numel[i];
+    }
+    // enough CTAs per tensor to keep every SM busy even when only a few tensors are large
+    int64_t bx = (biggest / (16 / hp_size_of(hp_dtype)) + 512 * 4 - 1) / (512 * 4);
+    int64_t cap = ((int64_t)sm_count() * 8 + cnt - 1) / cnt;
+    if (cap < 1) cap = 1;
+    if (bx > cap) bx = cap;
+    if (bx < 1) bx = 1;
+    dim3 grid((unsigned)bx, (unsigned)cnt);
+    rc = dispatch_hp(hp_dtype, [&](auto hp) {
+      multi_amax_kernel<decltype(hp)::value><<<grid, 512, 0, st>>>(args, reinterpret_cast<uint32_t*>(amax_out) + base);
+      return check_launch();
+    });
+    if (rc != F8B200_OK) return rc;
+  }
+  return F8B200_OK;
+}
+
+extern "C" int f8b200_amax_to_scale(const float* amax, int64_t n, int fp8_kind, int amax_dtype, int orig_dtype,
+                                    float* scale_out, void* stream) {
+  if (n < 0 || (n > 0 && (amax == nullptr || scale_out == nullptr))) return F8B200_ERR_BAD_ARG;
+  if (fp8_kind < 0 || fp8_kind > 1 || amax_dtype < 0 || amax_dtype > 2 || orig_dtype < 0 || orig_dtype > 2)
+    return F8B200_ERR_BAD_ARG;
+  if (n == 0) return F8B200_OK;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  amax_to_scale_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      amax, n, fp8_max_of(fp8_kind), amax_dtype, orig_dtype == F8B200_FP16 ? 1 : 0, scale_out);
+  return check_launch();
+}
+
+extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
+                           const float* scale_in, float* scale_out, int product_fp32, int fp8_kind, void* out,
+                           int64_t ld_out, void* out_t, int64_t ld_out_t, float* amax_out, int reverse,
+                           void* stream) {
+  if (rows < 0 || cols < 0 || hp_dtype < 0 || hp_dtype > 2 || fp8_kind < 0 || fp8_kind > 1) return F8B200_ERR_BAD_ARG;
+  if (scale_src < 0 || scale_src > 1 || scale_in == nullptr) return F8B200_ERR_BAD_ARG;
+  if (ld_x < cols || (out != nullptr && ld_out < cols) || (out_t != nullptr && ld_out_t < rows)) return F8B200_ERR_BAD_ARG;
+  if (rows > 0 && cols > 0 && x == nullptr) return F8B200_ERR_BAD_ARG;
+  const int es = hp_size_of(hp_dtype);
+  if (!aligned_to(x, es) || !aligned_to(scale_in, 4) || !aligned_to(scale_out, 4) || !aligned_to(amax_out, 4))
+    return F8B200_ERR_ALIGNMENT;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (amax_out != nullptr) {
+    rc = record_cuda_error(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    if (rc != F8B200_OK) return rc;
+  }
+  CastParams p;
+  p.x = x; p.rows = rows; p.cols = cols; p.ld_x = ld_x;
+  p.scale_in = scale_in; p.scale_out = scale_out; p.scale_src = scale_src; p.product_fp32 = product_fp32;
+  p.out = static_cast<uint8_t*>(out); p.ld_out = ld_out;
+  p.out_t = static_cast<uint8_t*>(out_t); p.ld_out_t = ld_out_t;
+  p.amax_out = reinterpret_cast<uint32_t*>(amax_out); p.reverse = reverse;
+  p.tiles_c = (cols + 127) / 128;
+  p.ntiles = p.tiles_c * ((rows + 127) / 128);
+  const bool empty = rows == 0 || cols == 0;
+  if (empty) {
+    // nothing to cast; the scale of a dynamic cast is still defined by the amax word
+    p.ntiles = 0;
+  }
+  const bool fast = cols % 4 == 0 && ld_x % 4 == 0 && aligned_to(x, 4 * es) &&
+                    (out == nullptr || (ld_out % 4 == 0 && aligned_to(out, 4))) &&
+                    (out_t == nullptr || (ld_out_t % 16 == 0 && aligned_to(out_t, 16)));
+  return dispatch_hp(hp_dtype, [&](auto hp) {
+    constexpr int HP = decltype(hp)::value;
+    if (empty) {
+      if (scale_src == 1 && scale_out != nullptr) {
+        amax_to_scale_kernel<<<1, 32, 0, st>>>(scale_in, 1, fp8_max_of(fp8_kind), HP, HP == F8B200_FP16, scale_out);
+        return check_launch();
+      }
+      return (int)F8B200_OK;
+    }
+    if (fast) {
+      if (p.ntiles > 0x7FFFFFFFLL) return (int)F8B200_ERR_UNSUPPORTED;
+      if (fp8_kind == F8B200_E4M3) cast_tile_kernel<HP, F8B200_E4M3><<<(unsigned)p.ntiles, 256, 0, st>>>(p);
+      else cast_tile_kernel<HP, F8B200_E5M2><<<(unsigned)p.ntiles, 256, 0, st>>>(p);
+    } else {
+      int64_t blocks = (rows * cols + 255) / 256;
+      const int64_t cap = (int64_t)sm_count() * 16;
+      if (blocks > cap) blocks = cap;
+      if (fp8_kind == F8B200_E4M3) cast_generic_kernel<HP, F8B200_E4M3><<<(unsigned)blocks, 256, 0, st>>>(p);
+      else cast_generic_kernel<HP, F8B200_E5M2><<<(unsigned)blocks, 256, 0, st>>>(p);
+    }
+    return check_launch();
+  });
+}
+
+extern "C" int f8b200_transpose_u8(const void* in, int64_t rows, int64_t cols, int64_t ld_in, void* out,
+                                   int64_t ld_out, void* stream) {
+  if (rows < 0 || cols < 0 || ld_in < cols || ld_out < rows) return F8B200_ERR_BAD_ARG;
+  if (rows == 0 || cols == 0) return F8B200_OK;
+  if (in == nullptr || out == nullptr) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fast = cols % 4 == 0 && ld_in % 4 == 0 && aligned_to(in, 4) && ld_out % 16 == 0 && aligned_to(out, 16);
+  if (fast) {
+    const int64_t tiles_c = (cols + 127) / 128;
+    const int64_t ntiles = tiles_c * ((rows + 127) / 128);
+    if (ntiles > 0x7FFFFFFFLL) return F8B200_ERR_UNSUPPORTED;
+    transpose_u8_tile_kernel<<<(unsigned)ntiles, 256, 0, st>>>(static_cast<const uint8_t*>(in), rows, cols, ld_in,
+                                                               static_cast<uint8_t*>(out), ld_out, tiles_c);
+  } else {
+    int64_t blocks = (rows * cols + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    transpose_u8_generic_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(in), rows, cols, ld_in,
+                                                                  static_cast<uint8_t*>(out), ld_out);
+  }
+  return check_launch();
+}
+
+extern "C" int f8b200_delayed_sync(const float* amax, const float* hist, int64_t ld_hist, int64_t rows, int hist_len,
+                                   int64_t n_e4m3, int orig_dtype, float* scale_out, float* hist_out,
+                                   int64_t ld_hist_out, void* stream) {
+  if (rows < 0 || hist_len < 1 || n_e4m3 < 0 || orig_dtype < 0 || orig_dtype > 2) return F8B200_ERR_BAD_ARG;
+  if (rows == 0) return F8B200_OK;
+  if (amax == nullptr || hist == nullptr || scale_out == nullptr || ld_hist < hist_len) return F8B200_ERR_BAD_ARG;
+  if (hist_out != nullptr && ld_hist_out < hist_len) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  const unsigned blocks = (unsigned)((rows + 127) / 128);
+  delayed_sync_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      amax, hist, ld_hist, rows, hist_len, n_e4m3, orig_dtype == F8B200_FP16 ? 1 : 0, scale_out, hist_out,
+      ld_hist_out);
+  return check_launch();
+}

@@ -1,0 +1,73 @@
+// Shared device/host helpers for the sm_100a float8 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/f8b200.h"
+
+namespace f8b200 {
+
+constexpr float kE4M3Max = 448.0f;
+constexpr float kE5M2Max = 57344.0f;
+constexpr float kFp16Max = 65504.0f;
+constexpr float kEps = 1e-12f;  // float8_experimental/float8_utils.py:19
+
+// Remembers the last CUDA error text for f8b200_last_cuda_error().
+int record_cuda_error(cudaError_t e);
+int sm_count();  // SM count of the current device
+inline int check_launch() { return record_cuda_error(cudaGetLastError()); }
+
+__host__ __device__ inline float fp8_max_of(int kind) { return kind == F8B200_E4M3 ? kE4M3Max : kE5M2Max; }
+__host__ __device__ inline int hp_size_of(int dt) { return dt == F8B200_FP32 ? 4 : 2; }
+
+// Rounds an fp32 value to the high-precision dtype and widens it back.
+template <int HP>
+__device__ __forceinline__ float round_hp(float v) {
+  if constexpr (HP == F8B200_BF16) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+  } else if constexpr (HP == F8B200_FP16) {
+    return __half2float(__float2half_rn(v));
+  } else {
+    return v;
+  }
+}
+
+__device__ __forceinline__ float round_hp_rt(float v, int hp) {
+  if (hp == F8B200_BF16) return round_hp<F8B200_BF16>(v);
+  if (hp == F8B200_FP16) return round_hp<F8B200_FP16>(v);
+  return v;
+}
+
+// scale = RN_T( RN_T(1 / max(amax, RN_T(eps))) * fp8_max ), fp16 clamp on request.
+// Reciprocal-then-multiply with a rounding after every step is what
+// `finfo.max / clamp(amax, EPS)` evaluates to in PyTorch eager mode.
+__device__ __forceinline__ float amax_to_scale_dev(float amax, float fp8_max, int amax_dtype,
+                                                   bool clamp_fp16) {
+  const float eps_t = round_hp_rt(kEps, amax_dtype);
+  const float c = (amax != amax) ? amax : fmaxf(amax, eps_t);
+  const float r = round_hp_rt(__fdiv_rn(1.0f, c), amax_dtype);
+  float s = round_hp_rt(__fmul_rn(r, fp8_max), amax_dtype);
+  if (clamp_fp16 && s == s) s = fminf(s, kFp16Max);
+  return s;
+}
+
+// Two fp32 values -> two fp8 bytes (low byte = a).  cvt.rn.satfinite clamps to the
+// finite range and rounds to nearest even, subnormals included; NaN is forced to 0x7F.
+template <int KIND>
+__device__ __forceinline__ uint32_t cvt_pair(float a, float b) {
+  const __nv_fp8_interpretation_t interp = (KIND == F8B200_E4M3) ? __NV_E4M3 : __NV_E5M2;
+  uint32_t r = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, interp);
+  if (a != a) r = (r & 0xFF00u) | 0x7Fu;
+  if (b != b) r = (r & 0x00FFu) | 0x7F00u;
+  return r;
+}
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+  return __reduce_max_sync(0xFFFFFFFFu, v);
+}
+
+}  // namespace f8b200

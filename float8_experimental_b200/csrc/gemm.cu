@@ -1,0 +1,445 @@
+// Scaled fp8 GEMM for sm_100a:  out[M,N] = (A[M,K] . B[N,K]^T) / (sa * sb) (+ bias).
+//
+// Both operands are K-major fp8 bytes.  One persistent CTA per SM walks 128x256
+// output tiles.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor 128-byte-swizzled boxes of A (128x128 B)
+//               and B (256x128 B) into a 4-stage shared-memory ring, mbarrier complete_tx.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f8f6f4 (M128 N256 K32)
+//               from shared-memory descriptors into one of two 256-column fp32
+//               accumulators in tensor memory; tcgen05.commit releases ring slots and
+//               publishes finished accumulators.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, multiply by 1/(sa*sb), add bias,
+//               convert to the output dtype and store; runs under the next tile's
+//               main loop because the accumulator is double buffered.
+// Every mbarrier wait is bounded by a cycle budget; on expiry the kernel raises a flag
+// in a device error word, all roles leave their loops, tensor memory is released and
+// the kernel returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace f8b200 {
+
+__device__ uint32_t g_device_error = 0;
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes == fp8 elements; one 128-byte swizzle span
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 16;  // tile rasterisation: walk 16 M-tiles before moving along N
+constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;  // about one second
+
+struct __align__(8) Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Barriers);
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the budget ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t who) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (bars->abort_flag != 0u) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
+    }
+  }
+  bars->abort_flag = 1u;
+  atomicOr(&g_device_error, who);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
+// bytes with the 128-byte swizzle (what the TMA box load produces): 8-row groups are
+// 1024 bytes apart (stride byte offset), the leading byte offset is unused for
+// swizzled K-major layouts (encoded 1), descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f8f6f4: fp32 accumulate, A/B formats
+// (0 = e4m3, 1 = e5m2), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int a_kind, int b_kind) {
+  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(BN >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+struct TileCoord {
+  int m, n;
+};
+__device__ __forceinline__ TileCoord tile_coord(int64_t idx, int tiles_m, int tiles_n) {
+  const int64_t per_group = (int64_t)GROUP_M * tiles_n;
+  const int g = (int)(idx / per_group);
+  const int first_m = g * GROUP_M;
+  const int gsz = min(GROUP_M, tiles_m - first_m);
+  const int64_t in_g = idx - (int64_t)g * per_group;
+  TileCoord c;
+  c.m = first_m + (int)(in_g % gsz);
+  c.n = (int)(in_g / gsz);
+  return c;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int ncols, bool vec_ok) {
+  if constexpr (sizeof(OutT) == 2) {
+    if (vec_ok && ncols == 32) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          OutT lo = static_cast<OutT>(v[q * 8 + 2 * e]), hi = static_cast<OutT>(v[q * 8 + 2 * e + 1]);
+          w[e] = (uint32_t)(*reinterpret_cast<unsigned short*>(&lo)) |
+                 ((uint32_t)(*reinterpret_cast<unsigned short*>(&hi)) << 16);
+        }
+        *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      return;
+    }
+  } else {
+    if (vec_ok && ncols == 32) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      return;
+    }
+  }
+  for (int e = 0; e < 32; ++e)
+    if (e < ncols) dst[e] = static_cast<OutT>(v[e]);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                const float* __restrict__ scale_a, const float* __restrict__ scale_b, const OutT* __restrict__ bias,
+                OutT* __restrict__ out, int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+  const int num_kb = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 4);
+    }
+    bars->abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, bars, 1u)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * STAGE_BYTES;
+          mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tma_a, kb * BK, tc.m * BM, &bars->full[stage]);
+          tma_load_2d(sa + A_BYTES, &tma_b, kb * BK, tc.n * BN, &bars->full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let bulk copies already in flight land before the CTA's shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, bars, 2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, bars, 4u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // advancing 32 bytes along K inside the swizzle span = +2 in the 16-byte address field
+            tc_mma_f8(tmem_d, da + (uint64_t)(kk * (UMMA_K >> 4)), db + (uint64_t)(kk * (UMMA_K >> 4)), idesc,
+                      (kb | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit(&bars->empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    float inv = 0.f;
+    {
+      const float sa = __ldg(scale_a), sb = __ldg(scale_b);
+      inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
+    }
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const int acc = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, bars, 8u)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tc.m * BM + quarter * 32 + lane;
+      const int col0 = tc.n * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        const int col = col0 + c * 32;
+        int ncols = n - col;
+        if (ncols > 32) ncols = 32;
+        if (row < m && ncols > 0) {
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * inv;
+          if (bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (e < ncols) v[e] += static_cast<float>(bias[col + e]);
+          }
+          store_chunk<OutT>(out + (int64_t)row * ldo + col, v, ncols, out_vec_ok != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }
+  });
+  return fn;
+}
+
+// 2-D byte tensor [rows, k] with row stride ld, box = [box_rows, 128 bytes], 128B swizzle.
+static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return F8B200_ERR_DRIVER;
+  const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)ld};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
+}
+
+template <typename OutT>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa, const float* sb, const void* bias,
+                  void* out, int64_t ldo, int m, int n, int k, uint32_t idesc, int vec_ok, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_fp8_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
+  const int64_t tiles = (int64_t)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  int grid = sm_count();
+  if (tiles < grid) grid = (int)tiles;
+  gemm_fp8_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, sa, sb, static_cast<const OutT*>(bias),
+                                                                static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok);
+  return check_launch();
+}
+
+}  // namespace gemm
+}  // namespace f8b200
+
+using namespace f8b200;
+
+extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                               const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
+                               int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream) {
+  (void)use_fast_accum;  // tcgen05 accumulates in fp32 tensor memory either way
+  if (m < 0 || n < 0 || k < 0) return F8B200_ERR_BAD_ARG;
+  if (a_kind < 0 || a_kind > 1 || b_kind < 0 || b_kind > 1 || out_dtype < 0 || out_dtype > 2) return F8B200_ERR_BAD_ARG;
+  if (m == 0 || n == 0) return F8B200_OK;
+  if (a == nullptr || b == nullptr || out == nullptr || scale_a == nullptr || scale_b == nullptr) return F8B200_ERR_BAD_ARG;
+  if (k == 0) return F8B200_ERR_UNSUPPORTED;
+  if (lda < k || ldb < k || ldo < n) return F8B200_ERR_BAD_ARG;
+  if (m > 0x7FFFFFFFLL || n > 0x7FFFFFFFLL || k > 0x7FFFFFFFLL) return F8B200_ERR_UNSUPPORTED;
+  if (lda % 16 != 0 || ldb % 16 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(b) % 16 != 0)
+    return F8B200_ERR_ALIGNMENT;
+  const int osz = out_dtype == F8B200_FP32 ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(out) % osz != 0 || (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % osz != 0))
+    return F8B200_ERR_ALIGNMENT;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+
+  CUtensorMap ma, mb;
+  rc = gemm::encode_operand_map(&ma, a, m, k, lda, gemm::BM);
+  if (rc != F8B200_OK) return rc;
+  rc = gemm::encode_operand_map(&mb, b, n, k, ldb, gemm::BN);
+  if (rc != F8B200_OK) return rc;
+
+  const uint32_t idesc = gemm::make_idesc(a_kind, b_kind);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (out_dtype) {
+    case F8B200_BF16:
+      return gemm::launch<__nv_bfloat16>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+    case F8B200_FP16:
+      return gemm::launch<__half>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+    default:
+      return gemm::launch<float>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+  }
+}
+
+extern "C" int f8b200_read_device_error(uint32_t* flags_out) {
+  if (flags_out == nullptr) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  uint32_t v = 0;
+  rc = record_cuda_error(cudaMemcpyFromSymbol(&v, g_device_error, sizeof(v)));
+  if (rc != F8B200_OK) return rc;
+  const uint32_t zero = 0;
+  rc = record_cuda_error(cudaMemcpyToSymbol(g_device_error, &zero, sizeof(zero)));
+  *flags_out = v;
+  return rc;
+}

@@ -1,0 +1,170 @@
+/*
+ * f8b200.h -- C ABI of the B200 (sm_100a) float8 training kernels.
+ *
+ * This is the drop-in boundary for the Float8Linear hot path of
+ * pytorch-labs/float8_experimental.  The reference reaches its arithmetic through
+ * PyTorch operators; each entry point below names the reference call site(s) it
+ * replaces (paths are relative to the reference project root).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - calls are asynchronous with respect to the host and never synchronise;
+ *   - the library allocates nothing: all buffers belong to the caller;
+ *   - every call returns an int status (0 = ok, negative = error, see below), never
+ *     throws, aborts or traps;
+ *   - fp8 tensors are raw bytes (OCP e4m3fn / e5m2 bit patterns).
+ */
+#ifndef F8B200_H_
+#define F8B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* high-precision element types */
+#define F8B200_BF16 0
+#define F8B200_FP16 1
+#define F8B200_FP32 2
+
+/* fp8 formats */
+#define F8B200_E4M3 0 /* torch.float8_e4m3fn, max 448   */
+#define F8B200_E5M2 1 /* torch.float8_e5m2,   max 57344 */
+
+/* status codes */
+#define F8B200_OK 0
+#define F8B200_ERR_BAD_ARG (-1)     /* null pointer, negative size, unknown enum      */
+#define F8B200_ERR_ALIGNMENT (-2)   /* pointer or leading dimension not aligned       */
+#define F8B200_ERR_ARCH (-3)        /* current device is not compute capability 10.x  */
+#define F8B200_ERR_LAUNCH (-4)      /* CUDA reported an error at launch               */
+#define F8B200_ERR_DRIVER (-5)      /* tensor-map encode / driver entry point failed  */
+#define F8B200_ERR_UNSUPPORTED (-6) /* valid request the kernels do not implement     */
+#define F8B200_ERR_TIMEOUT (-7)     /* a bounded device-side wait ran out             */
+
+const char* f8b200_status_string(int status);
+
+/* 0 when the current device can run these kernels (compute capability 10.x). */
+int f8b200_device_check(void);
+
+/* Text of the last CUDA error seen by this library on the calling thread. */
+const char* f8b200_last_cuda_error(void);
+
+/*
+ * amax = max |x| over `numel` contiguous elements, written to amax_out[0] as fp32
+ * (exactly representable: it is one of the inputs).  NaN anywhere gives NaN.
+ * Replaces torch.max(torch.abs(x)) in float8_experimental/float8_utils.py:102-104
+ * (tensor_to_amax).  numel == 0 is F8B200_ERR_BAD_ARG (torch.max raises there).
+ */
+int f8b200_amax(const void* x, int hp_dtype, int64_t numel, float* amax_out, void* stream);
+
+/*
+ * Same reduction for `n` separate tensors in one launch: amax_out[i] = max |x_i|.
+ * `ptrs` and `numels` are HOST arrays of length n (device pointers inside `ptrs`).
+ * A tensor with numels[i] == 0 yields 0.  Replaces torch._foreach_norm(weights, inf)
+ * in float8_experimental/fsdp_utils.py:62 (precompute_float8_dynamic_scale_for_fsdp).
+ */
+int f8b200_multi_amax(const void* const* ptrs, const int64_t* numels, int n, int hp_dtype,
+                      float* amax_out, void* stream);
+
+/*
+ * scale_out[i] = amax_to_scale(amax[i]) for i < n:
+ *   c = max(amax, RN_T(1e-12)); r = RN_T(1/c); s = RN_T(r * fp8_max);
+ *   if orig_dtype == FP16: s = min(s, 65504)
+ * with T = amax_dtype (the dtype the reference holds the amax in) and the result
+ * stored as fp32.  Replaces float8_experimental/float8_utils.py:35-57 (amax_to_scale),
+ * including the reciprocal-then-multiply evaluation of `fp8_max / clamp(amax, EPS)`.
+ */
+int f8b200_amax_to_scale(const float* amax, int64_t n, int fp8_kind, int amax_dtype,
+                         int orig_dtype, float* scale_out, void* stream);
+
+/*
+ * Saturating round-to-nearest-even cast of a [rows, cols] matrix (row stride ld_x
+ * elements) to fp8:  out = fp8(clamp(RN_P(x * scale), +-fp8_max)).
+ *
+ *   scale_src    0: `scale_in` points at the fp32 scale to use (delayed scaling,
+ *                   precomputed FSDP scale);
+ *                1: `scale_in` points at an fp32 amax; the kernel derives the scale
+ *                   from it exactly as f8b200_amax_to_scale(amax_dtype = orig_dtype =
+ *                   hp_dtype) and, when scale_out != NULL, stores it there (dynamic
+ *                   scaling).
+ *   product_fp32 0: the product x*scale is rounded to hp_dtype before the clamp
+ *                   (PyTorch semantics for a 0-dim scale); 1: it stays fp32 (scale of
+ *                   shape [1], or fp32 input).
+ *   out          row-major fp8 bytes, row stride ld_out; may be NULL.
+ *   out_t        the transposed copy [cols, rows], row stride ld_out_t; may be NULL.
+ *   amax_out     optional fp32 word that receives max |x| of this same read
+ *                (delayed scaling records the current amax while casting).
+ *   reverse      non-zero walks the tiles from the end of the tensor backwards, so
+ *                that a cast that follows an amax pass over the same tensor starts on
+ *                the part still held in L2.
+ *
+ * Replaces `tensor * scale` (float8_experimental/float8_tensor.py:158) +
+ * to_fp8_saturated (float8_utils.py:123-139), the scale computation of
+ * tensor_to_scale (float8_utils.py:115-120) in dynamic mode, the amax fill of
+ * hp_tensor_to_float8_delayed (float8_scaling_utils.py:89), and the layout copies of
+ * preprocess_addmm (float8_ops.py:150-153) through `out_t`.
+ */
+int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                int scale_src, const float* scale_in, float* scale_out, int product_fp32,
+                int fp8_kind, void* out, int64_t ld_out, void* out_t, int64_t ld_out_t,
+                float* amax_out, int reverse, void* stream);
+
+/*
+ * out[c, r] = in[r, c] for an fp8 (byte) matrix [rows, cols].  Replaces the
+ * `.contiguous()` / `.t().contiguous().t()` fix-ups in
+ * float8_experimental/float8_ops.py:150-153 when no transposed copy was emitted by
+ * the cast (for example an fp8 weight that arrived through the FSDP all-gather).
+ */
+int f8b200_transpose_u8(const void* in, int64_t rows, int64_t cols, int64_t ld_in, void* out,
+                        int64_t ld_out, void* stream);
+
+/*
+ * Delayed-scaling bookkeeping for R = n_input + n_weight + n_grad_output rows in one
+ * launch.  Per row r:  rolled = [amax[r], hist[r,0..H-2]];
+ *   scale[r] = amax_to_scale(max(rolled))  in fp32 arithmetic, with fp8_max = 448 for
+ *   the first n_e4m3 rows and 57344 for the rest, and the fp16 clamp when
+ *   orig_dtype == F8B200_FP16.
+ * hist_out == NULL leaves the history untouched (what the reference does: it rolls a
+ * stacked copy and never writes it back); otherwise the rolled history is written to
+ * hist_out (may alias hist).  Replaces _update_history_stack +
+ * amax_history_to_scale_stack + the per-layer copy_ loops in
+ * float8_experimental/float8_linear_utils.py:286-319 and float8_utils.py:80-99.
+ */
+int f8b200_delayed_sync(const float* amax, const float* hist, int64_t ld_hist, int64_t rows,
+                        int hist_len, int64_t n_e4m3, int orig_dtype, float* scale_out,
+                        float* hist_out, int64_t ld_hist_out, void* stream);
+
+/*
+ * out[M,N] = (A[M,K] . B[N,K]^T) * (1/scale_a) * (1/scale_b) (+ bias[N]) in out_dtype.
+ *
+ *   a, b      fp8 bytes, both with K contiguous ("row-major A, column-major B" in the
+ *             reference's words); lda, ldb in elements, multiples of 16, bases 16-byte
+ *             aligned (TMA requirement).
+ *   scale_a/b fp32 words holding the scales the operands were MULTIPLIED by when they
+ *             were cast; the kernel divides them out in its epilogue.
+ *   bias      optional [N] vector in out_dtype.
+ *   out       row-major, row stride ldo elements, dtype F8B200_BF16/FP16/FP32.
+ *   fp32 accumulation in tensor memory; use_fast_accum is accepted and ignored.
+ *
+ * Replaces addmm_float8_unwrapped -> torch._scaled_mm in
+ * float8_experimental/float8_python_api.py:24-64 (and the two scale.reciprocal()
+ * launches at :39-40, and the bias add at float8_linear.py:368-369).
+ */
+int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                    const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
+                    void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum,
+                    void* stream);
+
+/*
+ * Reads and clears the device error word of the current device (synchronises the
+ * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
+ * last read; the result of that launch is undefined.  Test and debugging aid.
+ */
+int f8b200_read_device_error(uint32_t* flags_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* F8B200_H_ */
