@@ -1,0 +1,372 @@
+"""Benchmark of the Float8Linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 2): the four LLaMa-2-70B linear shapes, M = 16384 tokens,
+dynamic scaling of input / weight / grad_output, bf16 in and out.  One "step" is one
+forward + backward of each of the four `Float8Linear` layers through the public module
+API (3 amax reductions, 3 casts, 3 fp8 GEMMs per layer).  FLOPs per layer = 3*2*M*K*N.
+Inputs are synthetic (seeded normal draws of the configured scales).
+
+Prints ONE JSON line on rank 0 (see `main`).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_TOKENS = 16384
+SHAPES = [("wqkv", 8192, 10240), ("wo", 8192, 8192), ("w13", 8192, 57344), ("w2", 28672, 8192)]
+METRIC = "Float8Linear fwd+bwd TFLOP/s (LLaMa-2-70B shapes); amax+cast HBM GB/s"
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def layer_flops(k: int, n: int, m: int = M_TOKENS) -> float:
+    return 3.0 * 2.0 * m * k * n
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d} | {"source": "measured"}
+    return dict(FALLBACK_PEAKS) | {"source": "fallback"}
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, power = [], [], []
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load: the upper half by power draw
+        cut = statistics.median(power)
+        loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's emulate path
+# ---------------------------------------------------------------------------
+def cpu_sample_step(sample):
+    from oracle import f8_oracle as O
+
+    return O.float8_linear_fwd_bwd(sample["x"], sample["w"], sample["go"], O.BF16)
+
+
+def make_cpu_sample(rows: int = 256):
+    """`rows` tokens of the `wo` layer (K = N = 8192)."""
+    import numpy as np
+
+    from oracle import f8_oracle as O
+
+    rng = np.random.default_rng(7)
+    k, n = SHAPES[1][1], SHAPES[1][2]
+    f = lambda a: O.f32_to_bf16_bits(a.astype(np.float32))  # noqa: E731
+    return {"x": f(rng.standard_normal((rows, k))), "w": f(rng.standard_normal((n, k)) * 0.02),
+            "go": f(rng.standard_normal((rows, n)) * 1e-3), "rows": rows, "k": k, "n": n,
+            "flops": layer_flops(k, n, rows),
+            "desc": f"wo layer (K=N=8192) fwd+bwd on {rows} of {M_TOKENS} token rows, numpy port of the emulate=True path"}
+
+
+def time_cpu(sample, steps: int, warmup: int):
+    for _ in range(warmup):
+        cpu_sample_step(sample)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_sample_step(sample)
+        ts.append(time.perf_counter() - t0)
+    return ts
+
+
+def run_reference_arm(args, rank: int, world: int):
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    sample = make_cpu_sample()
+    ts = time_cpu(sample, steps, warmup)
+    tflops = sample["flops"] / statistics.median(ts) / 1e12
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": statistics.median(ts) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {"workload": "LLaMa-2-70B linear shapes, M=16384, dynamic scaling (CPU arm: bounded sample)",
+                   "sample": sample["desc"]},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample["desc"]},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_gpu_arm(args, rank: int, local_rank: int, world: int):
+    import torch
+    import torch.distributed as dist
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200 import _native
+    from float8_experimental_b200.float8_linear import Float8Linear
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    _native.load()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    layers, xs, gos, host = [], [], [], []
+    for name, k, n in SHAPES:
+        lin = torch.nn.Linear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            lin.weight.normal_(0.0, 0.02, generator=gen)
+        layers.append(Float8Linear.from_float(lin, f8.Float8LinearConfig()))
+        xs.append(torch.randn(M_TOKENS, k, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True))
+        gos.append(torch.randn(M_TOKENS, n, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3))
+
+    def step():
+        for layer, x, go in zip(layers, xs, gos):
+            x.grad = None
+            layer.weight.grad = None
+            layer(x).backward(go)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _native.reset_counters()
+    _native.enable_kernel_events(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    _native.enable_kernel_events(False)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    launches = _native.launch_count()
+    kernel_ms = _native.kernel_event_totals()  # {"gemm": (ms, calls), "cast": ..., "amax": ...}
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = t.item()
+    ms_per_step = ms_total / args.steps
+    flops_per_step = sum(layer_flops(k, n) for _, k, n in SHAPES)
+    value = world * flops_per_step / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host inputs, H2D per step, D2H of a result ------
+    for x, go in zip(xs, gos):
+        host.append((torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x.detach()),
+                     torch.empty(go.shape, dtype=go.dtype, pin_memory=True).copy_(go)))
+    result_host = torch.empty(len(SHAPES), 8, dtype=torch.bfloat16, pin_memory=True)
+    copy_stream = torch.cuda.Stream(device=dev)
+    h2d_bytes = sum(hx.numel() * 2 + hg.numel() * 2 for hx, hg in host)
+    d2h_bytes = result_host.numel() * 2
+
+    def e2e_step():
+        main = torch.cuda.current_stream()
+        ready = []
+        copy_stream.wait_stream(main)  # previous step's readers are done with the buffers
+        with torch.cuda.stream(copy_stream):
+            for (hx, hg), x, go in zip(host, xs, gos):
+                x.detach().copy_(hx, non_blocking=True)
+                go.copy_(hg, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+                ready.append(ev)
+        for i, (layer, x, go) in enumerate(zip(layers, xs, gos)):
+            main.wait_event(ready[i])
+            x.grad = None
+            layer.weight.grad = None
+            layer(x).backward(go)
+            result_host[i].copy_(layer.weight.grad[0, :8], non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = t.item()
+    e2e_value = world * flops_per_step / e2e_s / 1e12
+
+    # ---- library kernel to beat, outside every timed region -----------------
+    cublaslt = None
+    if rank == 0:
+        try:
+            k, n = SHAPES[1][1], SHAPES[1][2]
+            a = torch.randn(M_TOKENS, k, device=dev).to(torch.float8_e4m3fn)
+            b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
+            one = torch.tensor(1.0, device=dev)
+            f = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, use_fast_accum=True)  # noqa: E731
+            for _ in range(3):
+                f()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(10):
+                f()
+            s1.record()
+            torch.cuda.synchronize()
+            cublaslt = 2.0 * M_TOKENS * k * n / (s0.elapsed_time(s1) / 10 * 1e-3) / 1e12
+            del a, b
+        except Exception as e:  # pragma: no cover
+            cublaslt = f"unavailable: {e}"
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    gemm_ms, gemm_calls = kernel_ms.get("gemm", (0.0, 0))
+    cast_ms, cast_calls = kernel_ms.get("cast", (0.0, 0))
+    amax_ms, amax_calls = kernel_ms.get("amax", (0.0, 0))
+    gemm_flops = args.steps * flops_per_step
+    gemm_tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # dynamic amax+cast of n bf16 elements with the transposed copy: 2n + 2n + n + n bytes
+    cast_elems = args.steps * sum(M_TOKENS * k + n * k + M_TOKENS * n for _, k, n in SHAPES)
+    cast_gbs = 6.0 * cast_elems / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
+
+    # bounded CPU sample (rank 0, N = 1 only)
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample = make_cpu_sample()
+        ts = time_cpu(sample, 2, 0)
+        cpu_baseline = {"value": sample["flops"] / min(ts) / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
+                        "kind": "port", "sample": sample["desc"]}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {
+            "workload": "LLaMa-2-70B linear shapes (wqkv, wo, w13, w2), M=16384 tokens per GPU, Float8Linear fwd+bwd, "
+                        "dynamic scaling, bf16 in/out",
+            "shapes_KN": {name: [k, n] for name, k, n in SHAPES},
+            "l2": "inputs larger than L2 (smallest tensor cast per layer is 134 MB; L2 is 126 MB)",
+            "parallelism": "replicas" if world > 1 else "single",
+        },
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": launches,
+        "roofline": {
+            "kernel": "gemm_fp8_kernel (tcgen05 kind::f8f6f4)", "bound": "tensor", "achieved": gemm_tflops,
+            "peak": fp8_peak, "unit": "TFLOP/s", "frac": (gemm_tflops / fp8_peak) if gemm_tflops else None,
+            "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (fp8 issues at twice the bf16 rate)",
+            "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
+            "launches": gemm_calls, "traffic": None,
+        },
+        "roofline_cast": {
+            "kernel": "amax_flat_kernel + cast_tile_kernel (dynamic amax+cast with transposed copy)", "bound": "hbm",
+            "achieved": cast_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": (cast_gbs / peaks["hbm_gbs"]) if cast_gbs else None,
+            "frac_of_nominal_8000": (cast_gbs / NOMINAL_HBM_GBS) if cast_gbs else None,
+            "algorithmic_bytes": "6 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8 + 1 transposed fp8)",
+            "launches": cast_calls + amax_calls, "traffic": None,
+        },
+        "time_share_ms_per_step": {"gemm": gemm_ms / args.steps, "cast": cast_ms / args.steps,
+                                   "amax": amax_ms / args.steps},
+        "cublaslt_fp8_tflops_wo_fwd": cublaslt,
+        "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+    run_gpu_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
   const bool col_ok = col < p.cols;
   const float s = load_scale<HP>(p, (KIND == F8B200_E4M3) ? kE4M3Max : kE5M2Max);
   const char* xb = static_cast<const char*>(p.x);
+  const bool round_to_hp = (ES == 2) && !p.product_fp32;
 
   uint32_t rw[16];
   AbsMax<HP> acc;
@@ -238,11 +239,7 @@ __global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v[i].y));
         f0 = a.x; f1 = a.y; f2 = b.x; f3 = b.y;
       }
-      float p0 = __fmul_rn(f0, s), p1 = __fmul_rn(f1, s), p2 = __fmul_rn(f2, s), p3 = __fmul_rn(f3, s);
-      if (!p.product_fp32) {
-        p0 = round_hp<HP>(p0); p1 = round_hp<HP>(p1); p2 = round_hp<HP>(p2); p3 = round_hp<HP>(p3);
-      }
-      rw[i] = cvt_pair<KIND>(p0, p1) | (cvt_pair<KIND>(p2, p3) << 16);
+      rw[i] = cast4<HP, KIND>(__fmul_rn(f0, s), __fmul_rn(f1, s), __fmul_rn(f2, s), __fmul_rn(f3, s), round_to_hp);
     }
   } else {
 #pragma unroll
@@ -257,9 +254,9 @@ __global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         acc.add_word(v[i].x); acc.add_word(v[i].y); acc.add_word(v[i].z); acc.add_word(v[i].w);
-        const float p0 = __fmul_rn(__uint_as_float(v[i].x), s), p1 = __fmul_rn(__uint_as_float(v[i].y), s);
-        const float p2 = __fmul_rn(__uint_as_float(v[i].z), s), p3 = __fmul_rn(__uint_as_float(v[i].w), s);
-        rw[h * 8 + i] = cvt_pair<KIND>(p0, p1) | (cvt_pair<KIND>(p2, p3) << 16);
+        rw[h * 8 + i] = cast4<HP, KIND>(__fmul_rn(__uint_as_float(v[i].x), s), __fmul_rn(__uint_as_float(v[i].y), s),
+                                        __fmul_rn(__uint_as_float(v[i].z), s), __fmul_rn(__uint_as_float(v[i].w), s),
+                                        false);
       }
     }
   }

@@ -66,6 +66,45 @@ __device__ __forceinline__ uint32_t cvt_pair(float a, float b) {
   return r;
 }
 
+// Same rounding as round_hp, but bf16 goes through integer arithmetic (add half an
+// ulp, ties to even, truncate) instead of the conversion pipe.  NaN inputs may come out
+// as arbitrary values: callers test the UNROUNDED value for NaN.
+template <int HP>
+__device__ __forceinline__ float round_hp_fast(float v) {
+  if constexpr (HP == F8B200_BF16) {
+    uint32_t u = __float_as_uint(v);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return __uint_as_float(u & 0xFFFF0000u);
+  } else {
+    return round_hp<HP>(v);
+  }
+}
+
+// cvt_pair without the NaN fix-up.
+template <int KIND>
+__device__ __forceinline__ uint32_t cvt_pair_raw(float a, float b) {
+  const __nv_fp8_interpretation_t interp = (KIND == F8B200_E4M3) ? __NV_E4M3 : __NV_E5M2;
+  return __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, interp);
+}
+
+// Four products -> four fp8 bytes (byte i = element i): optional rounding to the
+// high-precision dtype, saturating RNE conversion, NaN forced to 0x7F.
+template <int HP, int KIND>
+__device__ __forceinline__ uint32_t cast4(float q0, float q1, float q2, float q3, bool round_to_hp) {
+  float p0 = q0, p1 = q1, p2 = q2, p3 = q3;
+  if (round_to_hp) {
+    p0 = round_hp_fast<HP>(q0); p1 = round_hp_fast<HP>(q1); p2 = round_hp_fast<HP>(q2); p3 = round_hp_fast<HP>(q3);
+  }
+  uint32_t w = cvt_pair_raw<KIND>(p0, p1) | (cvt_pair_raw<KIND>(p2, p3) << 16);
+  if ((q0 != q0) | (q1 != q1) | (q2 != q2) | (q3 != q3)) {
+    if (q0 != q0) w = (w & 0xFFFFFF00u) | 0x0000007Fu;
+    if (q1 != q1) w = (w & 0xFFFF00FFu) | 0x00007F00u;
+    if (q2 != q2) w = (w & 0xFF00FFFFu) | 0x007F0000u;
+    if (q3 != q3) w = (w & 0x00FFFFFFu) | 0x7F000000u;
+  }
+  return w;
+}
+
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
   return __reduce_max_sync(0xFFFFFFFFu, v);
 }

@@ -1,0 +1,121 @@
+"""TEST-ONLY: CPU implementations of the `f8b200::*` ops backed by the numpy oracle.
+
+The package ships CUDA implementations only.  Host-side logic (module swap, autograd
+wiring, the Float8Tensor operator table, sync bookkeeping, FSDP2 / DTensor hooks over
+gloo) still has to be testable on a machine without a GPU, so the tests register these
+stand-ins under the CPU dispatch key.  Nothing outside `tests/` imports this file.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import float8_experimental_b200._ops  # noqa: F401  (defines the op schemas)
+from float8_experimental_b200 import _native as N
+from oracle import f8_oracle as O
+
+_HP = {torch.bfloat16: O.BF16, torch.float16: O.FP16, torch.float32: O.FP32}
+_HP_BY_CODE = {N.BF16: O.BF16, N.FP16: O.FP16, N.FP32: O.FP32}
+_F8 = {N.E4M3: O.E4M3, N.E5M2: O.E5M2}
+_installed = False
+
+
+def to_np(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().contiguous()
+    if t.dtype == torch.float32:
+        return t.numpy()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.view(torch.uint8).numpy()
+
+
+def from_np(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+    a = np.ascontiguousarray(a)
+    if dtype == torch.float32:
+        return torch.from_numpy(a.astype(np.float32))
+    if dtype in (torch.bfloat16, torch.float16):
+        return torch.from_numpy(a.view(np.int16).copy()).view(dtype)
+    return torch.from_numpy(a.copy()).view(dtype)
+
+
+def _amax(x):
+    return torch.tensor(float(O.tensor_to_amax(to_np(x), _HP[x.dtype])), dtype=torch.float32)
+
+
+def _multi_amax(xs):
+    return torch.tensor([float(O.tensor_to_amax(to_np(x), _HP[x.dtype])) if x.numel() else 0.0 for x in xs],
+                        dtype=torch.float32)
+
+
+def _amax_to_scale(amax, fp8_kind, amax_dtype, orig_dtype):
+    s = O.amax_to_scale(amax.float().numpy(), _F8[fp8_kind], _HP_BY_CODE[orig_dtype], _HP_BY_CODE[amax_dtype])
+    return torch.from_numpy(np.asarray(s, dtype=np.float32).reshape(tuple(amax.shape)).copy())
+
+
+def _cast_outputs(x, bits, fp8_kind, with_transpose):
+    f8 = N.FP8_DTYPE[fp8_kind]
+    data = from_np(bits.reshape(tuple(x.shape)), f8)
+    if with_transpose:
+        cols = x.shape[-1]
+        data_t = from_np(bits.reshape(-1, cols).T.copy(), f8)
+    else:
+        data_t = torch.empty((0,), dtype=f8)
+    return data, data_t
+
+
+def _cast_from_amax(x, amax, fp8_kind, with_transpose):
+    name = _HP[x.dtype]
+    scale = np.float32(O.amax_to_scale(np.float32(amax.item()), _F8[fp8_kind], name, name))
+    bits = O.cast_to_fp8(to_np(x), name, scale, _F8[fp8_kind], name)
+    data, data_t = _cast_outputs(x, bits, fp8_kind, with_transpose)
+    return data, data_t, torch.tensor(float(scale), dtype=torch.float32)
+
+
+def _cast_with_scale(x, scale, fp8_kind, product_fp32, with_transpose, amax_out):
+    name = _HP[x.dtype]
+    bits = O.cast_to_fp8(to_np(x), name, np.float32(scale.float().item()), _F8[fp8_kind],
+                         O.FP32 if product_fp32 else name)
+    if amax_out is not None:
+        amax_out.fill_(float(O.tensor_to_amax(to_np(x), name)))
+    return _cast_outputs(x, bits, fp8_kind, with_transpose)
+
+
+def _transpose_fp8(x):
+    return x.view(torch.uint8).t().contiguous().view(x.dtype)
+
+
+def _delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out, hist_out):
+    rows = hist.shape[0]
+    kinds = [O.E4M3] * min(n_e4m3, rows) + [O.E5M2] * max(rows - n_e4m3, 0)
+    scales, rolled = O.sync_amax_and_scale(amax.numpy(), hist.numpy(), kinds, _HP_BY_CODE[orig_dtype], True)
+    scale_out.copy_(torch.from_numpy(scales.copy()))
+    if hist_out is not None:
+        hist_out.copy_(torch.from_numpy(rolled.copy()))
+
+
+def _scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum):
+    fa = O.E4M3 if a.dtype == torch.float8_e4m3fn else O.E5M2
+    fb = O.E4M3 if b_t.dtype == torch.float8_e4m3fn else O.E5M2
+    out = O.mm_float8_emulated(to_np(a), fa, scale_a.float().item(), to_np(b_t).T, fb, scale_b.float().item(), O.FP32)
+    res = torch.from_numpy(np.ascontiguousarray(out))
+    if bias is not None:
+        res = res + bias.float()
+    return res.to(out_dtype)
+
+
+def install() -> None:
+    """Registers the CPU stand-ins once per process."""
+    global _installed
+    if _installed:
+        return
+    lib = torch.library.Library("f8b200", "IMPL")
+    lib.impl("amax", _amax, "CPU")
+    lib.impl("multi_amax", _multi_amax, "CPU")
+    lib.impl("amax_to_scale", _amax_to_scale, "CPU")
+    lib.impl("cast_from_amax", _cast_from_amax, "CPU")
+    lib.impl("cast_with_scale", _cast_with_scale, "CPU")
+    lib.impl("transpose_fp8", _transpose_fp8, "CPU")
+    lib.impl("delayed_sync", _delayed_sync, "CPU")
+    lib.impl("scaled_mm", _scaled_mm, "CPU")
+    install._lib = lib  # keep the registrations alive
+    _installed = True

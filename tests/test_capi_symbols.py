@@ -1,0 +1,43 @@
+"""The C-ABI library builds, loads and exports every symbol the header declares.
+No compute calls: this runs on machines without a GPU."""
+import ctypes
+import os
+import re
+
+from float8_experimental_b200 import _native
+from float8_experimental_b200.csrc import build as builder
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "f8b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(f8b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    path = builder.build()
+    assert os.path.exists(path)
+    lib = ctypes.CDLL(path)
+    names = declared_symbols()
+    assert len(names) >= 11
+    for name in names:
+        assert hasattr(lib, name), name
+    assert sorted(_native.EXPORTS) == names
+
+
+def test_status_strings_and_argument_validation():
+    lib = _native.load()
+    assert lib.f8b200_status_string(0) == b"ok"
+    for code in range(-7, 0):
+        assert lib.f8b200_status_string(code) != b"unknown status"
+    # argument checks happen before any CUDA call
+    assert lib.f8b200_amax(None, 0, 16, None, None) == -1
+    assert lib.f8b200_amax(ctypes.c_void_p(16), 7, 16, ctypes.c_void_p(16), None) == -1
+    assert lib.f8b200_gemm_fp8(ctypes.c_void_p(16), 0, 8, ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(4),
+                               ctypes.c_void_p(4), None, 0, ctypes.c_void_p(16), 16, 4, 4, 16, 0, None) == -1
+    assert lib.f8b200_gemm_fp8(ctypes.c_void_p(16), 0, 24, ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(4),
+                               ctypes.c_void_p(4), None, 0, ctypes.c_void_p(16), 16, 4, 4, 16, 0, None) == -2
+    assert lib.f8b200_cast(ctypes.c_void_p(16), 0, 4, 4, 2, 0, ctypes.c_void_p(4), None, 0, 0, None, 0, None, 0,
+                           None, 0, None) == -1

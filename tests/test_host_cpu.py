@@ -1,0 +1,353 @@
+"""Host-side logic on CPU: the package's Python layer runs unchanged, the `f8b200::*`
+ops are served by the oracle-backed stand-ins from `tests/oracle_backend.py`."""
+import copy
+import io
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+import oracle_backend
+from oracle import f8_oracle as O
+
+oracle_backend.install()
+
+import float8_experimental_b200 as f8  # noqa: E402
+from float8_experimental_b200 import float8_linear_utils  # noqa: E402
+from float8_experimental_b200.float8_linear import Float8Linear  # noqa: E402
+from float8_experimental_b200.float8_ops import FLOAT8_OPS_TABLE  # noqa: E402
+from float8_experimental_b200.float8_scaling_utils import (  # noqa: E402
+    hp_tensor_to_float8_delayed,
+    hp_tensor_to_float8_dynamic,
+)
+from float8_experimental_b200.float8_tensor import (  # noqa: E402
+    Float8Tensor,
+    GemmInputRole,
+    hp_tensor_and_scale_to_float8,
+    LinearMMConfig,
+    ScaledMMConfig,
+)
+from float8_experimental_b200.float8_utils import (  # noqa: E402
+    amax_to_scale,
+    compute_error,
+    e4m3_dtype,
+    e5m2_dtype,
+    fp8_tensor_statistics,
+    tensor_to_amax,
+    tensor_to_scale,
+    to_fp8_saturated,
+)
+
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+F8 = {"e4m3fn": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def t_from(arr, dname):
+    return oracle_backend.from_np(arr, DT[dname])
+
+
+def delayed_config(**kw):
+    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    return f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d, **kw)
+
+
+def make_linear(w, config):
+    lin = nn.Linear(w.shape[1], w.shape[0], bias=False, dtype=w.dtype)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    return Float8Linear.from_float(lin, config)
+
+
+# ---------------------------------------------------------------------------
+def test_casts_through_public_functions(golden_dir):
+    g = np.load(os.path.join(golden_dir, "casts.npz"))
+    cfg = LinearMMConfig()
+    for i in range(int(g["n"])):
+        dname, fname = [str(s) for s in g[f"c{i}_meta"]]
+        x = t_from(g[f"c{i}_x"], dname)
+        dyn = hp_tensor_to_float8_dynamic(x, F8[fname], cfg)
+        assert isinstance(dyn, Float8Tensor) and dyn._scale.dim() == 0 and dyn._scale.dtype == torch.float32
+        assert np.array_equal(oracle_backend.to_np(dyn._data), g[f"c{i}_dyn_bits"])
+        assert dyn._scale.item() == g[f"c{i}_dyn_scale"]
+        buf = torch.tensor([0.0])
+        dly = hp_tensor_to_float8_delayed(x, torch.from_numpy(g[f"c{i}_del_scale"].copy()), F8[fname], buf, cfg)
+        assert np.array_equal(oracle_backend.to_np(dly._data), g[f"c{i}_del_bits"])
+        assert buf.item() == g[f"c{i}_del_amax"][0]
+        # the emitted second layout holds the same values
+        if dyn._alt is not None:
+            flat = dyn._data.reshape(-1, dyn._data.shape[-1]).view(torch.uint8)
+            assert torch.equal(dyn._alt.view(torch.uint8), flat)
+            assert dyn._alt.stride(0) == 1
+
+
+def test_scale_helpers_match_reference_semantics():
+    x = torch.randn(64, 32, dtype=torch.bfloat16)
+    amax = tensor_to_amax(x)
+    assert amax.dtype == torch.bfloat16 and amax.dim() == 0
+    assert amax == x.abs().max()
+    s = tensor_to_scale(x, e4m3_dtype)
+    assert s.dtype == torch.float32
+    # scale computed in bf16: representable in bf16
+    assert s == s.to(torch.bfloat16).float()
+    tiny = torch.tensor([1e-7], dtype=torch.float16)
+    assert torch.isfinite(amax_to_scale(tiny.abs().max(), e4m3_dtype, torch.float16))
+    assert amax_to_scale(torch.tensor(0.0, dtype=torch.float16), e5m2_dtype, torch.float16) == 65504.0
+    y = to_fp8_saturated(torch.tensor([1e6, -1e6, 1.0]), e4m3_dtype)
+    assert y.float().tolist() == [448.0, -448.0, 1.0]
+
+
+def test_linear_dynamic_matches_reference(golden_dir):
+    g = np.load(os.path.join(golden_dir, "linear_small.npz"))
+    for dname in ("bf16", "fp32"):
+        m = make_linear(t_from(g[f"{dname}_w"], dname), f8.Float8LinearConfig())
+        x = t_from(g[f"{dname}_x0"], dname).requires_grad_(True)
+        y = m(x)
+        assert y.dtype == DT[dname]
+        y.backward(t_from(g[f"{dname}_go0"], dname))
+        for got, key in ((y, "y"), (x.grad, "dx"), (m.weight.grad, "dw")):
+            ref = t_from(g[f"{dname}_dyn_{key}"], dname).float()
+            assert got.shape == ref.shape
+            assert compute_error(ref, got.detach().float()) > 55.0, (dname, key)
+
+
+def test_linear_delayed_three_iterations(golden_dir):
+    g = np.load(os.path.join(golden_dir, "linear_small.npz"))
+    dname = "bf16"
+    m = make_linear(t_from(g[f"{dname}_w"], dname), delayed_config())
+    names = ("input", "weight", "grad_output")
+    for it in range(3):
+        if it > 0:
+            f8.sync_float8_amax_and_scale_history(m)
+        x = t_from(g[f"{dname}_x{it}"], dname).requires_grad_(True)
+        m.weight.grad = None
+        y = m(x)
+        y.backward(t_from(g[f"{dname}_go{it}"], dname))
+        for n in names:
+            assert getattr(m, f"fp8_amax_{n}").item() == g[f"{dname}_del{it}_amax_{n}"][0], (it, n)
+            assert getattr(m, f"fp8_scale_{n}").item() == g[f"{dname}_del{it}_scale_{n}"][0], (it, n)
+            assert np.array_equal(getattr(m, f"fp8_amax_history_{n}").numpy(), g[f"{dname}_del{it}_hist_{n}"])
+        ref = t_from(g[f"{dname}_del{it}_y"], dname).float()
+        assert compute_error(ref, y.detach().float()) > 55.0
+    f8.sync_float8_amax_and_scale_history(m)
+    for n in names:
+        assert getattr(m, f"fp8_scale_{n}").item() == g[f"{dname}_del3_scale_{n}"][0]
+        assert np.array_equal(getattr(m, f"fp8_amax_history_{n}").numpy(), g[f"{dname}_del3_hist_{n}"])
+
+
+def test_forward_without_sync_raises(golden_dir):
+    m = make_linear(torch.randn(16, 32), delayed_config())
+    x = torch.randn(4, 32)
+    m(x)
+    with pytest.raises(AssertionError, match="amaxes and scales not synced"):
+        m(x)
+    f8.sync_float8_amax_and_scale_history(m)
+    m(x)
+
+
+def test_sync_batched_over_layers(golden_dir):
+    g = np.load(os.path.join(golden_dir, "sync.npz"))
+    for dname in ("bf16", "fp16", "fp32"):
+        amax, hist = g[f"{dname}_amax"], g[f"{dname}_hist"]
+        L = amax.shape[1]
+        model = nn.Sequential(*[nn.Linear(8, 8, bias=False) for _ in range(L)])
+        f8.convert_to_float8_training(model, config=delayed_config())
+        for i, layer in enumerate(model):
+            layer.last_seen_input_dtype = DT[dname]
+            for k, n in enumerate(("input", "weight", "grad_output")):
+                getattr(layer, f"fp8_amax_{n}").fill_(float(amax[k, i]))
+                getattr(layer, f"fp8_amax_history_{n}").copy_(torch.from_numpy(hist[k, i].copy()))
+        f8.sync_float8_amax_and_scale_history(model)
+        for i, layer in enumerate(model):
+            assert layer.amax_and_scale_synced
+            for k, n in enumerate(("input", "weight", "grad_output")):
+                assert getattr(layer, f"fp8_scale_{n}").item() == g[f"{dname}_scales"][k, i], (dname, n, i)
+                assert np.array_equal(getattr(layer, f"fp8_amax_history_{n}").numpy(), g[f"{dname}_hist_after"][k, i])
+        # second call reuses the slabs; buffers are views into them
+        slabs = getattr(model[0], "_f8_sync_slabs")
+        f8.sync_float8_amax_and_scale_history(model)
+        assert getattr(model[0], "_f8_sync_slabs") is slabs
+        assert model[1].fp8_scale_weight.data_ptr() == slabs.scale[L + 1 : L + 2].data_ptr()
+        # moving the module invalidates the views; the next sync re-packs
+        model.to(torch.float32)
+        f8.sync_float8_amax_and_scale_history(model)
+        assert getattr(model[0], "_f8_sync_slabs") is not slabs
+        assert model[2].fp8_scale_input.item() == g[f"{dname}_scales"][0, 2]
+
+
+def test_sync_write_back_flag():
+    model = nn.Sequential(nn.Linear(8, 8, bias=False))
+    f8.convert_to_float8_training(model, config=delayed_config())
+    model[0].last_seen_input_dtype = torch.float32
+    model[0].fp8_amax_input.fill_(3.0)
+    model[0].fp8_amax_history_input.copy_(torch.arange(16.0) / 16)
+    float8_linear_utils.WRITE_BACK_AMAX_HISTORY = True
+    try:
+        f8.sync_float8_amax_and_scale_history(model)
+    finally:
+        float8_linear_utils.WRITE_BACK_AMAX_HISTORY = False
+    h = model[0].fp8_amax_history_input
+    assert h[0] == 3.0 and torch.equal(h[1:], torch.arange(15.0) / 16)
+
+
+def test_sync_input_checks():
+    model = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8))
+    f8.convert_to_float8_training(model, config=delayed_config())
+    model[0].last_seen_input_dtype = torch.float32
+    model[1].last_seen_input_dtype = torch.bfloat16
+    with pytest.raises(ValueError, match="same last seen input_dtype"):
+        f8.sync_float8_amax_and_scale_history(model)
+    f8.sync_float8_amax_and_scale_history(nn.Sequential(nn.ReLU()))  # warns, returns
+
+
+# ---------------------------------------------------------------------------
+def test_module_swap_and_filter():
+    lin = nn.Linear(8, 16)
+    out = f8.convert_to_float8_training(copy.deepcopy(lin))
+    assert isinstance(out, Float8Linear) and out.bias is not None
+    assert 'scaling="i:dyn,w:dyn,go:dyn"' in repr(out)
+
+    class Root(nn.Linear):
+        def __init__(self):
+            super().__init__(4, 4)
+            self.child = nn.Linear(4, 4)
+
+    with pytest.raises(AssertionError, match="Does not support a root nn.Linear with children"):
+        f8.convert_to_float8_training(Root())
+
+    model = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Sequential(nn.Linear(16, 24), nn.Linear(24, 10)))
+    seen = []
+
+    def keep(mod, fqn):
+        seen.append(fqn)
+        return mod.out_features % 16 != 10 and fqn != "2.0"
+
+    f8.convert_to_float8_training(model, module_filter_fn=keep)
+    assert seen == ["0", "2.0", "2.1"]
+    assert isinstance(model[0], Float8Linear)
+    assert not isinstance(model[2][0], Float8Linear) and not isinstance(model[2][1], Float8Linear)
+    assert f8.linear_requires_sync(delayed_config()) and not f8.linear_requires_sync(f8.Float8LinearConfig())
+    with pytest.raises(AssertionError):
+        f8.DelayedScalingConfig(scale_fn_name="mean")
+
+
+def test_buffers_stay_fp32_and_state_dict_roundtrip():
+    m = make_linear(torch.randn(16, 32), delayed_config())
+    m.to(torch.bfloat16)
+    assert m.weight.dtype == torch.bfloat16
+    for name in m.always_float32_buffers:
+        assert getattr(m, name).dtype == torch.float32
+    sd = m.state_dict()
+    assert set(sd) == {"weight"} | {f"fp8_{k}_{n}" for k in ("amax", "amax_history", "scale")
+                                    for n in ("input", "weight", "grad_output")}
+    m2 = make_linear(torch.randn(16, 32), delayed_config()).to(torch.bfloat16)
+    m2.load_state_dict(sd)
+    assert torch.equal(m2.fp8_amax_history_weight, m.fp8_amax_history_weight)
+
+
+def test_float8_tensor_ops():
+    cfg = LinearMMConfig()
+    x = torch.randn(16, 32, dtype=torch.bfloat16)
+    a = hp_tensor_to_float8_dynamic(x, e4m3_dtype, cfg)
+    assert a.dtype == torch.bfloat16 and a._data.dtype == e4m3_dtype
+    # split / cat round trip is the identity on the bytes
+    parts = torch.split(a, 4, dim=0)
+    back = torch.cat(parts, dim=0)
+    assert isinstance(back, Float8Tensor) and torch.equal(back._data.view(torch.uint8), a._data.view(torch.uint8))
+    # t / transpose / view carry the second layout along
+    at = a.t()
+    assert at.shape == (32, 16) and at._alt is not None and at._alt.is_contiguous()
+    assert a.view(4, 4, 32).reshape(-1, 32)._alt is not None
+    assert a[2:5]._alt is None
+    # dequantisation
+    deq = a.to_original_precision()
+    assert deq.dtype == torch.bfloat16 and compute_error(x.float(), deq.float()) > 20
+    # copy_ rules
+    hp = torch.zeros(16, 32, dtype=torch.bfloat16)
+    hp.copy_(a)
+    assert torch.equal(hp, deq)
+    b = hp_tensor_and_scale_to_float8(x * 0.5, a._scale, e4m3_dtype, cfg)
+    a2 = a.detach().clone()
+    a2.copy_(b)
+    assert torch.equal(a2._data.view(torch.uint8), b._data.view(torch.uint8))
+    with pytest.raises(RuntimeError, match="Unsupported semantics for copy_"):
+        a2.copy_(x)
+    # index_put_
+    a3 = a.detach().clone()
+    a3[torch.tensor([0, 1])] = b[torch.tensor([2, 3])] if False else Float8Tensor(
+        b._data[2:4], b._scale, b._orig_dtype, b._linear_mm_config, b._gemm_input_role)
+    assert torch.equal(a3._data[0:2].view(torch.uint8), b._data[2:4].view(torch.uint8))
+    # unsupported op
+    with pytest.raises(NotImplementedError, match="this is not supported"):
+        torch.sin(a)
+    # statistics
+    z = hp_tensor_and_scale_to_float8(torch.tensor([[0.0, 1e9, 1.0, -1e9]]), torch.tensor(1.0), e4m3_dtype, cfg)
+    assert fp8_tensor_statistics(z) == (1, 2)
+
+
+def test_mm_config_mismatch_message():
+    x = torch.randn(16, 16, dtype=torch.bfloat16)
+    c1 = LinearMMConfig()
+    c2 = LinearMMConfig(ScaledMMConfig(True, False, False, False), c1.grad_input, c1.grad_weight)
+    a = hp_tensor_to_float8_dynamic(x, e4m3_dtype, c1)
+    b = hp_tensor_to_float8_dynamic(x, e4m3_dtype, c2, gemm_input_role=GemmInputRole.WEIGHT)
+    with pytest.raises(AssertionError, match="linear_mm_config.output mismatch"):
+        torch.mm(a, b.t())
+
+
+def test_backward_gemms_use_preemitted_layouts(monkeypatch):
+    calls = []
+    real = FLOAT8_OPS_TABLE  # noqa: F841
+    import float8_experimental_b200.float8_ops as fo
+
+    orig = fo.ops.transpose_fp8
+
+    class Spy:
+        def __getattr__(self, name):
+            if name == "transpose_fp8":
+                def wrapped(*a, **k):
+                    calls.append(1)
+                    return orig(*a, **k)
+                return wrapped
+            return getattr(torch.ops.f8b200, name)
+
+    monkeypatch.setattr(fo, "ops", Spy())
+    m = make_linear(torch.randn(48, 32, dtype=torch.bfloat16), f8.Float8LinearConfig())
+    x = torch.randn(2, 8, 32, dtype=torch.bfloat16, requires_grad=True)
+    m(x).sum().backward()
+    assert calls == [] and x.grad.shape == x.shape and m.weight.grad.shape == (48, 32)
+
+
+def test_autocast_output_dtype():
+    m = make_linear(torch.randn(16, 32), f8.Float8LinearConfig())
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=False):
+        assert m(torch.randn(4, 32)).dtype == torch.float32
+
+
+def test_weights_only_load_of_float8_tensor():
+    a = hp_tensor_to_float8_dynamic(torch.randn(8, 8), e4m3_dtype, LinearMMConfig())
+    buf = io.BytesIO()
+    torch.save(a, buf)
+    buf.seek(0)
+    b = torch.load(buf, weights_only=True)
+    assert isinstance(b, Float8Tensor) and torch.equal(b._data.view(torch.uint8), a._data.view(torch.uint8))
+
+
+def test_package_has_no_cpu_path():
+    code = (
+        "import torch, float8_experimental_b200 as f\n"
+        "from float8_experimental_b200.float8_linear import Float8Linear\n"
+        "m = Float8Linear.from_float(torch.nn.Linear(16, 16))\n"
+        "try:\n"
+        "    m(torch.randn(4, 16))\n"
+        "except Exception as e:\n"
+        "    print('RAISED', type(e).__name__)\n"
+        "else:\n"
+        "    print('RAN')\n"
+    )
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT)
+    assert "RAISED" in out.stdout, out.stdout + out.stderr
