@@ -174,7 +174,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     layers, xs, gos, host = [], [], [], []
-    for name, k, n in SHAPES:
+    shapes = [s for s in SHAPES if args.layers is None or s[0] in args.layers.split(",")]
+    for name, k, n in shapes:
         lin = torch.nn.Linear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
             lin.weight.normal_(0.0, 0.02, generator=gen)
@@ -218,14 +219,21 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = t.item()
     ms_per_step = ms_total / args.steps
-    flops_per_step = sum(layer_flops(k, n) for _, k, n in SHAPES)
+    flops_per_step = sum(layer_flops(k, n) for _, k, n in shapes)
     value = world * flops_per_step / (ms_per_step * 1e-3) / 1e12
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "layers": [s[0] for s in shapes], "value": value,
+                              "unit": "TFLOP/s", "ms_per_step": ms_per_step, "kernel_ms": kernel_ms}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end: pinned host inputs, H2D per step, D2H of a result ------
     for x, go in zip(xs, gos):
         host.append((torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x.detach()),
                      torch.empty(go.shape, dtype=go.dtype, pin_memory=True).copy_(go)))
-    result_host = torch.empty(len(SHAPES), 8, dtype=torch.bfloat16, pin_memory=True)
+    result_host = torch.empty(len(shapes), 8, dtype=torch.bfloat16, pin_memory=True)
     copy_stream = torch.cuda.Stream(device=dev)
     h2d_bytes = sum(hx.numel() * 2 + hg.numel() * 2 for hx, hg in host)
     d2h_bytes = result_host.numel() * 2
@@ -298,7 +306,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     gemm_tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     # dynamic amax+cast of n bf16 elements with the transposed copy: 2n + 2n + n + n bytes
-    cast_elems = args.steps * sum(M_TOKENS * k + n * k + M_TOKENS * n for _, k, n in SHAPES)
+    cast_elems = args.steps * sum(M_TOKENS * k + n * k + M_TOKENS * n for _, k, n in shapes)
     cast_gbs = 6.0 * cast_elems / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
 
     # bounded CPU sample (rank 0, N = 1 only)
@@ -316,7 +324,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         "config": {
             "workload": "LLaMa-2-70B linear shapes (wqkv, wo, w13, w2), M=16384 tokens per GPU, Float8Linear fwd+bwd, "
                         "dynamic scaling, bf16 in/out",
-            "shapes_KN": {name: [k, n] for name, k, n in SHAPES},
+            "shapes_KN": {name: [k, n] for name, k, n in shapes},
             "l2": "inputs larger than L2 (smallest tensor cast per layer is 134 MB; L2 is 126 MB)",
             "parallelism": "replicas" if world > 1 else "single",
         },
@@ -356,6 +364,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", default=None, help="comma list out of wqkv,wo,w13,w2 (default: all four)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-timed part only, short JSON; for profiler captures of a small case")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -363,7 +374,7 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
-    if args.warmup < 3:
+    if args.warmup < 3 and not args.kernel_only:
         args.warmup = 3
     run_gpu_arm(args, rank, local_rank, world)
 

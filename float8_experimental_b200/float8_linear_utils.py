@@ -174,8 +174,8 @@ def sync_float8_amax_and_scale_history(model: torch.nn.Module, fp8_layers=None) 
     if len(recipes) != 1:
         raise ValueError(f"All layers must have the same scale_fn recipe, got {recipes}")
     (x_dtype,) = x_dtypes
-    if x_dtype is None:
-        raise ValueError("sync_float8_amax_and_scale_history called before any forward pass")
+    # None (no forward seen yet) behaves like any non-fp16 dtype: no fp16 clamp of the scale
+    orig_code = N.hp_code(x_dtype) if x_dtype is not None else N.FP32
 
     anchor = fp8_layers[0]
     slabs: Optional[_SyncSlabs] = getattr(anchor, _SLABS_ATTR, None)
@@ -187,7 +187,7 @@ def sync_float8_amax_and_scale_history(model: torch.nn.Module, fp8_layers=None) 
         dist.all_reduce(slabs.amax, op=dist.ReduceOp.MAX)
 
     ops.delayed_sync(
-        slabs.amax, slabs.hist, 2 * slabs.n_layers, N.hp_code(x_dtype), slabs.scale,
+        slabs.amax, slabs.hist, 2 * slabs.n_layers, orig_code, slabs.scale,
         slabs.hist if WRITE_BACK_AMAX_HISTORY else None,
     )
     for m in fp8_layers:
