@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -341,6 +342,282 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   }
 }
 
+// ===========================================================================
+// Two-CTA variant: a cluster of two CTAs (two SMs) works on one 256x256 output tile
+// with tcgen05.mma.cta_group::2 (instruction shape M256 N256 K32).  CTA r of the pair
+// loads rows [128r, 128r+128) of the A tile and rows [128r, 128r+128) of the B tile, so
+// each SM stages 32 KB per k-block instead of 48 KB and the tensor core of each SM reads
+// half of B from its partner's shared memory.  Only the pair's leader (rank 0) issues
+// MMAs.  Cross-CTA signalling:
+//   full[s]        lives in the leader; both CTAs' TMA loads complete_tx on it
+//   empty[s]       one per CTA; released by a multicast tcgen05.commit from the leader
+//   tmem_full[a]   one per CTA; same multicast commit when a tile's MMAs are done
+//   tmem_empty[a]  lives in the leader; 8 arrivals (4 epilogue warps of each CTA)
+// No TMA load here uses cluster multicast: every CTA fetches its own boxes.
+// ===========================================================================
+namespace pair {
+
+constexpr int PBM = 256;  // rows of the pair tile (128 per CTA)
+constexpr int PBN = 256;  // columns of the pair tile (each CTA stages 128 of B's rows)
+constexpr int PSTAGES = 6;
+constexpr int PA_BYTES = 128 * BK;
+constexpr int PB_BYTES = 128 * BK;
+constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
+constexpr int PGROUP_M = 8;
+
+struct __align__(8) PairBarriers {
+  uint64_t full[PSTAGES];
+  uint64_t empty[PSTAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + (int)sizeof(PairBarriers);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t mbar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+      "[%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_cluster_addr)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once all
+// MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind) {
+  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(PBN >> 3) << 17) |
+         ((uint32_t)(PBM >> 4) << 24);
+}
+
+// Bounded wait that also raises the partner's abort flag when it gives up.
+__device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBarriers* bars, uint32_t peer_rank,
+                                          uint32_t who) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (bars->abort_flag != 0u) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
+    }
+  }
+  bars->abort_flag = 1u;
+  st_cluster_u32(mapa_u32(smem_u32(const_cast<uint32_t*>(&bars->abort_flag)), peer_rank), 1u);
+  atomicOr(&g_device_error, who | 0x100u);
+  return false;
+}
+
+__device__ __forceinline__ TileCoord pair_tile_coord(int64_t idx, int tiles_m, int tiles_n) {
+  const int64_t per_group = (int64_t)PGROUP_M * tiles_n;
+  const int g = (int)(idx / per_group);
+  const int first_m = g * PGROUP_M;
+  const int gsz = min(PGROUP_M, tiles_m - first_m);
+  const int64_t in_g = idx - (int64_t)g * per_group;
+  TileCoord c;
+  c.m = first_m + (int)(in_g % gsz);
+  c.n = (int)(in_g / gsz);
+  return c;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                     const float* __restrict__ scale_a, const float* __restrict__ scale_b,
+                     const OutT* __restrict__ bias, OutT* __restrict__ out, int64_t ldo, int m, int n, int k,
+                     uint32_t idesc, int out_vec_ok) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(tiles + PSTAGES * PSTAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t peer = rank ^ 1u;
+  const bool leader = rank == 0;
+  const int tiles_m = (m + PBM - 1) / PBM, tiles_n = (n + PBN - 1) / PBN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+  const int num_kb = (k + BK - 1) / BK;
+  const int64_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 8);
+    }
+    bars->abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters) {
+        const TileCoord tc = pair_tile_coord(t, tiles_m, tiles_n);
+        const int row_a = tc.m * PBM + (int)rank * 128;
+        const int row_b = tc.n * PBN + (int)rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * PSTAGE_BYTES;
+          if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
+          const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
+          tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader);
+          tma_load_2d_pair(sa + PA_BYTES, &tma_b, kb * BK, row_b, full_in_leader);
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // tail: every release the leader multicast to this CTA's empty barriers has landed
+      for (int s = 0; ok && s < PSTAGES; ++s) {
+        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u)) { ok = false; break; }
+        if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!pair_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, bars, peer, 2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * PBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * PSTAGE_BYTES);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + PA_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            tc_mma_f8_pair(tmem_d, da + (uint64_t)(kk * (UMMA_K >> 4)), db + (uint64_t)(kk * (UMMA_K >> 4)), idesc,
+                           (kb | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&bars->empty[stage]);
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit_pair(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int quarter = warp & 3;
+    float inv = 0.f;
+    {
+      const float sa = __ldg(scale_a), sb = __ldg(scale_b);
+      inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
+    }
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
+      const TileCoord tc = pair_tile_coord(t, tiles_m, tiles_n);
+      const int acc = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!pair_wait(&bars->tmem_full[acc], acc_phase, bars, peer, 8u)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tc.m * PBM + (int)rank * 128 + quarter * 32 + lane;
+      const int col0 = tc.n * PBN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PBN);
+#pragma unroll 1
+      for (int c = 0; c < PBN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        const int col = col0 + c * 32;
+        int ncols = n - col;
+        if (ncols > 32) ncols = 32;
+        if (row < m && ncols > 0) {
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * inv;
+          if (bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (e < ncols) v[e] += static_cast<float>(bias[col + e]);
+          }
+          store_chunk<OutT>(out + (int64_t)row * ldo + col, v, ncols, out_vec_ok != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0u));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers or TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace pair
+
 // ---- host side --------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -387,6 +664,52 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa,
   return check_launch();
 }
 
+template <typename OutT>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa, const float* sb, const void* bias,
+                       void* out, int64_t ldo, int m, int n, int k, uint32_t idesc, int vec_ok, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  static int max_clusters = 0;
+  auto kernel = pair::gemm_fp8_pair_kernel<OutT>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = pair::PSMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::PSMEM_BYTES);
+    if (attr_err == cudaSuccess) {
+      cfg.gridDim = dim3(2 * (sm_count() / 2));
+      attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+    }
+  });
+  if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
+  if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
+  const int64_t tiles = (int64_t)((m + pair::PBM - 1) / pair::PBM) * ((n + pair::PBN - 1) / pair::PBN);
+  int clusters = max_clusters;
+  if (tiles < clusters) clusters = (int)tiles;
+  cfg.gridDim = dim3(2 * clusters);
+  const OutT* bias_t = static_cast<const OutT*>(bias);
+  OutT* out_t = static_cast<OutT*>(out);
+  return record_cuda_error(
+      cudaLaunchKernelEx(&cfg, kernel, ma, mb, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok));
+}
+
+// 0 = one CTA per tile (128x256), 1 = CTA pairs (256x256, cta_group::2).  The environment
+// variable F8B200_GEMM_MODE ("1cta" / "2cta") overrides the default; it is read at every
+// call so that tests can exercise both kernels in one process.
+static int gemm_mode() {
+  const char* e = getenv("F8B200_GEMM_MODE");
+  if (e != nullptr && e[0] == '1') return 0;
+  return 1;
+}
+
 }  // namespace gemm
 }  // namespace f8b200
 
@@ -412,15 +735,36 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
 
+  const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap ma, mb;
+  if (gemm::gemm_mode() == 1) {
+    // each CTA of a pair fetches 128-row boxes of both operands
+    rc = gemm::encode_operand_map(&ma, a, m, k, lda, 128);
+    if (rc != F8B200_OK) return rc;
+    rc = gemm::encode_operand_map(&mb, b, n, k, ldb, 128);
+    if (rc != F8B200_OK) return rc;
+    const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind);
+    switch (out_dtype) {
+      case F8B200_BF16:
+        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        break;
+      case F8B200_FP16:
+        rc = gemm::launch_pair<__half>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        break;
+      default:
+        rc = gemm::launch_pair<float>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        break;
+    }
+    if (rc != F8B200_ERR_UNSUPPORTED) return rc;
+    // no room for a two-CTA cluster on this device: fall through to the one-CTA kernel
+  }
   rc = gemm::encode_operand_map(&ma, a, m, k, lda, gemm::BM);
   if (rc != F8B200_OK) return rc;
   rc = gemm::encode_operand_map(&mb, b, n, k, ldb, gemm::BN);
   if (rc != F8B200_OK) return rc;
 
   const uint32_t idesc = gemm::make_idesc(a_kind, b_kind);
-  const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (out_dtype) {
     case F8B200_BF16:
       return gemm::launch<__nv_bfloat16>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);

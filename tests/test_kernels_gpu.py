@@ -190,6 +190,13 @@ def test_transpose_u8():
 
 
 # ---------------------------------------------------------------------------
+@pytest.fixture(params=["2cta", "1cta"])
+def gemm_mode(request, monkeypatch):
+    """Both GEMM kernels: CTA pairs (cta_group::2, the default) and one CTA per tile."""
+    monkeypatch.setenv("F8B200_GEMM_MODE", request.param)
+    return request.param
+
+
 def gemm(a8, b8, sa, sb, out_dtype=torch.bfloat16, bias=None):
     m, k = a8.shape
     n = b8.shape[0]
@@ -209,9 +216,9 @@ def check_gemm(out, ref):
 
 
 @pytest.mark.parametrize("mnk", [(128, 256, 128), (256, 512, 1024), (200, 264, 144), (1, 8, 16), (130, 40, 4096),
-                                 (640, 1024, 2064)])
+                                 (640, 1024, 2064), (300, 520, 272)])
 @pytest.mark.parametrize("a_kind", [O.E4M3, O.E5M2])
-def test_gemm_against_oracle(mnk, a_kind):
+def test_gemm_against_oracle(mnk, a_kind, gemm_mode):
     m, n, k = mnk
     g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
     a = torch.randn(m, k, generator=g).to(TF8[a_kind]).cuda()
@@ -223,7 +230,7 @@ def test_gemm_against_oracle(mnk, a_kind):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16, torch.bfloat16])
-def test_gemm_output_types_and_bias(out_dtype):
+def test_gemm_output_types_and_bias(out_dtype, gemm_mode):
     a = torch.randn(256, 512, device="cuda").to(torch.float8_e4m3fn)
     b = torch.randn(384, 512, device="cuda").to(torch.float8_e4m3fn)
     bias = torch.randn(384, device="cuda").to(out_dtype)
@@ -236,7 +243,7 @@ def test_gemm_output_types_and_bias(out_dtype):
         assert (out - ref).abs().max().item() < 1e-3
 
 
-def test_gemm_full_size_linearity():
+def test_gemm_full_size_linearity(gemm_mode):
     """At a BASELINE shape the oracle is too slow; check size-independent properties:
     agreement with an fp32 GEMM of the dequantised operands on sampled rows, and
     out(2a, b) == 2 out(a, b) exactly (powers of two commute with every rounding)."""
