@@ -146,16 +146,21 @@ def kernel_event_totals():
 
 
 class _Launch:
-    """Context manager around one kernel launch: counts it, optionally times it."""
+    """Context manager around one kernel launch on `device`: makes that device current
+    (only if it is not already), counts the launch, optionally times it."""
 
-    __slots__ = ("kind", "n", "start")
+    __slots__ = ("kind", "n", "start", "guard")
 
-    def __init__(self, kind: str, n: int = 1):
+    def __init__(self, kind: str, device: torch.device, n: int = 1):
         self.kind, self.n, self.start = kind, n, None
+        idx = device.index
+        self.guard = None if (idx is None or idx == torch.cuda.current_device()) else torch.cuda.device(idx)
 
     def __enter__(self):
         global _launches
         _launches += self.n
+        if self.guard is not None:
+            self.guard.__enter__()
         if _events_on:
             self.start = torch.cuda.Event(enable_timing=True)
             self.start.record()
@@ -166,6 +171,8 @@ class _Launch:
             end = torch.cuda.Event(enable_timing=True)
             end.record()
             _events.setdefault(self.kind, []).append((self.start, end))
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
         return False
 
 
@@ -174,7 +181,7 @@ class _Launch:
 # ---------------------------------------------------------------------------
 def amax(x: torch.Tensor, out: torch.Tensor) -> None:
     _require_cuda(x, out)
-    with torch.cuda.device(x.device), _Launch("amax"):
+    with _Launch("amax", x.device):
         _check(load().f8b200_amax(x.data_ptr(), hp_code(x.dtype), x.numel(), out.data_ptr(), _stream(x)), "f8b200_amax")
 
 
@@ -188,13 +195,13 @@ def multi_amax(xs: Sequence[torch.Tensor], out: torch.Tensor) -> None:
         raise F8B200Error("multi_amax needs tensors of one dtype")
     ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in xs])
     numels = (ctypes.c_int64 * n)(*[t.numel() for t in xs])
-    with torch.cuda.device(out.device), _Launch("amax", (n + 127) // 128):
+    with _Launch("amax", out.device, (n + 127) // 128):
         _check(load().f8b200_multi_amax(ptrs, numels, n, hp_code(dt), out.data_ptr(), _stream(out)), "f8b200_multi_amax")
 
 
 def amax_to_scale(amax_t: torch.Tensor, fp8_kind: int, amax_dtype: int, orig_dtype: int, out: torch.Tensor) -> None:
     _require_cuda(amax_t, out)
-    with torch.cuda.device(out.device), _Launch("scale"):
+    with _Launch("scale", out.device):
         _check(
             load().f8b200_amax_to_scale(amax_t.data_ptr(), amax_t.numel(), fp8_kind, amax_dtype, orig_dtype,
                                         out.data_ptr(), _stream(out)),
@@ -207,7 +214,7 @@ def cast(x: torch.Tensor, rows: int, cols: int, ld_x: int, scale_src: int, scale
          ld_out: int, out_t: Optional[torch.Tensor], ld_out_t: int, amax_out: Optional[torch.Tensor],
          reverse: bool) -> None:
     _require_cuda(x, scale_in, scale_out, out, out_t, amax_out)
-    with torch.cuda.device(x.device), _Launch("cast"):
+    with _Launch("cast", x.device):
         _check(
             load().f8b200_cast(x.data_ptr(), hp_code(x.dtype), rows, cols, ld_x, scale_src, scale_in.data_ptr(),
                                _ptr(scale_out), int(product_fp32), fp8_kind, _ptr(out), ld_out, _ptr(out_t),
@@ -218,7 +225,7 @@ def cast(x: torch.Tensor, rows: int, cols: int, ld_x: int, scale_src: int, scale
 
 def transpose_u8(src: torch.Tensor, rows: int, cols: int, ld_in: int, dst: torch.Tensor, ld_out: int) -> None:
     _require_cuda(src, dst)
-    with torch.cuda.device(src.device), _Launch("transpose"):
+    with _Launch("transpose", src.device):
         _check(load().f8b200_transpose_u8(src.data_ptr(), rows, cols, ld_in, dst.data_ptr(), ld_out, _stream(src)),
                "f8b200_transpose_u8")
 
@@ -227,7 +234,7 @@ def delayed_sync(amax_t: torch.Tensor, hist: torch.Tensor, n_e4m3: int, orig_dty
                  hist_out: Optional[torch.Tensor]) -> None:
     _require_cuda(amax_t, hist, scale_out, hist_out)
     rows, hist_len = hist.shape
-    with torch.cuda.device(hist.device), _Launch("sync"):
+    with _Launch("sync", hist.device):
         _check(
             load().f8b200_delayed_sync(amax_t.data_ptr(), hist.data_ptr(), hist.stride(0), rows, hist_len, n_e4m3,
                                        orig_dtype, scale_out.data_ptr(), _ptr(hist_out),
@@ -240,7 +247,7 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
              bias: Optional[torch.Tensor], out: torch.Tensor, ldo: int, m: int, n: int, k: int,
              use_fast_accum: bool) -> None:
     _require_cuda(a, b, scale_a, scale_b, bias, out)
-    with torch.cuda.device(a.device), _Launch("gemm"):
+    with _Launch("gemm", a.device):
         _check(
             load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
                                    scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),

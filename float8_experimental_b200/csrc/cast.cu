@@ -78,12 +78,15 @@ __device__ __forceinline__ uint32_t amax_flat_body(const char* base, int64_t n, 
   }
   const uint4* v = reinterpret_cast<const uint4*>(base + head * ES);
   int64_t i = gtid;
-  for (; i + 3 * gstride < nvec; i += 4 * gstride) {
-    const uint4 a = v[i], b = v[i + gstride], c = v[i + 2 * gstride], d = v[i + 3 * gstride];
-    acc.add_word(a.x); acc.add_word(a.y); acc.add_word(a.z); acc.add_word(a.w);
-    acc.add_word(b.x); acc.add_word(b.y); acc.add_word(b.z); acc.add_word(b.w);
-    acc.add_word(c.x); acc.add_word(c.y); acc.add_word(c.z); acc.add_word(c.w);
-    acc.add_word(d.x); acc.add_word(d.y); acc.add_word(d.z); acc.add_word(d.w);
+  // eight independent 16-byte loads in flight per thread
+  for (; i + 7 * gstride < nvec; i += 8 * gstride) {
+    uint4 a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = v[i + u * gstride];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      acc.add_word(a[u].x); acc.add_word(a[u].y); acc.add_word(a[u].z); acc.add_word(a[u].w);
+    }
   }
   for (; i < nvec; i += gstride) {
     const uint4 a = v[i];
@@ -274,6 +277,198 @@ __global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
   if (p.amax_out != nullptr) block_atomic_max(acc.f32_bits(), p.amax_out, smem_max);
 }
 
+// ---------------------------------------------------------------------------
+// Main cast kernel: 128x128 tile per CTA, 8 rows x 8 columns per thread.
+//   loads   16 bytes per row (two for fp32 input): a half-warp reads 256 contiguous bytes
+//   stores  8 fp8 bytes per row: a half-warp writes 128 contiguous bytes
+//   transposed copy: 8x8 byte transpose in registers (byte permutes), 8-byte columns
+//           staged through 16 KB of shared memory with an XOR swizzle (conflict free in
+//           both directions), written as 128-byte contiguous segments
+// When the product x*scale is to be rounded to the input dtype and the scale itself is
+// representable in that dtype (always true for a scale derived from the amax in that
+// dtype) the product is taken with packed half-precision multiplies: the exact product
+// of two 8-bit (bf16) or 11-bit (fp16) significands fits fp32, so
+// RN_T(RN_fp32(x*s)) == RN_T(x*s), which is what HMUL2 returns.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t& c0,
+                                             uint32_t& c1, uint32_t& c2, uint32_t& c3) {
+  const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+  const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+  c0 = __byte_perm(t0, t1, 0x5410);
+  c1 = __byte_perm(t0, t1, 0x7632);
+  c2 = __byte_perm(t2, t3, 0x5410);
+  c3 = __byte_perm(t2, t3, 0x7632);
+}
+
+// lo[i] / hi[i]: fp8 bytes of columns 0..3 / 4..7 of row i (8 rows per thread).
+__device__ __forceinline__ void store_transposed_tile8(const uint32_t (&lo)[8], const uint32_t (&hi)[8], uint2* smem_t,
+                                                       uint8_t* out_t, int64_t ld_out_t, int64_t tile_row0,
+                                                       int64_t tile_col0, int64_t rows, int64_t cols) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int cg = lane & 15, rg = w * 2 + (lane >> 4);
+  uint32_t c[8][2];
+  transpose4x4(lo[0], lo[1], lo[2], lo[3], c[0][0], c[1][0], c[2][0], c[3][0]);
+  transpose4x4(lo[4], lo[5], lo[6], lo[7], c[0][1], c[1][1], c[2][1], c[3][1]);
+  transpose4x4(hi[0], hi[1], hi[2], hi[3], c[4][0], c[5][0], c[6][0], c[7][0]);
+  transpose4x4(hi[4], hi[5], hi[6], hi[7], c[4][1], c[5][1], c[6][1], c[7][1]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) smem_t[(cg * 8 + j) * 16 + (rg ^ cg)] = make_uint2(c[j][0], c[j][1]);
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = it * 256 + tid;
+    const int col = idx >> 4, chunk = idx & 15;
+    const uint2 val = smem_t[col * 16 + (chunk ^ ((col >> 3) & 15))];
+    const int64_t gc = tile_col0 + col, gr = tile_row0 + chunk * 8;
+    if (gc < cols && gr < rows) {
+      uint8_t* dst = out_t + gc * ld_out_t + gr;
+      if (gr + 8 <= rows) {
+        *reinterpret_cast<uint2*>(dst) = val;
+      } else {
+        for (int b = 0; b < 8 && gr + b < rows; ++b)
+          dst[b] = (uint8_t)((b < 4 ? val.x : val.y) >> (8 * (b & 3)));
+      }
+    }
+  }
+}
+
+template <int KIND>
+__device__ __forceinline__ uint32_t cvt_f16x2(uint32_t h2) {
+  const __nv_fp8_interpretation_t interp = (KIND == F8B200_E4M3) ? __NV_E4M3 : __NV_E5M2;
+  __half2_raw r;
+  r.x = (unsigned short)(h2 & 0xFFFFu);
+  r.y = (unsigned short)(h2 >> 16);
+  return __nv_cvt_halfraw2_to_fp8x2(r, __NV_SATFINITE, interp);
+}
+
+// Two packed high-precision elements times the packed scale -> two fp8 bytes.
+template <int HP, int KIND>
+__device__ __forceinline__ uint32_t packed_mul_cvt(uint32_t x2, uint32_t s2) {
+  if constexpr (HP == F8B200_BF16) {
+    const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&x2),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&s2));
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&p);
+    return cvt_pair_raw<KIND>(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+  } else {
+    const __half2 p = __hmul2(*reinterpret_cast<const __half2*>(&x2), *reinterpret_cast<const __half2*>(&s2));
+    return cvt_f16x2<KIND>(*reinterpret_cast<const uint32_t*>(&p));
+  }
+}
+
+template <int HP>
+__device__ __forceinline__ void unpack2(uint32_t x2, float& a, float& b) {
+  if constexpr (HP == F8B200_BF16) {
+    a = __uint_as_float(x2 << 16);
+    b = __uint_as_float(x2 & 0xFFFF0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x2));
+    a = f.x;
+    b = f.y;
+  }
+}
+
+template <int HP, int KIND, bool WANT_AMAX>
+__global__ void __launch_bounds__(256, 2) cast_tile8_kernel(const CastParams p) {
+  __shared__ uint2 smem_t[128 * 16];
+  __shared__ uint32_t smem_max[8];
+  constexpr int ES = (HP == F8B200_FP32) ? 4 : 2;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int cg = lane & 15, rg = w * 2 + (lane >> 4);
+  const int64_t t = p.reverse ? (p.ntiles - 1 - (int64_t)blockIdx.x) : (int64_t)blockIdx.x;
+  const int64_t tile_row0 = (t / p.tiles_c) * 128, tile_col0 = (t % p.tiles_c) * 128;
+  const int64_t r0 = tile_row0 + rg * 8, c0 = tile_col0 + cg * 8;
+  const bool col_ok = c0 < p.cols;  // cols is a multiple of 8 on this path
+  int nrows = 0;
+  if (col_ok && r0 < p.rows) nrows = (p.rows - r0) >= 8 ? 8 : (int)(p.rows - r0);
+  const float s = load_scale<HP>(p, (KIND == F8B200_E4M3) ? kE4M3Max : kE5M2Max);
+  const char* src = static_cast<const char*>(p.x) + (r0 * p.ld_x + c0) * ES;
+  const int64_t row_bytes = p.ld_x * ES;
+
+  uint32_t lo[8], hi[8];
+  AbsMax<HP> acc;
+  if constexpr (ES == 2) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < nrows) v[i] = __ldcs(reinterpret_cast<const uint4*>(src + i * row_bytes));
+    }
+    if constexpr (WANT_AMAX) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc.add_word(v[i].x); acc.add_word(v[i].y); acc.add_word(v[i].z); acc.add_word(v[i].w);
+      }
+    }
+    // packed multiply only when it is bit-identical to the fp32 route (see above)
+    const bool packed = !p.product_fp32 && round_hp<HP>(s) == s;
+    if (packed) {
+      uint32_t s2;
+      if constexpr (HP == F8B200_BF16) {
+        const __nv_bfloat162 sb = __float2bfloat162_rn(s);
+        s2 = *reinterpret_cast<const uint32_t*>(&sb);
+      } else {
+        const __half2 sh = __float2half2_rn(s);
+        s2 = *reinterpret_cast<const uint32_t*>(&sh);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        lo[i] = packed_mul_cvt<HP, KIND>(v[i].x, s2) | (packed_mul_cvt<HP, KIND>(v[i].y, s2) << 16);
+        hi[i] = packed_mul_cvt<HP, KIND>(v[i].z, s2) | (packed_mul_cvt<HP, KIND>(v[i].w, s2) << 16);
+      }
+    } else {
+      const bool round_to_hp = !p.product_fp32;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f0, f1, f2, f3;
+        unpack2<HP>(v[i].x, f0, f1);
+        unpack2<HP>(v[i].y, f2, f3);
+        lo[i] = cast4<HP, KIND>(__fmul_rn(f0, s), __fmul_rn(f1, s), __fmul_rn(f2, s), __fmul_rn(f3, s), round_to_hp);
+        unpack2<HP>(v[i].z, f0, f1);
+        unpack2<HP>(v[i].w, f2, f3);
+        hi[i] = cast4<HP, KIND>(__fmul_rn(f0, s), __fmul_rn(f1, s), __fmul_rn(f2, s), __fmul_rn(f3, s), round_to_hp);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 va[4], vb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        va[i] = make_uint4(0u, 0u, 0u, 0u);
+        vb[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (h * 4 + i < nrows) {
+          va[i] = __ldcs(reinterpret_cast<const uint4*>(src + (h * 4 + i) * row_bytes));
+          vb[i] = __ldcs(reinterpret_cast<const uint4*>(src + (h * 4 + i) * row_bytes + 16));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (WANT_AMAX) {
+          acc.add_word(va[i].x); acc.add_word(va[i].y); acc.add_word(va[i].z); acc.add_word(va[i].w);
+          acc.add_word(vb[i].x); acc.add_word(vb[i].y); acc.add_word(vb[i].z); acc.add_word(vb[i].w);
+        }
+        lo[h * 4 + i] = cast4<HP, KIND>(__fmul_rn(__uint_as_float(va[i].x), s), __fmul_rn(__uint_as_float(va[i].y), s),
+                                        __fmul_rn(__uint_as_float(va[i].z), s), __fmul_rn(__uint_as_float(va[i].w), s),
+                                        false);
+        hi[h * 4 + i] = cast4<HP, KIND>(__fmul_rn(__uint_as_float(vb[i].x), s), __fmul_rn(__uint_as_float(vb[i].y), s),
+                                        __fmul_rn(__uint_as_float(vb[i].z), s), __fmul_rn(__uint_as_float(vb[i].w), s),
+                                        false);
+      }
+    }
+  }
+
+  if (p.out != nullptr) {
+    uint8_t* dst = p.out + r0 * p.ld_out + c0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nrows) *reinterpret_cast<uint2*>(dst + i * p.ld_out) = make_uint2(lo[i], hi[i]);
+  }
+  if (p.out_t != nullptr) {
+    store_transposed_tile8(lo, hi, smem_t, p.out_t, p.ld_out_t, tile_row0, tile_col0, p.rows, p.cols);
+  }
+  if constexpr (WANT_AMAX) block_atomic_max(acc.f32_bits(), p.amax_out, smem_max);
+}
+
 // Any shape, stride or alignment: one element per thread.  Used only when the tiled
 // kernel's alignment requirements do not hold.
 template <int HP, int KIND>
@@ -322,6 +517,26 @@ __global__ void __launch_bounds__(256) transpose_u8_tile_kernel(const uint8_t* i
     if (col < cols && r < rows) rw[i] = __ldcs(reinterpret_cast<const uint32_t*>(in + r * ld_in + col));
   }
   store_transposed_tile(rw, smem_t, out, ld_out, tile_row0, tile_col0, rows, cols);
+}
+
+__global__ void __launch_bounds__(256) transpose_u8_tile8_kernel(const uint8_t* in, int64_t rows, int64_t cols,
+                                                                 int64_t ld_in, uint8_t* out, int64_t ld_out,
+                                                                 int64_t tiles_c) {
+  __shared__ uint2 smem_t[128 * 16];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int cg = lane & 15, rg = w * 2 + (lane >> 4);
+  const int64_t t = blockIdx.x;
+  const int64_t tile_row0 = (t / tiles_c) * 128, tile_col0 = (t % tiles_c) * 128;
+  const int64_t r0 = tile_row0 + rg * 8, c0 = tile_col0 + cg * 8;
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint2 v = make_uint2(0u, 0u);
+    if (c0 < cols && r0 + i < rows) v = __ldcs(reinterpret_cast<const uint2*>(in + (r0 + i) * ld_in + c0));
+    lo[i] = v.x;
+    hi[i] = v.y;
+  }
+  store_transposed_tile8(lo, hi, smem_t, out, ld_out, tile_row0, tile_col0, rows, cols);
 }
 
 __global__ void transpose_u8_generic_kernel(const uint8_t* in, int64_t rows, int64_t cols, int64_t ld_in,
@@ -389,8 +604,8 @@ extern "C" int f8b200_amax(const void* x, int hp_dtype, int64_t numel, float* am
   rc = record_cuda_error(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
   if (rc != F8B200_OK) return rc;
   const int64_t nvec = numel / (16 / hp_size_of(hp_dtype));
-  int64_t blocks = (nvec + 512 * 4 - 1) / (512 * 4);
-  const int64_t cap = (int64_t)sm_count() * 4;
+  int64_t blocks = (nvec + 512 * 8 - 1) / (512 * 8);
+  const int64_t cap = (int64_t)sm_count() * 3;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return dispatch_hp(hp_dtype, [&](auto hp) {
@@ -486,6 +701,9 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
   const bool fast = cols % 4 == 0 && ld_x % 4 == 0 && aligned_to(x, 4 * es) &&
                     (out == nullptr || (ld_out % 4 == 0 && aligned_to(out, 4))) &&
                     (out_t == nullptr || (ld_out_t % 16 == 0 && aligned_to(out_t, 16)));
+  const bool fast8 = cols % 8 == 0 && (ld_x * es) % 16 == 0 && aligned_to(x, 16) &&
+                     (out == nullptr || (ld_out % 8 == 0 && aligned_to(out, 8))) &&
+                     (out_t == nullptr || (ld_out_t % 8 == 0 && aligned_to(out_t, 8)));
   return dispatch_hp(hp_dtype, [&](auto hp) {
     constexpr int HP = decltype(hp)::value;
     if (empty) {
@@ -495,7 +713,17 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
       }
       return (int)F8B200_OK;
     }
-    if (fast) {
+    if (fast8) {
+      if (p.ntiles > 0x7FFFFFFFLL) return (int)F8B200_ERR_UNSUPPORTED;
+      const unsigned g = (unsigned)p.ntiles;
+      if (fp8_kind == F8B200_E4M3) {
+        if (amax_out != nullptr) cast_tile8_kernel<HP, F8B200_E4M3, true><<<g, 256, 0, st>>>(p);
+        else cast_tile8_kernel<HP, F8B200_E4M3, false><<<g, 256, 0, st>>>(p);
+      } else {
+        if (amax_out != nullptr) cast_tile8_kernel<HP, F8B200_E5M2, true><<<g, 256, 0, st>>>(p);
+        else cast_tile8_kernel<HP, F8B200_E5M2, false><<<g, 256, 0, st>>>(p);
+      }
+    } else if (fast) {
       if (p.ntiles > 0x7FFFFFFFLL) return (int)F8B200_ERR_UNSUPPORTED;
       if (fp8_kind == F8B200_E4M3) cast_tile_kernel<HP, F8B200_E4M3><<<(unsigned)p.ntiles, 256, 0, st>>>(p);
       else cast_tile_kernel<HP, F8B200_E5M2><<<(unsigned)p.ntiles, 256, 0, st>>>(p);
@@ -519,7 +747,14 @@ extern "C" int f8b200_transpose_u8(const void* in, int64_t rows, int64_t cols, i
   if (rc != F8B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool fast = cols % 4 == 0 && ld_in % 4 == 0 && aligned_to(in, 4) && ld_out % 16 == 0 && aligned_to(out, 16);
-  if (fast) {
+  const bool fast8 = cols % 8 == 0 && ld_in % 8 == 0 && aligned_to(in, 8) && ld_out % 8 == 0 && aligned_to(out, 8);
+  if (fast8) {
+    const int64_t tiles_c = (cols + 127) / 128;
+    const int64_t ntiles = tiles_c * ((rows + 127) / 128);
+    if (ntiles > 0x7FFFFFFFLL) return F8B200_ERR_UNSUPPORTED;
+    transpose_u8_tile8_kernel<<<(unsigned)ntiles, 256, 0, st>>>(static_cast<const uint8_t*>(in), rows, cols, ld_in,
+                                                                static_cast<uint8_t*>(out), ld_out, tiles_c);
+  } else if (fast) {
     const int64_t tiles_c = (cols + 127) / 128;
     const int64_t ntiles = tiles_c * ((rows + 127) / 128);
     if (ntiles > 0x7FFFFFFFLL) return F8B200_ERR_UNSUPPORTED;

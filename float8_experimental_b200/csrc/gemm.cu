@@ -18,6 +18,7 @@
 #include <cudaTypedefs.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -50,7 +51,8 @@ struct __align__(8) Barriers {
   volatile uint32_t abort_flag;
 };
 
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Barriers);
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * 2 * 32 * 128 /* epilogue staging */ + 1024 /* alignment slack */ +
+                           (int)sizeof(Barriers);
 
 // ---- PTX wrappers ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -76,11 +78,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the budget ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t who) {
+// `backoff_ns` > 0 puts the polling thread to sleep between probes: waits that are long
+// and off the critical path (ring slots coming free, a whole tile being accumulated)
+// should not burn issue slots and power that the tensor pipe could use.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t who,
+                                          uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns != 0u) __nanosleep(backoff_ns);
     if ((it & 63u) == 63u) {
       if (bars->abort_flag != 0u) return false;
       if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
@@ -196,14 +203,127 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int
     if (e < ncols) dst[e] = static_cast<OutT>(v[e]);
 }
 
+// ---- epilogue: accumulator -> scaled output ---------------------------------
+// Each epilogue warp owns 32 accumulator rows.  Preferred path: the warp converts 32
+// columns at a time, writes them into a 128-byte-swizzled staging box in shared memory
+// (32 rows x 128 bytes) and one lane hands the box to a TMA store, so the output leaves
+// the SM as full 128-byte lines and rows/columns beyond M/N are clipped by the tensor
+// map.  Two boxes per warp alternate so conversion overlaps the stores.  The direct path
+// (16-byte stores per thread) is used when the output does not meet TMA alignment.
+constexpr int EPI_BOX_BYTES = 32 * 128;
+constexpr int EPI_STAGING_BYTES = 4 /*warps*/ * 2 /*boxes*/ * EPI_BOX_BYTES;
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <typename OutT>
+struct EpilogueArgs {
+  const OutT* bias;
+  OutT* out;
+  int64_t ldo;
+  int m, n;
+  int out_vec_ok;
+  int use_tma;
+  const CUtensorMap* tma_out;
+  uint8_t* staging;  // this warp's two boxes, 1024-byte aligned
+  float inv;
+};
+
+// Drains `ncol_total` accumulator columns starting at TMEM address `taddr` for the 32
+// rows row0..row0+31 (lane = row).  `boxes` counts the TMA boxes this warp has issued so
+// far (selects the staging box and tells how many stores may still be reading it).
+template <typename OutT>
+__device__ __forceinline__ void drain_accumulator(const EpilogueArgs<OutT>& e, uint32_t taddr, int row0, int col0,
+                                                  int ncol_total, uint32_t& boxes) {
+  constexpr int COLS_PER_BOX = 128 / (int)sizeof(OutT);  // 64 (16-bit) or 32 (fp32)
+  constexpr int CHUNKS_PER_BOX = COLS_PER_BOX / 32;      // tcgen05.ld chunks of 32 columns
+  const int lane = threadIdx.x & 31;
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c = 0; c < ncol_total / 32; ++c) {
+    uint32_t r[32];
+    tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+    tc_wait_ld();
+    const int col = col0 + c * 32;
+    int ncols = e.n - col;
+    if (ncols > 32) ncols = 32;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * e.inv;
+    if (e.bias != nullptr && ncols > 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) v[i] += static_cast<float>(e.bias[col + i]);
+    }
+    if (!e.use_tma) {
+      if (row < e.m && ncols > 0) store_chunk<OutT>(e.out + (int64_t)row * e.ldo + col, v, ncols, e.out_vec_ok != 0);
+      continue;
+    }
+    const int sub = c % CHUNKS_PER_BOX;  // which 32-column part of the box
+    // boxes that start beyond the matrix are skipped altogether (uniform over the warp);
+    // partial ones are clipped by the tensor map
+    if (col - sub * 32 >= e.n || row0 >= e.m) continue;
+    uint8_t* box = e.staging + (boxes & 1u) * EPI_BOX_BYTES;
+    if (sub == 0 && boxes >= 2u) {
+      // the store issued two boxes ago (same staging box) must have finished reading it
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+    }
+    // row `lane` of the box is 128 bytes = eight 16-byte chunks; chunk j lives at j ^ (lane & 7)
+    uint8_t* rowp = box + lane * 128;
+    if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          OutT lo = static_cast<OutT>(v[q * 8 + 2 * h]), hi = static_cast<OutT>(v[q * 8 + 2 * h + 1]);
+          w[h] = (uint32_t)(*reinterpret_cast<unsigned short*>(&lo)) |
+                 ((uint32_t)(*reinterpret_cast<unsigned short*>(&hi)) << 16);
+        }
+        const int j = sub * 4 + q;
+        *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+            make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      }
+    }
+    if (sub == CHUNKS_PER_BOX - 1) {
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(e.tma_out, box, col - sub * 32, row0);
+        bulk_commit();
+      }
+      ++boxes;
+    }
+  }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                const float* __restrict__ scale_a, const float* __restrict__ scale_b, const OutT* __restrict__ bias,
-                OutT* __restrict__ out, int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok) {
+                const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
+                const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out, int64_t ldo,
+                int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
+  uint8_t* staging = tiles + STAGES * STAGE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(staging + EPI_STAGING_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
@@ -244,7 +364,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
         const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, bars, 1u)) { ok = false; break; }
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
           mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
           tma_load_2d(sa, &tma_a, kb * BK, tc.m * BM, &bars->full[stage]);
@@ -296,41 +416,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const float sa = __ldg(scale_a), sb = __ldg(scale_b);
       inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
     }
+    const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
+                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv};
+    uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
     for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, bars, 8u)) { ok = false; break; }
+      // one lane polls, the rest of the warp sleeps at the shuffle
+      int got = 1;
+      if (lane == 0) got = mbar_wait(&bars->tmem_full[acc], acc_phase, bars, 8u, 256u) ? 1 : 0;
+      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
       tc_fence_after();
-      const int row = tc.m * BM + quarter * 32 + lane;
-      const int col0 = tc.n * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
-        tc_wait_ld();
-        const int col = col0 + c * 32;
-        int ncols = n - col;
-        if (ncols > 32) ncols = 32;
-        if (row < m && ncols > 0) {
-          float v[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * inv;
-          if (bias != nullptr) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (e < ncols) v[e] += static_cast<float>(bias[col + e]);
-          }
-          store_chunk<OutT>(out + (int64_t)row * ldo + col, v, ncols, out_vec_ok != 0);
-        }
-      }
+      drain_accumulator<OutT>(ea, taddr, tc.m * BM + quarter * 32, tc.n * BN, BN, boxes);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
     }
+    if (use_tma_store && lane == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -374,7 +480,7 @@ struct __align__(8) PairBarriers {
   volatile uint32_t abort_flag;
 };
 
-constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + (int)sizeof(PairBarriers);
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + EPI_STAGING_BYTES + 1024 + (int)sizeof(PairBarriers);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -429,11 +535,12 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind) {
 
 // Bounded wait that also raises the partner's abort flag when it gives up.
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBarriers* bars, uint32_t peer_rank,
-                                          uint32_t who) {
+                                          uint32_t who, uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns != 0u) __nanosleep(backoff_ns);
     if ((it & 63u) == 63u) {
       if (bars->abort_flag != 0u) return false;
       if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
@@ -460,12 +567,13 @@ __device__ __forceinline__ TileCoord pair_tile_coord(int64_t idx, int tiles_m, i
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                     const float* __restrict__ scale_a, const float* __restrict__ scale_b,
-                     const OutT* __restrict__ bias, OutT* __restrict__ out, int64_t ldo, int m, int n, int k,
-                     uint32_t idesc, int out_vec_ok) {
+                     const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
+                     const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
+                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  PairBarriers* bars = reinterpret_cast<PairBarriers*>(tiles + PSTAGES * PSTAGE_BYTES);
+  uint8_t* staging = tiles + PSTAGES * PSTAGE_BYTES;
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(staging + EPI_STAGING_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -513,7 +621,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         const int row_a = tc.m * PBM + (int)rank * 128;
         const int row_b = tc.n * PBN + (int)rank * 128;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u)) { ok = false; break; }
+          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * PSTAGE_BYTES;
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
           const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
@@ -524,7 +632,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       }
       // tail: every release the leader multicast to this CTA's empty barriers has landed
       for (int s = 0; ok && s < PSTAGES; ++s) {
-        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u)) { ok = false; break; }
+        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
         if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
       }
       if (!ok) {
@@ -569,41 +677,26 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       const float sa = __ldg(scale_a), sb = __ldg(scale_b);
       inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
     }
+    const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
+                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv};
+    uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
     for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
       const TileCoord tc = pair_tile_coord(t, tiles_m, tiles_n);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      if (!pair_wait(&bars->tmem_full[acc], acc_phase, bars, peer, 8u)) { ok = false; break; }
+      int got = 1;
+      if (lane == 0) got = pair_wait(&bars->tmem_full[acc], acc_phase, bars, peer, 8u, 256u) ? 1 : 0;
+      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
       tc_fence_after();
-      const int row = tc.m * PBM + (int)rank * 128 + quarter * 32 + lane;
-      const int col0 = tc.n * PBN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PBN);
-#pragma unroll 1
-      for (int c = 0; c < PBN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
-        tc_wait_ld();
-        const int col = col0 + c * 32;
-        int ncols = n - col;
-        if (ncols > 32) ncols = 32;
-        if (row < m && ncols > 0) {
-          float v[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * inv;
-          if (bias != nullptr) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (e < ncols) v[e] += static_cast<float>(bias[col + e]);
-          }
-          store_chunk<OutT>(out + (int64_t)row * ldo + col, v, ncols, out_vec_ok != 0);
-        }
-      }
+      drain_accumulator<OutT>(ea, taddr, tc.m * PBM + (int)rank * 128 + quarter * 32, tc.n * PBN, PBN, boxes);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0u));
     }
+    if (use_tma_store && lane == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -647,9 +740,27 @@ static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, 
   return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
 }
 
+// Output tensor map for the TMA-store epilogue: boxes of 32 rows x 128 bytes, 128B swizzle.
+static int encode_output_map(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int out_dtype) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return F8B200_ERR_DRIVER;
+  const int esz = out_dtype == F8B200_FP32 ? 4 : 2;
+  const CUtensorMapDataType dt = out_dtype == F8B200_FP32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : out_dtype == F8B200_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const cuuint64_t gdim[2] = {(cuuint64_t)n, (cuuint64_t)m};
+  const cuuint64_t gstride[1] = {(cuuint64_t)(ldo * esz)};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, dt, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
+}
+
 template <typename OutT>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa, const float* sb, const void* bias,
-                  void* out, int64_t ldo, int m, int n, int k, uint32_t idesc, int vec_ok, cudaStream_t st) {
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma, const float* sa,
+                  const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k, uint32_t idesc,
+                  int vec_ok, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -659,14 +770,16 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa,
   const int64_t tiles = (int64_t)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   int grid = sm_count();
   if (tiles < grid) grid = (int)tiles;
-  gemm_fp8_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, sa, sb, static_cast<const OutT*>(bias),
-                                                                static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok);
+  gemm_fp8_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mo, sa, sb, static_cast<const OutT*>(bias),
+                                                                static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
+                                                                use_tma);
   return check_launch();
 }
 
 template <typename OutT>
-static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const float* sa, const float* sb, const void* bias,
-                       void* out, int64_t ldo, int m, int n, int k, uint32_t idesc, int vec_ok, cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
+                       const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
+                       uint32_t idesc, int vec_ok, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int max_clusters = 0;
@@ -698,7 +811,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const float
   const OutT* bias_t = static_cast<const OutT*>(bias);
   OutT* out_t = static_cast<OutT*>(out);
   return record_cuda_error(
-      cudaLaunchKernelEx(&cfg, kernel, ma, mb, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok));
+      cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma));
 }
 
 // 0 = one CTA per tile (128x256), 1 = CTA pairs (256x256, cta_group::2).  The environment
@@ -737,7 +850,20 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
 
   const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mo;
+  // TMA-store epilogue needs a 16-byte aligned base and row pitch; F8B200_GEMM_STORE=direct forces the
+  // per-thread store path (used by the tests to cover both)
+  int use_tma = vec_ok;
+  {
+    const char* e = getenv("F8B200_GEMM_STORE");
+    if (e != nullptr && e[0] == 'd') use_tma = 0;
+  }
+  if (use_tma) {
+    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype);
+    if (rc != F8B200_OK) return rc;
+  } else {
+    memset(&mo, 0, sizeof(mo));
+  }
   if (gemm::gemm_mode() == 1) {
     // each CTA of a pair fetches 128-row boxes of both operands
     rc = gemm::encode_operand_map(&ma, a, m, k, lda, 128);
@@ -747,13 +873,13 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
     const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind);
     switch (out_dtype) {
       case F8B200_BF16:
-        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
         break;
       case F8B200_FP16:
-        rc = gemm::launch_pair<__half>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
         break;
       default:
-        rc = gemm::launch_pair<float>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
         break;
     }
     if (rc != F8B200_ERR_UNSUPPORTED) return rc;
@@ -767,11 +893,11 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
   const uint32_t idesc = gemm::make_idesc(a_kind, b_kind);
   switch (out_dtype) {
     case F8B200_BF16:
-      return gemm::launch<__nv_bfloat16>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+      return gemm::launch<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
     case F8B200_FP16:
-      return gemm::launch<__half>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+      return gemm::launch<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
     default:
-      return gemm::launch<float>(ma, mb, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
+      return gemm::launch<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
   }
 }
 

@@ -87,7 +87,10 @@ class NoopFwToFloat8E5M2BwDelayed(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tensor, fp8_amax_grad_output, fp8_amax_history_grad_output, fp8_scale_grad_output,
                 scale_fn_name, is_amax_initialized, linear_mm_config: LinearMMConfig):
-        ctx.save_for_backward(fp8_amax_grad_output, fp8_amax_history_grad_output, fp8_scale_grad_output)
+        # Plain attributes, not save_for_backward: the buffers are views into slabs shared by
+        # all layers (see sync_float8_amax_and_scale_history) and are legitimately written
+        # in place by other layers' backward passes before this one runs.
+        ctx.f8_buffers = (fp8_amax_grad_output, fp8_amax_history_grad_output, fp8_scale_grad_output)
         ctx.scale_fn_name = scale_fn_name
         ctx.is_amax_initialized = is_amax_initialized
         ctx.linear_mm_config = linear_mm_config
@@ -95,7 +98,7 @@ class NoopFwToFloat8E5M2BwDelayed(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, go):
-        amax_buf, history_buf, scale_buf = ctx.saved_tensors
+        amax_buf, history_buf, scale_buf = ctx.f8_buffers
         _maybe_initialize_amaxes_scales_for_float8_cast(
             go, amax_buf, history_buf, scale_buf, ctx.scale_fn_name, e5m2_dtype, ctx.is_amax_initialized,
             reduce_amax=True,
