@@ -163,7 +163,7 @@ class WeightWithDynamicFloat8CastTensor(torch.Tensor):
         return f"WeightWithDynamicFloat8CastTensor(tensor={self._tensor}, linear_mm_config={self._linear_mm_config})"
 
     @torch.no_grad()  # the transposed copy for backward GEMMs is pointless on a shard
-    def fsdp_pre_all_gather(self, mesh, *unused_args, **unused_kwargs):
+    def fsdp_pre_all_gather(self, mesh):
         if self._precomputed_scale is not None:
             fp8 = hp_tensor_and_scale_to_float8(
                 self._tensor, self._precomputed_scale, torch.float8_e4m3fn, self._linear_mm_config,
@@ -241,7 +241,7 @@ class WeightWithDelayedFloat8CastTensor(torch.Tensor):
         )
 
     @torch.no_grad()
-    def fsdp_pre_all_gather(self, mesh, *unused_args, **unused_kwargs):
+    def fsdp_pre_all_gather(self, mesh):
         if not self.is_amax_initialized:
             _maybe_initialize_amaxes_scales_for_float8_cast(
                 self._tensor, self._amax_buffer, self._amax_history_buffer, self._scale_buffer, "max", e4m3_dtype,

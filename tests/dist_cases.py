@@ -1,0 +1,280 @@
+"""Bodies of the multi-rank CPU tests (gloo, world_size 2).  Each function runs on every
+rank inside a process spawned by `tests/test_distributed_cpu.py`; the `f8b200::*` ops
+are served on CPU by the oracle-backed stand-ins of `tests/oracle_backend.py`."""
+from __future__ import annotations
+
+import copy
+import os
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def _init(rank: int, world: int, port: int):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle_backend
+
+    oracle_backend.install()
+
+
+def _delayed_config(f8, **kw):
+    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    return f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d, **kw)
+
+
+# ---------------------------------------------------------------------------
+def case_sync_all_reduce(rank, world, port):
+    """sync_float8_amax_and_scale_history takes the MAX of every amax over the ranks with
+    one all-reduce, then derives the scales from it."""
+    _init(rank, world, port)
+    import float8_experimental_b200 as f8
+    from oracle import f8_oracle as O
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 8, bias=False), nn.Linear(8, 8, bias=False))
+    f8.convert_to_float8_training(model, config=_delayed_config(f8))
+    for i, layer in enumerate(model):
+        layer.last_seen_input_dtype = torch.float32
+        layer.fp8_amax_input.fill_(1.0 + rank + i)          # max over ranks: world + i
+        layer.fp8_amax_weight.fill_(0.5 * (world - rank))   # max over ranks: 0.5 * world
+        layer.fp8_amax_grad_output.fill_(1e-3 * (1 + rank))
+    calls = []
+    real = dist.all_reduce
+
+    def counting(t, *a, **k):
+        calls.append(t.numel())
+        return real(t, *a, **k)
+
+    dist.all_reduce = counting
+    try:
+        f8.sync_float8_amax_and_scale_history(model)
+    finally:
+        dist.all_reduce = real
+    assert calls == [6], calls  # one collective over the [3 * n_layers] slab
+    for i, layer in enumerate(model):
+        assert layer.fp8_amax_input.item() == float(world + i)
+        assert layer.fp8_amax_weight.item() == 0.5 * world
+        exp = O.amax_to_scale(float(world + i), O.E4M3, O.FP32, O.FP32)
+        assert layer.fp8_scale_input.item() == float(exp)
+        exp = O.amax_to_scale(1e-3 * world, O.E5M2, O.FP32, O.FP32)
+        assert layer.fp8_scale_grad_output.item() == float(exp)
+    dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+class _MLP(nn.Module):
+    def __init__(self, dim=32, hidden=64, n=3):
+        super().__init__()
+        self.layers = nn.ModuleList(
+            [nn.Sequential(nn.Linear(dim, hidden, bias=False), nn.ReLU(), nn.Linear(hidden, dim, bias=False))
+             for _ in range(n)]
+        )
+
+    def forward(self, x):
+        for blk in self.layers:
+            x = x + blk(x)
+        return x
+
+
+def case_fsdp2_fp8_all_gather(rank, world, port, precompute):
+    """FSDP2 with fp8 weight all-gather reproduces, loss for loss, an unsharded float8
+    model whose gradients are averaged by hand (the reference's parity criterion,
+    test/test_fsdp2/test_fsdp2_common.py:17-54); the all-gather carries 1 byte per
+    weight element (test/test_fsdp2/test_fsdp2.py:324-405)."""
+    _init(rank, world, port)
+    from torch.distributed.fsdp import fully_shard
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.fsdp_utils import WeightWithDynamicFloat8CastTensor
+
+    torch.manual_seed(42)
+    base = _MLP()
+    ref_model = copy.deepcopy(base)
+    f8.convert_to_float8_training(ref_model, config=f8.Float8LinearConfig())
+    fsdp_model = copy.deepcopy(base)
+    f8.convert_to_float8_training(fsdp_model, config=f8.Float8LinearConfig(enable_fsdp_float8_all_gather=True))
+    assert isinstance(fsdp_model.layers[0][0].weight, WeightWithDynamicFloat8CastTensor)
+    for blk in fsdp_model.layers:
+        fully_shard(blk)
+    fully_shard(fsdp_model)
+
+    gathered = []
+    real_ag = dist.all_gather_into_tensor
+
+    def counting_ag(out, inp, *a, **k):
+        gathered.append((inp.dtype, inp.numel() * inp.element_size()))
+        return real_ag(out, inp, *a, **k)
+
+    dist.all_gather_into_tensor = counting_ag
+    ref_opt = torch.optim.Adam(ref_model.parameters(), lr=1e-2)
+    fsdp_opt = torch.optim.Adam(fsdp_model.parameters(), lr=1e-2)
+    torch.manual_seed(100 + rank)
+    try:
+        for step in range(3):
+            x = torch.randn(16, 32)
+            losses = []
+            for model, opt in ((ref_model, ref_opt), (fsdp_model, fsdp_opt)):
+                opt.zero_grad()
+                loss = model(x).pow(2).sum()
+                loss.backward()
+                if model is ref_model:
+                    for p in model.parameters():
+                        dist.all_reduce(p.grad)
+                        p.grad.div_(world)
+                opt.step()
+                if model is fsdp_model and precompute:
+                    f8.precompute_float8_dynamic_scale_for_fsdp(model)
+                losses.append(loss.detach())
+            assert torch.equal(losses[0], losses[1]), (step, losses)
+    finally:
+        dist.all_gather_into_tensor = real_ag
+    # every block all-gather moved bytes: (64*32 + 32*64) / world per rank, 1 byte each
+    per_block = (64 * 32 + 32 * 64) // world
+    block_gathers = [g for g in gathered if g[1] == per_block]
+    assert len(block_gathers) >= 3 * 3, gathered
+    assert all(dt == torch.uint8 for dt, _ in block_gathers)
+    if precompute:
+        w = fsdp_model.layers[0][0].weight._local_tensor
+        assert w._precomputed_scale is not None and w._precomputed_scale.dim() == 0
+    dist.destroy_process_group()
+
+
+def case_fsdp2_delayed(rank, world, port):
+    """Delayed weight scaling under FSDP2: the wrapper updates the layer's own buffers and
+    precompute refuses to run."""
+    _init(rank, world, port)
+    from torch.distributed.fsdp import fully_shard
+
+    import float8_experimental_b200 as f8
+
+    torch.manual_seed(1)
+    model = _MLP(n=2)
+    cfg = f8.Float8LinearConfig(
+        enable_fsdp_float8_all_gather=True,
+        cast_config_weight=f8.CastConfig(scaling_type=f8.ScalingType.DELAYED),
+    )
+    f8.convert_to_float8_training(model, config=cfg)
+    for blk in model.layers:
+        fully_shard(blk)
+    fully_shard(model)
+    lin = model.layers[0][0]
+    before = lin.fp8_amax_weight.clone()
+    torch.manual_seed(7 + rank)
+    for _ in range(2):
+        f8.sync_float8_amax_and_scale_history(model)
+        model(torch.randn(16, 32)).sum().backward()
+    assert not torch.equal(lin.fp8_amax_weight, before)
+    full_w = lin.weight.full_tensor()
+    assert lin.fp8_amax_history_weight[0].item() == full_w.abs().max().item()
+    try:
+        f8.precompute_float8_dynamic_scale_for_fsdp(model)
+    except NotImplementedError:
+        pass
+    else:
+        raise AssertionError("precompute must reject delayed weight scaling")
+    dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+class _FFN(nn.Module):
+    def __init__(self, dim=16, hidden=32):
+        super().__init__()
+        self.w1 = nn.Linear(dim, hidden, bias=False)
+        self.w2 = nn.Linear(hidden, dim, bias=False)
+        self.w3 = nn.Linear(dim, hidden, bias=False)
+
+    def forward(self, x):
+        return self.w2(nn.functional.silu(self.w1(x)) * self.w3(x))
+
+
+class _Toy(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.ffn = _FFN()
+
+    def forward(self, x):
+        return self.ffn(x)
+
+
+def case_tensor_parallel(rank, world, port, sequence_parallel):
+    """TP (and SP) float8 FFN == the unsharded float8 FFN
+    (the reference's criterion, test/test_dtensor.py:189-231)."""
+    _init(rank, world, port)
+    from torch.distributed._tensor import DTensor, Replicate, Shard
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.parallel import parallelize_module
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.float8_tensor import Float8Tensor
+    from float8_experimental_b200.float8_tensor_parallel import (
+        Float8ColwiseParallel,
+        Float8RowwiseParallel,
+        PrepareFloat8ModuleInput,
+    )
+
+    mesh = init_device_mesh("cpu", (world,))
+    torch.manual_seed(5)
+    ref = _Toy()
+    f8.convert_to_float8_training(ref, config=f8.Float8LinearConfig())
+    tp = copy.deepcopy(ref)
+
+    gathered_dtypes = []
+    if sequence_parallel:
+        plan = {
+            "ffn": PrepareFloat8ModuleInput(input_layouts=Shard(1), desired_input_layouts=Replicate()),
+            "ffn.w1": Float8ColwiseParallel(),
+            "ffn.w2": Float8RowwiseParallel(output_layouts=Shard(1)),
+            "ffn.w3": Float8ColwiseParallel(),
+        }
+    else:
+        plan = {
+            "ffn.w1": Float8ColwiseParallel(),
+            "ffn.w2": Float8RowwiseParallel(),
+            "ffn.w3": Float8ColwiseParallel(),
+        }
+    tp = parallelize_module(tp, mesh, plan)
+
+    torch.manual_seed(9)  # same global input on every rank
+    x_full = torch.randn(2, 8, 16)
+    x_ref = x_full.clone().requires_grad_(True)
+    y_ref = ref(x_ref)
+    y_ref.sum().backward()
+
+    if sequence_parallel:
+        x_loc = x_full.chunk(world, dim=1)[rank].clone().requires_grad_(True)
+        # spy on the functional all-gather payload
+        import float8_experimental_b200.float8_ops as fo
+
+        inner = fo.FLOAT8_OPS_TABLE[torch.ops._c10d_functional.all_gather_into_tensor.default]
+
+        def spy(op, args, kwargs=None):
+            gathered_dtypes.append((type(args[0]), args[0]._data.dtype))
+            return inner(op, args, kwargs)
+
+        fo.FLOAT8_OPS_TABLE[torch.ops._c10d_functional.all_gather_into_tensor.default] = spy
+        y = tp(x_loc)
+        y_full = torch.cat(_all_gather_list(y if not isinstance(y, DTensor) else y.to_local(), world), dim=1)
+        y.sum().backward() if not isinstance(y, DTensor) else y.to_local().sum().backward()
+        gx = torch.cat(_all_gather_list(x_loc.grad, world), dim=1)
+        assert gathered_dtypes and gathered_dtypes[0] == (Float8Tensor, torch.float8_e4m3fn), gathered_dtypes
+    else:
+        x_loc = x_full.clone().requires_grad_(True)
+        y = tp(x_loc)
+        y_full = y.full_tensor() if isinstance(y, DTensor) else y
+        y_full.sum().backward()
+        gx = x_loc.grad
+    torch.testing.assert_close(y_full.detach(), y_ref.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(gx, x_ref.grad, rtol=1e-5, atol=1e-6)
+    w1g = tp.ffn.w1.weight.grad
+    w1g = w1g.full_tensor() if isinstance(w1g, DTensor) else w1g
+    torch.testing.assert_close(w1g, ref.ffn.w1.weight.grad, rtol=1e-5, atol=1e-6)
+    dist.destroy_process_group()
+
+
+def _all_gather_list(t, world):
+    outs = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(outs, t.contiguous())
+    return outs

@@ -21,7 +21,9 @@ _installed = False
 
 
 def to_np(t: torch.Tensor) -> np.ndarray:
-    t = t.detach().contiguous()
+    # clone: exporting a tensor to numpy pins its storage (it can no longer be resized),
+    # which FSDP2 does to the buffers it owns
+    t = t.detach().contiguous().clone()
     if t.dtype == torch.float32:
         return t.numpy()
     if t.dtype in (torch.bfloat16, torch.float16):
