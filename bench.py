@@ -172,22 +172,39 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)  # activations differ per rank
+    wgen = torch.Generator(device=dev).manual_seed(99)           # weights are the same everywhere
+    # N > 1: FSDP2 over the ranks.  Every weight is sharded on dim 0, cast to e4m3 shard by
+    # shard and all-gathered as 1 byte per element before forward and again before backward;
+    # gradients are reduce-scattered in bf16; after the step ONE all-reduce refreshes all
+    # weight scales (precompute_float8_dynamic_scale_for_fsdp).  Tokens per GPU stay fixed.
+    fsdp = world > 1
+    cfg = f8.Float8LinearConfig(enable_fsdp_float8_all_gather=fsdp)
     layers, xs, gos, host = [], [], [], []
     shapes = [s for s in SHAPES if args.layers is None or s[0] in args.layers.split(",")]
     for name, k, n in shapes:
         lin = torch.nn.Linear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
-            lin.weight.normal_(0.0, 0.02, generator=gen)
-        layers.append(Float8Linear.from_float(lin, f8.Float8LinearConfig()))
+            lin.weight.normal_(0.0, 0.02, generator=wgen)
+        layers.append(Float8Linear.from_float(lin, cfg))
         xs.append(torch.randn(M_TOKENS, k, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True))
         gos.append(torch.randn(M_TOKENS, n, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3))
+
+    holder = torch.nn.ModuleList(layers)
+    if fsdp:
+        from torch.distributed.fsdp import fully_shard
+
+        for layer in layers:
+            fully_shard(layer)
+        f8.precompute_float8_dynamic_scale_for_fsdp(holder)
 
     def step():
         for layer, x, go in zip(layers, xs, gos):
             x.grad = None
             layer.weight.grad = None
             layer(x).backward(go)
+        if fsdp:
+            f8.precompute_float8_dynamic_scale_for_fsdp(holder)
 
     def barrier():
         if world > 1:
@@ -326,7 +343,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                         "dynamic scaling, bf16 in/out",
             "shapes_KN": {name: [k, n] for name, k, n in shapes},
             "l2": "inputs larger than L2 (smallest tensor cast per layer is 134 MB; L2 is 126 MB)",
-            "parallelism": "replicas" if world > 1 else "single",
+            "parallelism": f"fsdp2 x{world}: fp8 weight all-gather (1 B/elem) fwd+bwd, bf16 grad reduce-scatter, "
+                           "one amax all-reduce per step" if fsdp else "single GPU",
         },
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,

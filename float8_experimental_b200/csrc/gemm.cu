@@ -39,7 +39,6 @@ constexpr int B_BYTES = BN * BK;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 16;  // tile rasterisation: walk 16 M-tiles before moving along N
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;  // about one second
 
 struct __align__(8) Barriers {
@@ -162,15 +161,26 @@ __host__ __device__ constexpr uint32_t make_idesc(int a_kind, int b_kind) {
 struct TileCoord {
   int m, n;
 };
-__device__ __forceinline__ TileCoord tile_coord(int64_t idx, int tiles_m, int tiles_n) {
-  const int64_t per_group = (int64_t)GROUP_M * tiles_n;
+// Tile order for L2 reuse.  Tiles are visited in bands of `group` tiles along one
+// dimension (M when along_n == 0), fastest inside the band, then along the other
+// dimension.  The CTAs running at the same time then share one operand panel
+// (group x K bytes, sized on the host to stay in L2) while the other operand streams by.
+// `raster` packs group (low 16 bits) and along_n (bit 16).
+__device__ __forceinline__ TileCoord tile_coord(int64_t idx, int tiles_m, int tiles_n, int raster) {
+  const int group = raster & 0xFFFF;
+  const bool along_n = (raster >> 16) & 1;
+  const int t_band = along_n ? tiles_n : tiles_m;   // dimension cut into bands
+  const int t_other = along_n ? tiles_m : tiles_n;
+  const int64_t per_group = (int64_t)group * t_other;
   const int g = (int)(idx / per_group);
-  const int first_m = g * GROUP_M;
-  const int gsz = min(GROUP_M, tiles_m - first_m);
+  const int first = g * group;
+  const int gsz = min(group, t_band - first);
   const int64_t in_g = idx - (int64_t)g * per_group;
+  const int a = first + (int)(in_g % gsz);
+  const int b = (int)(in_g / gsz);
   TileCoord c;
-  c.m = first_m + (int)(in_g % gsz);
-  c.n = (int)(in_g / gsz);
+  c.m = along_n ? b : a;
+  c.n = along_n ? a : b;
   return c;
 }
 
@@ -319,7 +329,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
                 const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out, int64_t ldo,
-                int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store) {
+                int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = tiles + STAGES * STAGE_BYTES;
@@ -362,7 +372,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
@@ -422,7 +432,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     bool ok = true;
     int64_t local = 0;
     for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       // one lane polls, the rest of the warp sleeps at the shuffle
@@ -469,7 +479,6 @@ constexpr int PSTAGES = 6;
 constexpr int PA_BYTES = 128 * BK;
 constexpr int PB_BYTES = 128 * BK;
 constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
-constexpr int PGROUP_M = 8;
 
 struct __align__(8) PairBarriers {
   uint64_t full[PSTAGES];
@@ -552,24 +561,13 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBa
   return false;
 }
 
-__device__ __forceinline__ TileCoord pair_tile_coord(int64_t idx, int tiles_m, int tiles_n) {
-  const int64_t per_group = (int64_t)PGROUP_M * tiles_n;
-  const int g = (int)(idx / per_group);
-  const int first_m = g * PGROUP_M;
-  const int gsz = min(PGROUP_M, tiles_m - first_m);
-  const int64_t in_g = idx - (int64_t)g * per_group;
-  TileCoord c;
-  c.m = first_m + (int)(in_g % gsz);
-  c.n = (int)(in_g / gsz);
-  return c;
-}
 
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
-                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store) {
+                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = tiles + PSTAGES * PSTAGE_BYTES;
@@ -617,7 +615,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters) {
-        const TileCoord tc = pair_tile_coord(t, tiles_m, tiles_n);
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
         const int row_a = tc.m * PBM + (int)rank * 128;
         const int row_b = tc.n * PBN + (int)rank * 128;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -683,7 +681,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     bool ok = true;
     int64_t local = 0;
     for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
-      const TileCoord tc = pair_tile_coord(t, tiles_m, tiles_n);
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       int got = 1;
@@ -757,6 +755,30 @@ static int encode_output_map(CUtensorMap* map, void* base, int64_t m, int64_t n,
   return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
 }
 
+// Picks the band direction and width (see tile_coord): the band's operand panel
+// (width x tile x K bytes) should stay in L2 while the other operand is re-read once per
+// band; choose the direction with the smaller total HBM traffic.
+static int choose_raster(int64_t m, int64_t n, int64_t k, int tile_m, int tile_n) {
+  int64_t panel_bytes = 32ll << 20;
+  if (const char* e = getenv("F8B200_GEMM_PANEL_MB")) {
+    const long v = atol(e);
+    if (v > 0) panel_bytes = (int64_t)v << 20;
+  }
+  const int64_t tiles_m = (m + tile_m - 1) / tile_m, tiles_n = (n + tile_n - 1) / tile_n;
+  auto width = [&](int tile, int64_t tiles) {
+    int64_t g = panel_bytes / ((int64_t)tile * (k > 0 ? k : 1));
+    if (g < 8) g = 8;  // very long K: the panel cannot stay resident anyway, keep the band wide
+    if (g > tiles) g = tiles;
+    if (g > 0xFFFF) g = 0xFFFF;
+    return g < 1 ? (int64_t)1 : g;
+  };
+  const int64_t gm = width(tile_m, tiles_m), gn = width(tile_n, tiles_n);
+  const double a_bytes = (double)m * k, b_bytes = (double)n * k;
+  const double cost_m = a_bytes + b_bytes * (double)((tiles_m + gm - 1) / gm);
+  const double cost_n = b_bytes + a_bytes * (double)((tiles_n + gn - 1) / gn);
+  return cost_n < cost_m ? (int)(gn | (1 << 16)) : (int)gm;
+}
+
 template <typename OutT>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma, const float* sa,
                   const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k, uint32_t idesc,
@@ -772,7 +794,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   if (tiles < grid) grid = (int)tiles;
   gemm_fp8_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mo, sa, sb, static_cast<const OutT*>(bias),
                                                                 static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
-                                                                use_tma);
+                                                                use_tma, choose_raster(m, n, k, BM, BN));
   return check_launch();
 }
 
@@ -811,7 +833,8 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   const OutT* bias_t = static_cast<const OutT*>(bias);
   OutT* out_t = static_cast<OutT*>(out);
   return record_cuda_error(
-      cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma));
+      cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
+                         choose_raster(m, n, k, pair::PBM, pair::PBN)));
 }
 
 // 0 = one CTA per tile (128x256), 1 = CTA pairs (256x256, cta_group::2).  The environment
