@@ -271,7 +271,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             x.grad = None
             layer.weight.grad = None
             layer(x).backward(go)
-            result_host[i].copy_(layer.weight.grad[0, :8], non_blocking=True)
+            g = layer.weight.grad
+            g = g.to_local() if hasattr(g, "to_local") else g  # FSDP2 hands out DTensor gradients
+            result_host[i].copy_(g[0, :8], non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result
 
     e2e_steps = max(1, min(args.steps, 5))
@@ -323,8 +325,14 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     gemm_tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     # dynamic amax+cast of n bf16 elements with the transposed copy: 2n + 2n + n + n bytes
-    cast_elems = args.steps * sum(M_TOKENS * k + n * k + M_TOKENS * n for _, k, n in shapes)
-    cast_gbs = 6.0 * cast_elems / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
+    # (under FSDP2 each rank casts 1/world of every weight, without the transposed copy, and
+    # the weight amaxes come from one multi-tensor launch)
+    act_elems = sum(M_TOKENS * k + M_TOKENS * n for _, k, n in shapes)
+    w_elems = sum(n * k for _, k, n in shapes)
+    cast_bytes = args.steps * (6.0 * act_elems + (5.0 * w_elems / world if fsdp else 6.0 * w_elems))
+    if fsdp:
+        cast_bytes += args.steps * 2.0 * w_elems / world  # forward + backward all-gather each re-cast the shard
+    cast_gbs = cast_bytes / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
 
     # bounded CPU sample (rank 0, N = 1 only)
     cpu_baseline = None

@@ -1,0 +1,53 @@
+"""The multi-rank cases of `dist_cases.py` on real GPUs: two NCCL ranks, one B200 each,
+the CUDA kernels instead of the CPU stand-ins.  Skipped with fewer than two GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORLD = 2
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, case, world, port, extra):
+    os.environ["F8_DIST_DEVICE"] = "cuda"
+    for p in (os.path.dirname(HERE), HERE, os.path.join(HERE, "golden")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import dist_cases
+
+    getattr(dist_cases, case)(rank, world, port, *extra)
+
+
+def _run(case, *extra):
+    if torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_entry, args=(case, WORLD, _free_port(), extra), nprocs=WORLD, join=True)
+
+
+def test_sync_all_reduces_amaxes_once():
+    _run("case_sync_all_reduce")
+
+
+@pytest.mark.parametrize("precompute", [False, True])
+def test_fsdp2_fp8_all_gather_matches_unsharded(precompute):
+    _run("case_fsdp2_fp8_all_gather", precompute)
+
+
+def test_fsdp2_delayed_weight_scaling():
+    _run("case_fsdp2_delayed")
+
+
+@pytest.mark.parametrize("sequence_parallel", [False, True])
+def test_tensor_parallel_matches_unsharded(sequence_parallel):
+    _run("case_tensor_parallel", sequence_parallel)
