@@ -103,12 +103,13 @@ class ClockSampler:
 # CPU arm: the oracle's restatement of the reference's emulate path
 # ---------------------------------------------------------------------------
 def cpu_sample_step(sample):
-    from oracle import f8_oracle as O
+    # C/OpenMP restatement of the casts + numpy BLAS for the three fp32 GEMMs
+    from oracle import f8_oracle_c as C
 
-    return O.float8_linear_fwd_bwd(sample["x"], sample["w"], sample["go"], O.BF16)
+    return C.float8_linear_fwd_bwd(sample["x"], sample["w"], sample["go"], "bf16")
 
 
-def make_cpu_sample(rows: int = 256):
+def make_cpu_sample(rows: int = 2048):
     """`rows` tokens of the `wo` layer (K = N = 8192)."""
     import numpy as np
 
@@ -120,7 +121,8 @@ def make_cpu_sample(rows: int = 256):
     return {"x": f(rng.standard_normal((rows, k))), "w": f(rng.standard_normal((n, k)) * 0.02),
             "go": f(rng.standard_normal((rows, n)) * 1e-3), "rows": rows, "k": k, "n": n,
             "flops": layer_flops(k, n, rows),
-            "desc": f"wo layer (K=N=8192) fwd+bwd on {rows} of {M_TOKENS} token rows, numpy port of the emulate=True path"}
+            "desc": f"wo layer (K=N=8192) fwd+bwd on {rows} of {M_TOKENS} token rows; port of the emulate=True path "
+                    "(casts in C with OpenMP, fp32 GEMMs through numpy BLAS, all host cores)"}
 
 
 def time_cpu(sample, steps: int, warmup: int):
@@ -137,7 +139,7 @@ def time_cpu(sample, steps: int, warmup: int):
 def run_reference_arm(args, rank: int, world: int):
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
     sample = make_cpu_sample()
     ts = time_cpu(sample, steps, warmup)
     tflops = sample["flops"] / statistics.median(ts) / 1e12
@@ -338,7 +340,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
         sample = make_cpu_sample()
-        ts = time_cpu(sample, 2, 0)
+        ts = time_cpu(sample, 6, 1)
         cpu_baseline = {"value": sample["flops"] / min(ts) / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
                         "kind": "port", "sample": sample["desc"]}
 
