@@ -157,6 +157,53 @@ def run_reference_arm(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+def measure_delayed(torch, f8, _native, dev, x):
+    """Config 3: one batched sync over 320 linears (960 rows, history 16) and the one-pass
+    delayed cast (amax + cast + transposed copy) of a [16384, 8192] bf16 activation."""
+    from float8_experimental_b200.float8_linear_utils import get_float8_layers
+
+    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    cfg = f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d)
+    model = torch.nn.Sequential(*[torch.nn.Linear(16, 16, bias=False, device=dev) for _ in range(320)])
+    f8.convert_to_float8_training(model, config=cfg)
+    layers = get_float8_layers(model)
+    g = torch.Generator(device=dev).manual_seed(3)
+    for m in layers:
+        m.last_seen_input_dtype = torch.bfloat16
+        for name, sigma in (("input", 1.0), ("weight", 0.02), ("grad_output", 1e-3)):
+            getattr(m, f"fp8_amax_history_{name}").copy_(torch.randn(16, device=dev, generator=g).abs() * 4 * sigma)
+            getattr(m, f"fp8_amax_{name}").copy_(torch.randn(1, device=dev, generator=g).abs() * 4 * sigma)
+    for _ in range(3):
+        f8.sync_float8_amax_and_scale_history(model, layers)
+    torch.cuda.synchronize()
+    _native.reset_counters()
+    _native.enable_kernel_events(True)
+    t0 = time.perf_counter()
+    for _ in range(20):
+        f8.sync_float8_amax_and_scale_history(model, layers)
+    torch.cuda.synchronize()
+    wall_us = (time.perf_counter() - t0) / 20 * 1e6
+    ev = _native.kernel_event_totals().get("sync", (0.0, 1))
+    _native.enable_kernel_events(False)
+    # one-pass delayed cast
+    from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_delayed
+
+    scale, amax = torch.ones(1, device=dev), torch.zeros(1, device=dev)
+    for _ in range(3):
+        hp_tensor_to_float8_delayed(x, scale, torch.float8_e4m3fn, amax)
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(20):
+        hp_tensor_to_float8_delayed(x, scale, torch.float8_e4m3fn, amax)
+    s1.record()
+    torch.cuda.synchronize()
+    cast_ms = s0.elapsed_time(s1) / 20
+    return {"sync_rows": 960, "sync_kernel_us": ev[0] / max(ev[1], 1) * 1e3, "sync_launches_per_call": 1,
+            "sync_wall_us_per_call": wall_us,
+            "delayed_cast_ms_16384x8192": cast_ms, "delayed_cast_gbs": 4.0 * x.numel() / (cast_ms * 1e-3) / 1e9,
+            "delayed_cast_bytes": "4 B per element: 2 read + 1 fp8 + 1 transposed fp8, amax from the same read"}
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -292,6 +339,11 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         e2e_s = t.item()
     e2e_value = world * flops_per_step / e2e_s / 1e12
 
+    # ---- delayed-scaling side measurements (BASELINE config 3), outside the timed region ----
+    delayed = None
+    if rank == 0 and world == 1:
+        delayed = measure_delayed(torch, f8, _native, dev, xs[0].detach())
+
     # ---- library kernel to beat, outside every timed region -----------------
     cublaslt = None
     if rank == 0:
@@ -378,6 +430,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         "time_share_ms_per_step": {"gemm": gemm_ms / args.steps, "cast": cast_ms / args.steps,
                                    "amax": amax_ms / args.steps},
         "cublaslt_fp8_tflops_wo_fwd": cublaslt,
+        "delayed_scaling": delayed,
         "cpu_baseline": cpu_baseline,
     }
     print(json.dumps(line), flush=True)

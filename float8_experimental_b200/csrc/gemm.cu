@@ -105,6 +105,24 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// L2 eviction-priority policies for the bulk tensor copies (0 = normal, 1 = evict first,
+// 2 = evict last).
+__device__ __forceinline__ uint64_t l2_policy(int kind) {
+  uint64_t p;
+  if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  else if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], "
+      "[%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -229,6 +247,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, const void* smem_src, int x, int y,
+                                                  uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
@@ -248,6 +273,7 @@ struct EpilogueArgs {
   const CUtensorMap* tma_out;
   uint8_t* staging;  // this warp's two boxes, 1024-byte aligned
   float inv;
+  int store_evict_first;  // the output is not read again by this kernel: do not let it displace operands in L2
 };
 
 // Drains `ncol_total` accumulator columns starting at TMEM address `taddr` for the 32
@@ -316,7 +342,8 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueArgs<OutT>& e, u
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(e.tma_out, box, col - sub * 32, row0);
+        if (e.store_evict_first) tma_store_2d_hint(e.tma_out, box, col - sub * 32, row0, l2_policy(1));
+        else tma_store_2d(e.tma_out, box, col - sub * 32, row0);
         bulk_commit();
       }
       ++boxes;
@@ -368,6 +395,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      // raster bit 16: bands run along N (B is the resident panel, A streams), else along M.
+      // hint bits: 21 = streaming operand evict-first, 22 = panel operand evict-last.
+      const bool panel_is_b = (raster >> 16) & 1;
+      const int pol_panel = ((raster >> 22) & 1) ? 2 : 0, pol_stream = ((raster >> 21) & 1) ? 1 : 0;
+      const uint64_t pol_a = l2_policy(panel_is_b ? pol_stream : pol_panel);
+      const uint64_t pol_b = l2_policy(panel_is_b ? pol_panel : pol_stream);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -377,8 +410,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           if (!mbar_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * STAGE_BYTES;
           mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tma_a, kb * BK, tc.m * BM, &bars->full[stage]);
-          tma_load_2d(sa + A_BYTES, &tma_b, kb * BK, tc.n * BN, &bars->full[stage]);
+          tma_load_2d_hint(sa, &tma_a, kb * BK, tc.m * BM, &bars->full[stage], pol_a);
+          tma_load_2d_hint(sa + A_BYTES, &tma_b, kb * BK, tc.n * BN, &bars->full[stage], pol_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -427,7 +460,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
     }
     const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
-                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv};
+                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
     uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
@@ -511,11 +544,11 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
-                                                 uint32_t mbar_cluster_addr) {
+                                                 uint32_t mbar_cluster_addr, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
-      "[%4];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_cluster_addr)
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_cluster_addr), "l"(policy)
       : "memory");
 }
 // Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once all
@@ -611,6 +644,12 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      // raster bit 16: bands run along N (B is the resident panel, A streams), else along M.
+      // hint bits: 21 = streaming operand evict-first, 22 = panel operand evict-last.
+      const bool panel_is_b = (raster >> 16) & 1;
+      const int pol_panel = ((raster >> 22) & 1) ? 2 : 0, pol_stream = ((raster >> 21) & 1) ? 1 : 0;
+      const uint64_t pol_a = l2_policy(panel_is_b ? pol_stream : pol_panel);
+      const uint64_t pol_b = l2_policy(panel_is_b ? pol_panel : pol_stream);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -623,8 +662,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           uint8_t* sa = tiles + stage * PSTAGE_BYTES;
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
           const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
-          tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader);
-          tma_load_2d_pair(sa + PA_BYTES, &tma_b, kb * BK, row_b, full_in_leader);
+          tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader, pol_a);
+          tma_load_2d_pair(sa + PA_BYTES, &tma_b, kb * BK, row_b, full_in_leader, pol_b);
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -676,7 +715,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
     }
     const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
-                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv};
+                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
     uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
@@ -776,7 +815,11 @@ static int choose_raster(int64_t m, int64_t n, int64_t k, int tile_m, int tile_n
   const double a_bytes = (double)m * k, b_bytes = (double)n * k;
   const double cost_m = a_bytes + b_bytes * (double)((tiles_m + gm - 1) / gm);
   const double cost_n = b_bytes + a_bytes * (double)((tiles_n + gn - 1) / gn);
-  return cost_n < cost_m ? (int)(gn | (1 << 16)) : (int)gm;
+  // L2 hints (bit 0: output stores evict-first, bit 1: streaming operand evict-first,
+  // bit 2: panel operand evict-last); F8B200_GEMM_L2HINT overrides the default.
+  int hints = 1;
+  if (const char* e = getenv("F8B200_GEMM_L2HINT")) hints = atoi(e) & 7;
+  return (cost_n < cost_m ? (int)(gn | (1 << 16)) : (int)gm) | (hints << 20);
 }
 
 template <typename OutT>
