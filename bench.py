@@ -239,21 +239,41 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         xs.append(torch.randn(M_TOKENS, k, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True))
         gos.append(torch.randn(M_TOKENS, n, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3))
 
-    holder = torch.nn.ModuleList(layers)
+    class _Layers(torch.nn.Module):
+        """The four independent linears under one root, so that FSDP2 shares one
+        communication context and prefetches the next layer's all-gather."""
+
+        def __init__(self, mods):
+            super().__init__()
+            self.mods = torch.nn.ModuleList(mods)
+
+        def forward(self, inputs):
+            return [m(x) for m, x in zip(self.mods, inputs)]
+
+    holder = _Layers(layers)
     if fsdp:
         from torch.distributed.fsdp import fully_shard
 
         for layer in layers:
             fully_shard(layer)
+        if args.fsdp_root:
+            fully_shard(holder)
         f8.precompute_float8_dynamic_scale_for_fsdp(holder)
 
     def step():
-        for layer, x, go in zip(layers, xs, gos):
+        for layer, x in zip(layers, xs):
             x.grad = None
             layer.weight.grad = None
-            layer(x).backward(go)
-        if fsdp:
+        if fsdp and args.fsdp_root:
+            torch.autograd.backward(holder(xs), gos)
             f8.precompute_float8_dynamic_scale_for_fsdp(holder)
+        elif fsdp:
+            for layer, x, go in zip(layers, xs, gos):
+                layer(x).backward(go)
+            f8.precompute_float8_dynamic_scale_for_fsdp(holder)
+        else:
+            for layer, x, go in zip(layers, xs, gos):
+                layer(x).backward(go)
 
     def barrier():
         if world > 1:
@@ -315,11 +335,16 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 ready.append(ev)
+        if fsdp:
+            for ev in ready:
+                main.wait_event(ev)
+            step()
         for i, (layer, x, go) in enumerate(zip(layers, xs, gos)):
-            main.wait_event(ready[i])
-            x.grad = None
-            layer.weight.grad = None
-            layer(x).backward(go)
+            if not fsdp:
+                main.wait_event(ready[i])
+                x.grad = None
+                layer.weight.grad = None
+                layer(x).backward(go)
             g = layer.weight.grad
             g = g.to_local() if hasattr(g, "to_local") else g  # FSDP2 hands out DTensor gradients
             result_host[i].copy_(g[0, :8], non_blocking=True)
@@ -446,6 +471,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", default=None, help="comma list out of wqkv,wo,w13,w2 (default: all four)")
+    ap.add_argument("--fsdp-root", type=int, default=1,
+                    help="N > 1: 1 = the four layers share one FSDP2 root (all-gather prefetch), 0 = four roots")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed part only, short JSON; for profiler captures of a small case")
     args = ap.parse_args()
