@@ -549,11 +549,12 @@ __global__ void transpose_u8_generic_kernel(const uint8_t* in, int64_t rows, int
 }
 
 // ---------------------------------------------------------------------------
-// delayed-scaling bookkeeping: one thread per (layer, tensor) row
+// delayed-scaling bookkeeping
 // ---------------------------------------------------------------------------
-__global__ void delayed_sync_kernel(const float* amax, const float* hist, int64_t ld_hist, int64_t rows,
-                                    int hist_len, int64_t n_e4m3, int clamp_fp16, float* scale_out,
-                                    float* hist_out, int64_t ld_hist_out) {
+// General form: one thread per (layer, tensor) row walks the history.
+__global__ void delayed_sync_serial_kernel(const float* amax, const float* hist, int64_t ld_hist, int64_t rows,
+                                           int hist_len, int64_t n_e4m3, int clamp_fp16, float* scale_out,
+                                           float* hist_out, int64_t ld_hist_out) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const float cur = amax[r];
@@ -573,6 +574,37 @@ __global__ void delayed_sync_kernel(const float* amax, const float* hist, int64_
   if (has_nan) m = __uint_as_float(0x7FC00000u);
   const float fmax8 = r < n_e4m3 ? kE4M3Max : kE5M2Max;
   scale_out[r] = amax_to_scale_dev(m, fmax8, F8B200_FP32, clamp_fp16 != 0);
+}
+
+// hist_len <= 16 (the default recipe): 16 lanes per row, one parallel load of the whole
+// history, roll by shuffle, max by butterfly.  All reads of a row happen before any write,
+// so hist_out may alias hist.
+__global__ void __launch_bounds__(128) delayed_sync_kernel(const float* amax, const float* hist, int64_t ld_hist,
+                                                           int64_t rows, int hist_len, int64_t n_e4m3,
+                                                           int clamp_fp16, float* scale_out, float* hist_out,
+                                                           int64_t ld_hist_out) {
+  const int sub = threadIdx.x & 15;
+  const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const bool live = r < rows;
+  const bool has_entry = live && sub < hist_len;
+  const float cur = live ? amax[r] : 0.0f;
+  const float old = has_entry ? hist[r * ld_hist + sub] : 0.0f;
+  float prev = __shfl_up_sync(0xFFFFFFFFu, old, 1, 16);  // entry sub-1 of the same row
+  if (sub == 0) prev = cur;
+  // entries 0..H-2 survive the roll; the current amax joins them
+  float m = (has_entry && sub < hist_len - 1) ? old : 0.0f;
+  bool has_nan = (m != m) || (cur != cur);
+  m = fmaxf(m, cur);
+  const unsigned nanbits = __ballot_sync(0xFFFFFFFFu, has_nan);
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  __syncwarp();
+  if (has_entry && hist_out != nullptr) hist_out[r * ld_hist_out + sub] = prev;
+  if (live && sub == 0) {
+    if (nanbits & (0xFFFFu << (threadIdx.x & 16))) m = __uint_as_float(0x7FC00000u);
+    const float fmax8 = r < n_e4m3 ? kE4M3Max : kE5M2Max;
+    scale_out[r] = amax_to_scale_dev(m, fmax8, F8B200_FP32, clamp_fp16 != 0);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -779,9 +811,16 @@ extern "C" int f8b200_delayed_sync(const float* amax, const float* hist, int64_t
   if (hist_out != nullptr && ld_hist_out < hist_len) return F8B200_ERR_BAD_ARG;
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
-  const unsigned blocks = (unsigned)((rows + 127) / 128);
-  delayed_sync_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      amax, hist, ld_hist, rows, hist_len, n_e4m3, orig_dtype == F8B200_FP16 ? 1 : 0, scale_out, hist_out,
-      ld_hist_out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int clamp = orig_dtype == F8B200_FP16 ? 1 : 0;
+  if (hist_len <= 16) {
+    const unsigned blocks = (unsigned)((rows * 16 + 127) / 128);
+    delayed_sync_kernel<<<blocks, 128, 0, st>>>(amax, hist, ld_hist, rows, hist_len, n_e4m3, clamp, scale_out,
+                                                hist_out, ld_hist_out);
+  } else {
+    const unsigned blocks = (unsigned)((rows + 127) / 128);
+    delayed_sync_serial_kernel<<<blocks, 128, 0, st>>>(amax, hist, ld_hist, rows, hist_len, n_e4m3, clamp,
+                                                       scale_out, hist_out, ld_hist_out);
+  }
   return check_launch();
 }

@@ -803,10 +803,15 @@ static int choose_raster(int64_t m, int64_t n, int64_t k, int tile_m, int tile_n
     const long v = atol(e);
     if (v > 0) panel_bytes = (int64_t)v << 20;
   }
+  int64_t min_band = 8;
+  if (const char* e = getenv("F8B200_GEMM_MINBAND")) {
+    const long v = atol(e);
+    if (v > 0) min_band = v;
+  }
   const int64_t tiles_m = (m + tile_m - 1) / tile_m, tiles_n = (n + tile_n - 1) / tile_n;
   auto width = [&](int tile, int64_t tiles) {
     int64_t g = panel_bytes / ((int64_t)tile * (k > 0 ? k : 1));
-    if (g < 8) g = 8;  // very long K: the panel cannot stay resident anyway, keep the band wide
+    if (g < min_band) g = min_band;  // very long K: the panel cannot stay resident anyway, keep the band wide
     if (g > tiles) g = tiles;
     if (g > 0xFFFF) g = 0xFFFF;
     return g < 1 ? (int64_t)1 : g;

@@ -262,3 +262,50 @@ def test_gemm_full_size_linearity(gemm_mode):
     half = torch.tensor(0.5, device="cuda")
     out2 = gemm(a, b, half, one)  # dividing by scale 0.5 doubles the result
     assert torch.equal(out2.float(), out.float() * 2)
+
+
+def test_cast_full_size_properties():
+    """BASELINE-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
+    size-independent properties: amax equals max|x|; the transposed copy is the transpose;
+    every decoded value is within half an fp8 step of x*scale; casting the dequantised
+    tensor again with the same scale returns the same bytes (idempotence)."""
+    torch.manual_seed(5)
+    x = torch.randn(16384, 8192, device="cuda", dtype=torch.bfloat16)
+    x[123, 4567] = 37.5
+    rows, cols = x.shape
+    out = torch.empty(rows, cols, dtype=torch.uint8, device="cuda")
+    out_t = torch.empty(cols, rows, dtype=torch.uint8, device="cuda")
+    amax, sc = torch.zeros((), device="cuda"), torch.zeros((), device="cuda")
+    N.amax(x, amax)
+    N.cast(x, rows, cols, cols, 1, amax, sc, False, N.E4M3, out, cols, out_t, rows, None, True)
+    torch.cuda.synchronize()
+    assert amax.item() == 37.5
+    assert sc.item() == float(O.amax_to_scale(np.float32(37.5), O.E4M3, O.BF16, O.BF16))
+    assert torch.equal(out_t, out.t())
+    deq = out.view(torch.float8_e4m3fn).float()
+    prod = (x * sc.to(torch.bfloat16)).float()  # the reference's bf16 product
+    err = (deq - prod).abs()
+    step = torch.maximum(prod.abs() * 2.0 ** -4, torch.tensor(2.0 ** -10, device="cuda"))  # half ulp of e4m3
+    assert bool((err <= step).all())
+    again = torch.empty_like(out)
+    one = torch.ones((), device="cuda")
+    N.cast(deq, rows, cols, cols, 0, one, None, True, N.E4M3, again, cols, None, 0, None, False)
+    assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("hist_len", [1, 4, 16, 17, 40])
+def test_delayed_sync_history_lengths(hist_len):
+    rng = np.random.default_rng(hist_len)
+    rows = 77
+    amax = (rng.random(rows) * 5).astype(np.float32)
+    hist = (rng.random((rows, hist_len)) * 5).astype(np.float32)
+    hist[3, 0] = np.nan
+    amax[9] = np.nan
+    kinds = [O.E4M3] * 50 + [O.E5M2] * 27
+    ref_scale, ref_hist = O.sync_amax_and_scale(amax, hist, kinds, O.FP32, True)
+    a, h = torch.from_numpy(amax).cuda(), torch.from_numpy(hist).cuda()
+    s = torch.zeros(rows, device="cuda")
+    N.delayed_sync(a, h, 50, N.FP32, s, h)  # in place
+    got_s, got_h = s.cpu().numpy(), h.cpu().numpy()
+    assert np.all((got_s == ref_scale) | (np.isnan(got_s) & np.isnan(ref_scale)))
+    assert np.all((got_h == ref_hist) | (np.isnan(got_h) & np.isnan(ref_hist)))
