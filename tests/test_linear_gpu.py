@@ -153,3 +153,23 @@ def test_model_conversion_and_training_step():
     assert losses[-1] < losses[0]
     with pytest.raises(AssertionError, match="amaxes and scales not synced"):
         model(x)
+
+
+def test_inference_flows_on_gpu():
+    """Weight-only, dynamic and static activation casting (reference: test/test_inference_flows.py)."""
+    from float8_experimental_b200.inference import ActivationCasting, QuantConfig, quantize_to_float8
+
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(256, 512, bias=True), nn.Linear(512, 256, bias=False)).cuda().to(torch.bfloat16)
+    x = torch.randn(4, 64, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        y_ref = ref(x)
+    for cfg in (QuantConfig(ActivationCasting.WEIGHT_ONLY), QuantConfig(ActivationCasting.DYNAMIC),
+                QuantConfig(ActivationCasting.STATIC, static_quantization_scale=torch.tensor([60.0], device="cuda"))):
+        import copy
+
+        q = quantize_to_float8(copy.deepcopy(ref), cfg)
+        with torch.no_grad():
+            y = q(x)
+        assert y.shape == y_ref.shape and y.dtype == torch.bfloat16
+        assert compute_error(y_ref.float(), y.float()) > 15.0, cfg.activation_casting
