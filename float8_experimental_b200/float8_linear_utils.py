@@ -167,19 +167,27 @@ def sync_float8_amax_and_scale_history(model: torch.nn.Module, fp8_layers=None) 
         log.warning("Calling sync_float8_amax_and_scale_history on a module with no Float8Linear layers")
         return
 
-    x_dtypes = {m.last_seen_input_dtype for m in fp8_layers}
-    if len(x_dtypes) != 1:
-        raise ValueError(f"All layers must have the same last seen input_dtype, got {x_dtypes}")
-    recipes = {m.config.delayed_scaling_config.scale_fn_name for m in fp8_layers}
-    if len(recipes) != 1:
-        raise ValueError(f"All layers must have the same scale_fn recipe, got {recipes}")
-    (x_dtype,) = x_dtypes
-    # None (no forward seen yet) behaves like any non-fp16 dtype: no fp16 clamp of the scale
-    orig_code = N.hp_code(x_dtype) if x_dtype is not None else N.FP32
-
     anchor = fp8_layers[0]
     slabs: Optional[_SyncSlabs] = getattr(anchor, _SLABS_ATTR, None)
-    if slabs is None or not slabs.matches(fp8_layers):
+    tok = slabs.token if slabs is not None else None
+    # one pass over the layers: recipe / dtype agreement and slab membership
+    x_dtype = anchor.last_seen_input_dtype
+    recipe = anchor.config.delayed_scaling_config.scale_fn_name
+    uniform, packed = True, slabs is not None and slabs.n_layers == len(fp8_layers)
+    for i, m in enumerate(fp8_layers):
+        if m.last_seen_input_dtype is not x_dtype or m.config.delayed_scaling_config.scale_fn_name != recipe:
+            uniform = False
+        if packed and getattr(m, "_f8_sync_slot", None) != (tok, i):
+            packed = False
+    if not uniform:
+        x_dtypes = {m.last_seen_input_dtype for m in fp8_layers}
+        if len(x_dtypes) != 1:
+            raise ValueError(f"All layers must have the same last seen input_dtype, got {x_dtypes}")
+        recipes = {m.config.delayed_scaling_config.scale_fn_name for m in fp8_layers}
+        raise ValueError(f"All layers must have the same scale_fn recipe, got {recipes}")
+    # None (no forward seen yet) behaves like any non-fp16 dtype: no fp16 clamp of the scale
+    orig_code = N.hp_code(x_dtype) if x_dtype is not None else N.FP32
+    if not packed:
         slabs = _SyncSlabs(list(fp8_layers))
         object.__setattr__(anchor, _SLABS_ATTR, slabs)
 
