@@ -438,19 +438,24 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                 "ms_per_step": e2e_s * 1e3},
         "gpu_launches": launches,
         "roofline": {
-            "kernel": "gemm_fp8_kernel (tcgen05 kind::f8f6f4)", "bound": "tensor", "achieved": gemm_tflops,
+            "kernel": "gemm_fp8_pair_kernel (tcgen05.mma.cta_group::2.kind::f8f6f4)", "bound": "tensor", "achieved": gemm_tflops,
             "peak": fp8_peak, "unit": "TFLOP/s", "frac": (gemm_tflops / fp8_peak) if gemm_tflops else None,
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (fp8 issues at twice the bf16 rate)",
             "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
-            "launches": gemm_calls, "traffic": None,
+            "launches": gemm_calls,
+            # dram__bytes_read + dram__bytes_write of one launch (wo forward, 16384x8192x8192) from the
+            # ncu capture summarised in profiles/gemm_fp8_pair_kernel_wo_16384x8192x8192.md
+            "traffic": 0.467e9 + 0.251e9, "traffic_algorithmic": 201.3e6 + 268.4e6,
         },
         "roofline_cast": {
-            "kernel": "amax_flat_kernel + cast_tile_kernel (dynamic amax+cast with transposed copy)", "bound": "hbm",
+            "kernel": "amax_flat_kernel + cast_tile8_kernel (dynamic amax+cast with transposed copy)", "bound": "hbm",
             "achieved": cast_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": (cast_gbs / peaks["hbm_gbs"]) if cast_gbs else None,
             "frac_of_nominal_8000": (cast_gbs / NOMINAL_HBM_GBS) if cast_gbs else None,
             "algorithmic_bytes": "6 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8 + 1 transposed fp8)",
-            "launches": cast_calls + amax_calls, "traffic": None,
+            "launches": cast_calls + amax_calls,
+            # one 16384x8192 bf16 tensor, amax + cast launches, from profiles/cast_tile8_kernel_16384x8192_bf16.md
+            "traffic": 268.4e6 + 268.5e6 + 211.9e6, "traffic_algorithmic": 6 * 134.2e6,
         },
         "time_share_ms_per_step": {"gemm": gemm_ms / args.steps, "cast": cast_ms / args.steps,
                                    "amax": amax_ms / args.steps},
