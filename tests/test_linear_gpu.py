@@ -173,3 +173,18 @@ def test_inference_flows_on_gpu():
             y = q(x)
         assert y.shape == y_ref.shape and y.dtype == torch.bfloat16
         assert compute_error(y_ref.float(), y.float()) > 15.0, cfg.activation_casting
+
+
+def test_autocast_sets_the_output_dtype():
+    """Under autocast the input is cast to the autocast dtype and the output follows it
+    (reference: test/test_base.py:268-317)."""
+    lin = nn.Linear(64, 32, bias=True, device="cuda")  # fp32 parameters
+    m = Float8Linear.from_float(lin, f8.Float8LinearConfig())
+    x = torch.randn(16, 64, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x)
+    assert y.dtype == torch.bfloat16
+    y.float().sum().backward()
+    assert m.weight.grad is not None and m.weight.grad.dtype == torch.float32
+    with torch.autocast("cuda", dtype=torch.float16):
+        assert m(x).dtype == torch.float16
