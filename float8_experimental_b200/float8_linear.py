@@ -125,7 +125,7 @@ class Float8Linear(torch.nn.Linear):
     def cast_input_to_float8(self, input: torch.Tensor, is_amax_initialized: bool) -> torch.Tensor:
         if torch.is_autocast_enabled():
             # same rule F.linear applies, so the output keeps the autocast dtype
-            input = input.to(torch.get_autocast_gpu_dtype())
+            input = input.to(torch.get_autocast_dtype("cuda"))
         if self.scaling_type_input is ScalingType.DELAYED:
             _maybe_initialize_amaxes_scales_for_float8_cast(
                 input, self.fp8_amax_input, self.fp8_amax_history_input, self.fp8_scale_input,
