@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE config 2): the four LLaMa-2-70B linear shapes, M = 16384 tokens,
+Workload (the headline single-GPU configuration): the four LLaMa-2-70B linear shapes, M = 16384 tokens,
 dynamic scaling of input / weight / grad_output, bf16 in and out.  One "step" is one
 forward + backward of each of the four `Float8Linear` layers through the public module
 API (3 amax reductions, 3 casts, 3 fp8 GEMMs per layer).  FLOPs per layer = 3*2*M*K*N.
@@ -364,7 +364,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         e2e_s = t.item()
     e2e_value = world * flops_per_step / e2e_s / 1e12
 
-    # ---- delayed-scaling side measurements (BASELINE config 3), outside the timed region ----
+    # ---- delayed-scaling side measurements (the delayed-scaling configuration: 320 linears, history 16), outside the timed region ----
     delayed = None
     if rank == 0 and world == 1:
         delayed = measure_delayed(torch, f8, _native, dev, xs[0].detach())

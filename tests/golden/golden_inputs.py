@@ -12,7 +12,7 @@ def sha256(arr: np.ndarray) -> str:
 
 
 def config1_inputs():
-    """BASELINE config 1: x bf16 [2048, 4096] ~ N(0,1) with 0.1 % of the elements (seeded
+    """The small reference configuration (one 4096x4096 layer, 2048 tokens): x bf16 [2048, 4096] ~ N(0,1) with 0.1 % of the elements (seeded
     positions) multiplied by 100; weight bf16 [4096, 4096] ~ N(0, 0.02); grad_output bf16
     [2048, 4096] ~ N(0, 1e-3).  CPU generators, so every machine with the same torch
     build produces the same bits (the fixture stores digests to detect drift)."""

@@ -1,13 +1,13 @@
 """Generates the golden fixtures in this directory by running the REFERENCE library
 (pytorch-labs/float8_experimental, imported from a checkout) on CPU with emulate=True.
 
-    python tests/golden/make_golden.py [/path/to/float8_experimental/checkout]
+    python tests/golden/make_golden.py /path/to/float8_experimental/checkout
 
 The fixtures pin the oracle (`oracle/f8_oracle.py`) and, through it and directly, the
 CUDA kernels.  They are small `.npz` files; bf16/fp16 tensors are stored as uint16 bit
 patterns, fp8 tensors as uint8.  Inputs are stored with the outputs, so the tests never
 depend on a random-number generator reproducing them.  The one exception is the
-BASELINE "config 1" case, whose inputs (16-32 MB each) are regenerated from fixed
+4096x4096-layer / 2048-token case, whose inputs (16-32 MB each) are regenerated from fixed
 torch seeds; its fixture stores SHA-256 digests of inputs and outputs plus a few
 sampled output rows.
 """
@@ -20,7 +20,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/float8_experimental/checkout")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
@@ -210,7 +212,7 @@ def gen_sync():
 
 
 def gen_config1():
-    """BASELINE config 1: Float8Linear(4096, 4096), M = 2048, dynamic, emulate."""
+    """Float8Linear(4096, 4096), M = 2048 tokens with outliers, dynamic scaling, emulate."""
     x, w, go = config1_inputs()
     rec = run_linear(x, w, go, Float8LinearConfig(emulate=True))[0]
     cfg = LinearMMConfig()

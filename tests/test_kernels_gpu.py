@@ -248,7 +248,7 @@ def test_gemm_output_types_and_bias(out_dtype, gemm_mode):
 
 
 def test_gemm_full_size_linearity(gemm_mode):
-    """At a BASELINE shape the oracle is too slow; check size-independent properties:
+    """At a full LLaMa-2-70B shape the oracle is too slow; check size-independent properties:
     agreement with an fp32 GEMM of the dequantised operands on sampled rows, and
     out(2a, b) == 2 out(a, b) exactly (powers of two commute with every rounding)."""
     m, n, k = 16384, 8192, 8192
@@ -265,7 +265,7 @@ def test_gemm_full_size_linearity(gemm_mode):
 
 
 def test_cast_full_size_properties():
-    """BASELINE-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
+    """Full-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
     size-independent properties: amax equals max|x|; the transposed copy is the transpose;
     every decoded value is within half an fp8 step of x*scale; casting the dequantised
     tensor again with the same scale returns the same bytes (idempotence)."""

@@ -83,7 +83,7 @@ def test_small_linear_delayed_three_iterations(golden_dir):
 
 
 def test_config1_bit_exact_casts_and_gemm_tolerance(golden_dir):
-    """BASELINE config 1: M=2048, K=N=4096, dynamic scaling, outliers in x."""
+    """The small reference configuration: M=2048, K=N=4096, dynamic scaling, outliers in x."""
     from golden_inputs import config1_inputs, sha256
 
     g = np.load(os.path.join(golden_dir, "config1.npz"))
