@@ -220,7 +220,7 @@ def check_gemm(out, ref):
 
 
 @pytest.mark.parametrize("mnk", [(128, 256, 128), (256, 512, 1024), (200, 264, 144), (1, 8, 16), (130, 40, 4096),
-                                 (640, 1024, 2064), (300, 520, 272)])
+                                 (640, 1024, 2064), (300, 520, 272), (130, 20, 64), (257, 72, 48)])
 @pytest.mark.parametrize("a_kind", [O.E4M3, O.E5M2])
 def test_gemm_against_oracle(mnk, a_kind, gemm_mode):
     m, n, k = mnk
