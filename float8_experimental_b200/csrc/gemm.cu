@@ -492,6 +492,258 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 }
 
 // ===========================================================================
+// Wide one-CTA variant: one CTA per 256x256 output tile, no cluster.  Each k-step issues
+// two M128 N256 K32 MMAs that share the B operand in this CTA's own shared memory; the
+// two 128-row halves accumulate in TMEM columns 0..255 and 256..511 (all of TMEM, so the
+// accumulator is not double buffered: the epilogue of a tile is exposed, but it is split
+// over two groups of four warps, one per half).  Per flop this moves as many bytes from
+// L2 as the two-CTA kernel and none between SMs.
+// ===========================================================================
+namespace wide {
+
+constexpr int WBM = 256;
+constexpr int WBN = 256;
+constexpr int WSTAGES = 3;
+constexpr int WA_BYTES = WBM * BK;  // 32 KB: rows 0..127 then 128..255
+constexpr int WB_BYTES = WBN * BK;  // 32 KB
+constexpr int WSTAGE_BYTES = WA_BYTES + WB_BYTES;
+constexpr int WTHREADS = 320;  // TMA warp, MMA warp, 2 x 4 epilogue warps
+
+struct __align__(8) WideBarriers {
+  uint64_t full[WSTAGES];
+  uint64_t empty[WSTAGES];
+  uint64_t tmem_full;
+  uint64_t tmem_empty;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+// 3 x 64 KB stages + 8 warps x 1 box x 4 KB would fit two boxes only with 2 stages; one box
+// per warp is enough here because a warp's stores are waited for before the box is reused.
+constexpr int WSMEM_BYTES = WSTAGES * WSTAGE_BYTES + 8 * EPI_BOX_BYTES + 1024 + (int)sizeof(WideBarriers);
+
+__device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideBarriers* bars, uint32_t who,
+                                          uint32_t backoff_ns = 0) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns != 0u) __nanosleep(backoff_ns);
+    if ((it & 63u) == 63u) {
+      if (bars->abort_flag != 0u) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
+    }
+  }
+  bars->abort_flag = 1u;
+  atomicOr(&g_device_error, who | 0x200u);
+  return false;
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_wide(int a_kind, int b_kind) {
+  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(WBN >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
+}
+
+// Like drain_accumulator, with ONE staging box per warp (the previous store of this warp
+// has to finish reading the box before it is refilled).
+template <typename OutT>
+__device__ __forceinline__ void drain_accumulator_1box(const EpilogueArgs<OutT>& e, uint32_t taddr, int row0, int col0,
+                                                       int ncol_total, uint32_t& boxes) {
+  constexpr int COLS_PER_BOX = 128 / (int)sizeof(OutT);
+  constexpr int CHUNKS_PER_BOX = COLS_PER_BOX / 32;
+  const int lane = threadIdx.x & 31;
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c = 0; c < ncol_total / 32; ++c) {
+    uint32_t r[32];
+    tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+    tc_wait_ld();
+    const int col = col0 + c * 32;
+    int ncols = e.n - col;
+    if (ncols > 32) ncols = 32;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * e.inv;
+    if (e.bias != nullptr && ncols > 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) v[i] += static_cast<float>(e.bias[col + i]);
+    }
+    if (!e.use_tma) {
+      if (row < e.m && ncols > 0) store_chunk<OutT>(e.out + (int64_t)row * e.ldo + col, v, ncols, e.out_vec_ok != 0);
+      continue;
+    }
+    const int sub = c % CHUNKS_PER_BOX;
+    if (col - sub * 32 >= e.n || row0 >= e.m) continue;
+    uint8_t* box = e.staging;
+    if (sub == 0 && boxes >= 1u) {
+      if (lane == 0) bulk_wait_read<0>();
+      __syncwarp();
+    }
+    uint8_t* rowp = box + lane * 128;
+    if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          OutT lo = static_cast<OutT>(v[q * 8 + 2 * h]), hi = static_cast<OutT>(v[q * 8 + 2 * h + 1]);
+          w[h] = (uint32_t)(*reinterpret_cast<unsigned short*>(&lo)) |
+                 ((uint32_t)(*reinterpret_cast<unsigned short*>(&hi)) << 16);
+        }
+        const int j = sub * 4 + q;
+        *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+            make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      }
+    }
+    if (sub == CHUNKS_PER_BOX - 1) {
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (e.store_evict_first) tma_store_2d_hint(e.tma_out, box, col - sub * 32, row0, l2_policy(1));
+        else tma_store_2d(e.tma_out, box, col - sub * 32, row0);
+        bulk_commit();
+      }
+      ++boxes;
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(WTHREADS, 1)
+gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                     const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
+                     const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
+                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = tiles + WSTAGES * WSTAGE_BYTES;
+  WideBarriers* bars = reinterpret_cast<WideBarriers*>(staging + 8 * EPI_BOX_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (m + WBM - 1) / WBM, tiles_n = (n + WBN - 1) / WBN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+  const int num_kb = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WSTAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->tmem_full, 1);
+    mbar_init(&bars->tmem_empty, 8);
+    bars->abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      const uint64_t pol = l2_policy(0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wide_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * WSTAGE_BYTES;
+          mbar_expect_tx(&bars->full[stage], WSTAGE_BYTES);
+          tma_load_2d_hint(sa, &tma_a, kb * BK, tc.m * WBM, &bars->full[stage], pol);               // 256 rows
+          tma_load_2d_hint(sa + WA_BYTES, &tma_b, kb * BK, tc.n * WBN, &bars->full[stage], pol);    // 256 rows
+          if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+        if (!wide_wait(&bars->tmem_empty, (uint32_t)(local & 1) ^ 1u, bars, 2u)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wide_wait(&bars->full[stage], phase, bars, 4u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * WSTAGE_BYTES);
+          const uint64_t da0 = make_smem_desc(a_addr), da1 = make_smem_desc(a_addr + 128 * BK);
+          const uint64_t db = make_smem_desc(a_addr + WA_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t off = (uint64_t)(kk * (UMMA_K >> 4));
+            const uint32_t accum = (kb | kk) != 0 ? 1u : 0u;
+            tc_mma_f8(tmem_base, da0 + off, db + off, idesc, accum);
+            tc_mma_f8(tmem_base + 256u, da1 + off, db + off, idesc, accum);
+          }
+          tc_commit(&bars->empty[stage]);
+          if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(&bars->tmem_full);
+      }
+    }
+  } else {
+    // warps 2..5 drain rows 0..127 (TMEM columns 0..255), warps 6..9 rows 128..255 (columns 256..511)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    float inv = 0.f;
+    {
+      const float sa = __ldg(scale_a), sb = __ldg(scale_b);
+      inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
+    }
+    const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
+                                staging + (warp - 2) * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
+    uint32_t boxes = 0;
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
+      int got = 1;
+      if (lane == 0) got = wide_wait(&bars->tmem_full, (uint32_t)(local & 1), bars, 8u, 256u) ? 1 : 0;
+      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
+      drain_accumulator_1box<OutT>(ea, taddr, tc.m * WBM + half * 128 + quarter * 32, tc.n * WBN, WBN, boxes);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty);
+    }
+    if (use_tma_store && lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace wide
+
+// ===========================================================================
 // Two-CTA variant: a cluster of two CTAs (two SMs) works on one 256x256 output tile
 // with tcgen05.mma.cta_group::2 (instruction shape M256 N256 K32).  CTA r of the pair
 // loads rows [128r, 128r+128) of the A tile and rows [128r, 128r+128) of the B tile, so
@@ -885,13 +1137,43 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
                          choose_raster(m, n, k, pair::PBM, pair::PBN)));
 }
 
-// 0 = one CTA per tile (128x256), 1 = CTA pairs (256x256, cta_group::2).  The environment
-// variable F8B200_GEMM_MODE ("1cta" / "2cta") overrides the default; it is read at every
-// call so that tests can exercise both kernels in one process.
-static int gemm_mode() {
+template <typename OutT>
+static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
+                       const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
+                       uint32_t idesc, int vec_ok, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(wide::gemm_fp8_wide_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    wide::WSMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
+  const int64_t tiles = (int64_t)((m + wide::WBM - 1) / wide::WBM) * ((n + wide::WBN - 1) / wide::WBN);
+  int grid = sm_count();
+  if (tiles < grid) grid = (int)tiles;
+  wide::gemm_fp8_wide_kernel<OutT><<<grid, wide::WTHREADS, wide::WSMEM_BYTES, st>>>(
+      ma, mb, mo, sa, sb, static_cast<const OutT*>(bias), static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
+      use_tma, choose_raster(m, n, k, wide::WBM, wide::WBN));
+  return check_launch();
+}
+
+// Kernel choice: 0 = one CTA per 128x256 tile, 1 = CTA pairs (256x256, cta_group::2), 2 = one CTA per 256x256 tile.
+// The pair kernel hides its epilogue behind the next tile's MMAs (two accumulators in tensor memory) but its MMAs
+// read half of B from the peer's shared memory; the wide kernel reads only its own shared memory but drains its
+// single 256x256 accumulator with the tensor pipe idle.  That drain is a fixed cost per tile, so the wide kernel
+// wins once the K loop is long enough to amortise it: measured under sustained load the two tie at K = 16384, the
+// pair kernel is 4-6 % faster at K = 8192 and the wide kernel 3-8 % faster at K >= 28672.
+// F8B200_GEMM_MODE ("1cta" / "2cta" / "wide") forces one kernel and F8B200_GEMM_WIDE_K moves the threshold; both are
+// read at every call so that tests can exercise every kernel in one process.
+static int gemm_mode(int64_t k) {
   const char* e = getenv("F8B200_GEMM_MODE");
   if (e != nullptr && e[0] == '1') return 0;
-  return 1;
+  if (e != nullptr && e[0] == '2') return 1;
+  if (e != nullptr && e[0] == 'w') return 2;
+  int64_t wide_k = 16384;
+  const char* t = getenv("F8B200_GEMM_WIDE_K");
+  if (t != nullptr && t[0] != 0) wide_k = atoll(t);
+  return k >= wide_k ? 2 : 1;
 }
 
 }  // namespace gemm
@@ -935,7 +1217,23 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
   } else {
     memset(&mo, 0, sizeof(mo));
   }
-  if (gemm::gemm_mode() == 1) {
+  const int mode = gemm::gemm_mode(k);
+  if (mode == 2) {
+    rc = gemm::encode_operand_map(&ma, a, m, k, lda, 256);
+    if (rc != F8B200_OK) return rc;
+    rc = gemm::encode_operand_map(&mb, b, n, k, ldb, 256);
+    if (rc != F8B200_OK) return rc;
+    const uint32_t idw = gemm::wide::make_idesc_wide(a_kind, b_kind);
+    switch (out_dtype) {
+      case F8B200_BF16:
+        return gemm::launch_wide<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+      case F8B200_FP16:
+        return gemm::launch_wide<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+      default:
+        return gemm::launch_wide<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+    }
+  }
+  if (mode == 1) {
     // each CTA of a pair fetches 128-row boxes of both operands
     rc = gemm::encode_operand_map(&ma, a, m, k, lda, 128);
     if (rc != F8B200_OK) return rc;

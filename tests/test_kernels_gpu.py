@@ -191,10 +191,11 @@ def test_transpose_u8():
 
 
 # ---------------------------------------------------------------------------
-@pytest.fixture(params=["2cta", "1cta", "2cta-direct", "1cta-direct"])
+@pytest.fixture(params=["2cta", "1cta", "wide", "2cta-direct", "1cta-direct", "wide-direct"])
 def gemm_mode(request, monkeypatch):
-    """Both GEMM kernels (CTA pairs with cta_group::2, the default, and one CTA per tile),
-    each with the TMA-store epilogue and with the per-thread store epilogue."""
+    """The three GEMM kernels (CTA pairs with cta_group::2, the default; one CTA per 128x256
+    tile; one CTA per 256x256 tile), each with the TMA-store epilogue and with the per-thread
+    store epilogue."""
     mode, _, store = request.param.partition("-")
     monkeypatch.setenv("F8B200_GEMM_MODE", mode)
     monkeypatch.setenv("F8B200_GEMM_STORE", store or "tma")
