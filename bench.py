@@ -443,9 +443,12 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (fp8 issues at twice the bf16 rate)",
             "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
             "launches": gemm_calls,
-            # dram__bytes_read + dram__bytes_write of one launch (wo forward, 16384x8192x8192) from the
-            # ncu capture summarised in profiles/gemm_fp8_pair_kernel_wo_16384x8192x8192.md
-            "traffic": 0.467e9 + 0.251e9, "traffic_algorithmic": 201.3e6 + 268.4e6,
+            # dram__bytes_read + dram__bytes_write per launch, mean of the three GEMMs of the wo layer (fwd and dgrad
+            # 16384x8192x8192 on the pair kernel, wgrad 8192x8192x16384 on the wide kernel), from the ncu captures
+            # summarised in profiles/gemm_fp8_pair_kernel_wo_16384x8192x8192.md and
+            # profiles/gemm_fp8_wide_kernel_wo_w2_w13.md
+            "traffic": (0.470e9 + 0.251e9 + 0.458e9 + 0.251e9 + 0.880e9 + 0.120e9) / 3,
+            "traffic_algorithmic": (2 * (201.3e6 + 268.4e6) + (268.4e6 + 134.2e6)) / 3,
         },
         "roofline_cast": {
             "kernel": "amax_flat_kernel + cast_tile8_kernel (dynamic amax+cast with transposed copy)", "bound": "hbm",
