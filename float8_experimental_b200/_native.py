@@ -33,6 +33,7 @@ EXPORTS = (
     "f8b200_transpose_u8",
     "f8b200_delayed_sync",
     "f8b200_gemm_fp8",
+    "f8b200_gemm_fp8_ws",
     "f8b200_read_device_error",
 )
 
@@ -69,6 +70,8 @@ def load() -> ctypes.CDLL:
     lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
     lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
+    lib.f8b200_gemm_fp8_ws.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp,
+                                       i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
         fn = getattr(lib, name)
@@ -243,17 +246,45 @@ def delayed_sync(amax_t: torch.Tensor, hist: torch.Tensor, n_e4m3: int, orig_dty
         )
 
 
+GEMM_WORKSPACE_BYTES = 256  # F8B200_GEMM_WORKSPACE_BYTES in include/f8b200.h
+_gemm_workspaces: dict = {}
+
+
+def _gemm_workspace(device: torch.device, stream: int) -> torch.Tensor:
+    """Scheduling workspace of the GEMMs issued on `stream` of `device`: one small buffer per
+    stream, kept for the life of the process, because GEMMs that may overlap must not share one."""
+    key = (device.index, stream)
+    ws = _gemm_workspaces.get(key)
+    if ws is None:
+        ws = torch.empty(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _gemm_workspaces[key] = ws
+    return ws
+
+
 def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor, scale_b: torch.Tensor,
              bias: Optional[torch.Tensor], out: torch.Tensor, ldo: int, m: int, n: int, k: int,
              use_fast_accum: bool) -> None:
+    """`f8b200_gemm_fp8_ws` with this stream's workspace (dynamic tile scheduling);
+    F8B200_GEMM_WS=0 in the environment selects the workspace-free `f8b200_gemm_fp8`."""
     _require_cuda(a, b, scale_a, scale_b, bias, out)
+    stream = _stream(a)
     with _Launch("gemm", a.device):
-        _check(
-            load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
-                                   scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
-                                   out.data_ptr(), ldo, m, n, k, int(use_fast_accum), _stream(a)),
-            "f8b200_gemm_fp8",
-        )
+        if os.environ.get("F8B200_GEMM_WS", "1") == "0":
+            _check(
+                load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
+                                       scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
+                                       out.data_ptr(), ldo, m, n, k, int(use_fast_accum), stream),
+                "f8b200_gemm_fp8",
+            )
+        else:
+            ws = _gemm_workspace(a.device, stream)
+            _check(
+                load().f8b200_gemm_fp8_ws(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
+                                          scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
+                                          out.data_ptr(), ldo, m, n, k, int(use_fast_accum), ws.data_ptr(),
+                                          ws.numel(), stream),
+                "f8b200_gemm_fp8_ws",
+            )
 
 
 def read_device_error() -> int:

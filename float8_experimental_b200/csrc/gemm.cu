@@ -202,6 +202,26 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t idx, int tiles_m, int ti
   return c;
 }
 
+// ---- dynamic tile scheduling ---------------------------------------------------
+// With a scheduling word (`sched`, one uint32 in global memory that the host zeroes before the
+// launch) the persistent CTAs do not walk a fixed stride of tiles: a CTA (or CTA pair) starts on the
+// tile of its own index and then claims tiles num_units + atomicAdd(sched, 1).  A CTA that gets its SM
+// late, because a kernel on another stream (a collective) held it, then simply does fewer tiles, where
+// the fixed stride would make the whole GEMM wait for it.  The TMA producer thread claims the next
+// tile a few k-blocks before the end of the current one and publishes it to the other roles through
+// a small ring in shared memory: ring.tile[j % RING] holds the (j+1)-th tile of this CTA, or -1 when
+// there is none, and ring.full[j % RING] completes once per publication.  The ring needs no "empty"
+// barrier: when the producer publishes entry j + RING it has issued the last loads of a tile whose
+// predecessor RING - 1 tiles back... more precisely the MMA thread has consumed a k-block at most
+// `stages` tiles back, it started that tile only after the epilogue had drained the tile one or two
+// before it, and every role reads entry j before it works on that tile; with at most 6 stages and
+// 2 accumulators every reader is past entry j + 7 by then, so RING = 16 cannot be lapped.
+constexpr int RING = 16;
+struct TileRing {
+  uint64_t full[RING];
+  int32_t tile[RING];
+};
+
 template <typename OutT>
 __device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], int ncols, bool vec_ok) {
   if constexpr (sizeof(OutT) == 2) {
@@ -514,6 +534,7 @@ struct __align__(8) WideBarriers {
   uint64_t empty[WSTAGES];
   uint64_t tmem_full;
   uint64_t tmem_empty;
+  TileRing ring;
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -619,7 +640,8 @@ __global__ void __launch_bounds__(WTHREADS, 1)
 gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
-                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster) {
+                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster,
+                     uint32_t* sched) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = tiles + WSTAGES * WSTAGE_BYTES;
@@ -637,6 +659,7 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     }
     mbar_init(&bars->tmem_full, 1);
     mbar_init(&bars->tmem_empty, 8);
+    for (int r = 0; r < RING; ++r) mbar_init(&bars->ring.full[r], 1);
     bars->abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -659,9 +682,14 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      const int claim_kb = num_kb > 4 ? num_kb - 4 : 0;
+      uint32_t published = 0;
+      int64_t t = blockIdx.x;
+      while (ok && t < num_tiles) {
         const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
+        int64_t next = t + gridDim.x;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (sched != nullptr && kb == claim_kb) next = (int64_t)gridDim.x + (int64_t)atomicAdd(sched, 1u);
           if (!wide_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * WSTAGE_BYTES;
           mbar_expect_tx(&bars->full[stage], WSTAGE_BYTES);
@@ -669,6 +697,14 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           tma_load_2d_hint(sa + WA_BYTES, &tma_b, kb * BK, tc.n * WBN, &bars->full[stage], pol);    // 256 rows
           if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
         }
+        if (!ok) break;
+        if (sched != nullptr) {
+          const uint32_t slot = published & (RING - 1);
+          bars->ring.tile[slot] = next < num_tiles ? (int32_t)next : -1;
+          mbar_arrive(&bars->ring.full[slot]);  // release: the entry is visible to whoever sees the phase
+          ++published;
+        }
+        t = next;
       }
       if (!ok) {
         const long long t0 = clock64();
@@ -681,7 +717,8 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       int64_t local = 0;
-      for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+      int64_t t = blockIdx.x;
+      for (; ok && t < num_tiles; ++local) {
         if (!wide_wait(&bars->tmem_empty, (uint32_t)(local & 1) ^ 1u, bars, 2u)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -700,7 +737,16 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           tc_commit(&bars->empty[stage]);
           if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(&bars->tmem_full);
+        if (!ok) break;
+        tc_commit(&bars->tmem_full);
+        if (sched != nullptr) {
+          const uint32_t slot = (uint32_t)local & (RING - 1);
+          if (!wide_wait(&bars->ring.full[slot], (uint32_t)(local >> 4) & 1u, bars, 16u)) { ok = false; break; }
+          const int32_t v = *reinterpret_cast<volatile int32_t*>(&bars->ring.tile[slot]);
+          t = v < 0 ? num_tiles : (int64_t)v;
+        } else {
+          t += gridDim.x;
+        }
       }
     }
   } else {
@@ -717,7 +763,8 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
-    for (int64_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++local) {
+    int64_t t = blockIdx.x;
+    for (; ok && t < num_tiles; ++local) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
       int got = 1;
       if (lane == 0) got = wide_wait(&bars->tmem_full, (uint32_t)(local & 1), bars, 8u, 256u) ? 1 : 0;
@@ -728,6 +775,19 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty);
+      if (sched != nullptr) {
+        int v = -2;  // -2: gave up waiting
+        if (lane == 0) {
+          const uint32_t slot = (uint32_t)local & (RING - 1);
+          if (wide_wait(&bars->ring.full[slot], (uint32_t)(local >> 4) & 1u, bars, 32u, 64u))
+            v = *reinterpret_cast<volatile int32_t*>(&bars->ring.tile[slot]);
+        }
+        v = __shfl_sync(0xFFFFFFFFu, v, 0);
+        if (v == -2) { ok = false; break; }
+        t = v < 0 ? num_tiles : (int64_t)v;
+      } else {
+        t += gridDim.x;
+      }
     }
     if (use_tma_store && lane == 0) bulk_wait_all();
   }
@@ -770,6 +830,7 @@ struct __align__(8) PairBarriers {
   uint64_t empty[PSTAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  TileRing ring;  // written in both CTAs by the leader's producer thread
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -791,6 +852,22 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Arrive that publishes this thread's earlier stores (also those to the partner's shared memory) to a
+// waiter in the partner CTA.
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -828,12 +905,14 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind) {
 }
 
 // Bounded wait that also raises the partner's abort flag when it gives up.
+template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBarriers* bars, uint32_t peer_rank,
                                           uint32_t who, uint32_t backoff_ns = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
+  auto probe = [&]() { return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  if (probe()) return true;
   const long long t0 = clock64();
   for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (probe()) return true;
     if (backoff_ns != 0u) __nanosleep(backoff_ns);
     if ((it & 63u) == 63u) {
       if (bars->abort_flag != 0u) return false;
@@ -846,13 +925,21 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBa
   return false;
 }
 
+// Entry `j` of this CTA's tile ring (the (j+1)-th tile of the pair): -1 = no more tiles, -2 = gave up.
+__device__ __forceinline__ int32_t pair_ring_read(PairBarriers* bars, uint32_t j, uint32_t peer_rank, uint32_t who,
+                                                  uint32_t backoff_ns) {
+  const uint32_t slot = j & (RING - 1);
+  if (!pair_wait<true>(&bars->ring.full[slot], (j >> 4) & 1u, bars, peer_rank, who, backoff_ns)) return -2;
+  return *reinterpret_cast<volatile int32_t*>(&bars->ring.tile[slot]);
+}
 
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
-                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster) {
+                     int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster,
+                     uint32_t* sched) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = tiles + PSTAGES * PSTAGE_BYTES;
@@ -876,6 +963,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], 8);
     }
+    for (int r = 0; r < RING; ++r) mbar_init(&bars->ring.full[r], 1);
     bars->abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -905,11 +993,16 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters) {
+      const int claim_kb = num_kb > 4 ? num_kb - 4 : 0;
+      uint32_t entry = 0;  // ring entries published (leader) or read (partner) so far
+      int64_t t = cluster_id;
+      while (ok && t < num_tiles) {
         const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
         const int row_a = tc.m * PBM + (int)rank * 128;
         const int row_b = tc.n * PBN + (int)rank * 128;
+        int64_t next = t + num_clusters;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (sched != nullptr && leader && kb == claim_kb) next = num_clusters + (int64_t)atomicAdd(sched, 1u);
           if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * PSTAGE_BYTES;
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
@@ -918,6 +1011,23 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           tma_load_2d_pair(sa + PA_BYTES, &tma_b, kb * BK, row_b, full_in_leader, pol_b);
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
+        if (!ok) break;
+        if (sched != nullptr) {
+          if (leader) {
+            const uint32_t slot = entry & (RING - 1);
+            const int32_t v = next < num_tiles ? (int32_t)next : -1;
+            bars->ring.tile[slot] = v;
+            mbar_arrive(&bars->ring.full[slot]);
+            st_cluster_u32(mapa_u32(smem_u32(&bars->ring.tile[slot]), 1u), (uint32_t)v);
+            mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->ring.full[slot]), 1u));
+          } else {
+            const int32_t v = pair_ring_read(bars, entry, peer, 64u, 32u);
+            if (v == -2) { ok = false; break; }
+            next = v < 0 ? num_tiles : (int64_t)v;
+          }
+          ++entry;
+        }
+        t = next;
       }
       // tail: every release the leader multicast to this CTA's empty barriers has landed
       for (int s = 0; ok && s < PSTAGES; ++s) {
@@ -936,7 +1046,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       int64_t local = 0;
-      for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
+      int64_t t = cluster_id;
+      for (; ok && t < num_tiles; ++local) {
         const int acc = (int)(local & 1);
         const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
         if (!pair_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, bars, peer, 2u)) { ok = false; break; }
@@ -955,7 +1066,15 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           tc_commit_pair(&bars->empty[stage]);
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit_pair(&bars->tmem_full[acc]);
+        if (!ok) break;
+        tc_commit_pair(&bars->tmem_full[acc]);
+        if (sched != nullptr) {
+          const int32_t v = pair_ring_read(bars, (uint32_t)local, peer, 16u, 0u);
+          if (v == -2) { ok = false; break; }
+          t = v < 0 ? num_tiles : (int64_t)v;
+        } else {
+          t += num_clusters;
+        }
       }
     }
   } else {
@@ -971,7 +1090,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
     uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
-    for (int64_t t = cluster_id; ok && t < num_tiles; t += num_clusters, ++local) {
+    int64_t t = cluster_id;
+    for (; ok && t < num_tiles; ++local) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
@@ -984,6 +1104,15 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0u));
+      if (sched != nullptr) {
+        int v = 0;
+        if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, 64u);
+        v = __shfl_sync(0xFFFFFFFFu, v, 0);
+        if (v == -2) { ok = false; break; }
+        t = v < 0 ? num_tiles : (int64_t)v;
+      } else {
+        t += num_clusters;
+      }
     }
     if (use_tma_store && lane == 0) bulk_wait_all();
   }
@@ -1079,6 +1208,30 @@ static int choose_raster(int64_t m, int64_t n, int64_t k, int tile_m, int tile_n
   return (cost_n < cost_m ? (int)(gn | (1 << 16)) : (int)gm) | (hints << 20);
 }
 
+// Dynamic tile scheduling is used when the caller gave a scheduling word, there is more than one
+// tile per CTA (or pair) to hand out, and tile indices fit the ring's int32 entries.
+// F8B200_GEMM_SCHED=static switches it off (read at every call).
+static uint32_t* usable_sched(uint32_t* sched, int64_t tiles, int units) {
+  if (sched == nullptr || tiles <= units || tiles + units >= 0x7FFFFFFFLL) return nullptr;
+  const char* e = getenv("F8B200_GEMM_SCHED");
+  if (e != nullptr && e[0] == 's') return nullptr;
+  return sched;
+}
+
+// SMs left free for kernels that run beside the GEMM on other streams (collectives): the persistent
+// GEMMs otherwise hold every SM until they end, which serialises a concurrent all-gather or
+// reduce-scatter behind them.  F8B200_GEMM_SM_MARGIN, read at every call; default 0.
+static int sm_margin() {
+  const char* e = getenv("F8B200_GEMM_SM_MARGIN");
+  if (e == nullptr || e[0] == 0) return 0;
+  const int v = atoi(e);
+  return v < 0 ? 0 : v;
+}
+static int persistent_ctas() {
+  const int g = sm_count() - sm_margin();
+  return g < 2 ? 2 : g;
+}
+
 template <typename OutT>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma, const float* sa,
                   const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k, uint32_t idesc,
@@ -1090,7 +1243,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   });
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   const int64_t tiles = (int64_t)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  int grid = sm_count();
+  int grid = persistent_ctas();
   if (tiles < grid) grid = (int)tiles;
   gemm_fp8_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, mo, sa, sb, static_cast<const OutT*>(bias),
                                                                 static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
@@ -1101,7 +1254,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
 template <typename OutT>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
-                       uint32_t idesc, int vec_ok, cudaStream_t st) {
+                       uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int max_clusters = 0;
@@ -1128,19 +1281,25 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
   const int64_t tiles = (int64_t)((m + pair::PBM - 1) / pair::PBM) * ((n + pair::PBN - 1) / pair::PBN);
   int clusters = max_clusters;
+  if (persistent_ctas() / 2 < clusters) clusters = persistent_ctas() / 2;
   if (tiles < clusters) clusters = (int)tiles;
   cfg.gridDim = dim3(2 * clusters);
   const OutT* bias_t = static_cast<const OutT*>(bias);
   OutT* out_t = static_cast<OutT*>(out);
+  sched = usable_sched(sched, tiles, clusters);
+  if (sched != nullptr) {
+    const cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(uint32_t), st);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
-                         choose_raster(m, n, k, pair::PBM, pair::PBN)));
+                         choose_raster(m, n, k, pair::PBM, pair::PBN), sched));
 }
 
 template <typename OutT>
 static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
-                       uint32_t idesc, int vec_ok, cudaStream_t st) {
+                       uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -1149,11 +1308,16 @@ static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   });
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   const int64_t tiles = (int64_t)((m + wide::WBM - 1) / wide::WBM) * ((n + wide::WBN - 1) / wide::WBN);
-  int grid = sm_count();
+  int grid = persistent_ctas();
   if (tiles < grid) grid = (int)tiles;
+  sched = usable_sched(sched, tiles, grid);
+  if (sched != nullptr) {
+    const cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(uint32_t), st);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
   wide::gemm_fp8_wide_kernel<OutT><<<grid, wide::WTHREADS, wide::WSMEM_BYTES, st>>>(
       ma, mb, mo, sa, sb, static_cast<const OutT*>(bias), static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
-      use_tma, choose_raster(m, n, k, wide::WBM, wide::WBN));
+      use_tma, choose_raster(m, n, k, wide::WBM, wide::WBN), sched);
   return check_launch();
 }
 
@@ -1181,10 +1345,9 @@ static int gemm_mode(int64_t k) {
 
 using namespace f8b200;
 
-extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
-                               const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
-                               int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream) {
-  (void)use_fast_accum;  // tcgen05 accumulates in fp32 tensor memory either way
+static int gemm_fp8_impl(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                         const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
+                         int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* sched, void* stream) {
   if (m < 0 || n < 0 || k < 0) return F8B200_ERR_BAD_ARG;
   if (a_kind < 0 || a_kind > 1 || b_kind < 0 || b_kind > 1 || out_dtype < 0 || out_dtype > 2) return F8B200_ERR_BAD_ARG;
   if (m == 0 || n == 0) return F8B200_OK;
@@ -1226,11 +1389,11 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
     const uint32_t idw = gemm::wide::make_idesc_wide(a_kind, b_kind);
     switch (out_dtype) {
       case F8B200_BF16:
-        return gemm::launch_wide<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+        return gemm::launch_wide<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
       case F8B200_FP16:
-        return gemm::launch_wide<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+        return gemm::launch_wide<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
       default:
-        return gemm::launch_wide<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, st);
+        return gemm::launch_wide<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
     }
   }
   if (mode == 1) {
@@ -1242,13 +1405,13 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
     const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind);
     switch (out_dtype) {
       case F8B200_BF16:
-        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
         break;
       case F8B200_FP16:
-        rc = gemm::launch_pair<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
         break;
       default:
-        rc = gemm::launch_pair<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, st);
+        rc = gemm::launch_pair<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
         break;
     }
     if (rc != F8B200_ERR_UNSUPPORTED) return rc;
@@ -1268,6 +1431,25 @@ extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const voi
     default:
       return gemm::launch<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
   }
+}
+
+extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                               const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
+                               int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream) {
+  (void)use_fast_accum;  // tcgen05 accumulates in fp32 tensor memory either way
+  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k, nullptr,
+                       stream);
+}
+
+extern "C" int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                                  const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
+                                  void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum,
+                                  void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)use_fast_accum;
+  if (workspace == nullptr || workspace_bytes < F8B200_GEMM_WORKSPACE_BYTES) return F8B200_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return F8B200_ERR_ALIGNMENT;
+  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k,
+                       static_cast<uint32_t*>(workspace), stream);
 }
 
 extern "C" int f8b200_read_device_error(uint32_t* flags_out) {

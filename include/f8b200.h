@@ -158,6 +158,29 @@ int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b
                     void* stream);
 
 /*
+ * f8b200_gemm_fp8 with a caller-owned workspace, which switches the persistent kernels from a
+ * fixed stride of output tiles per CTA to dynamic tile scheduling: CTAs claim tiles from a
+ * counter in the workspace, so that a CTA whose SM was held by a kernel of another stream (an
+ * all-gather or reduce-scatter running beside the GEMM) does fewer tiles instead of making the
+ * launch wait for its full share.  Results are bit-identical to f8b200_gemm_fp8 (each output
+ * tile is accumulated the same way whichever CTA computes it).
+ *
+ *   workspace        device memory, 16-byte aligned, at least F8B200_GEMM_WORKSPACE_BYTES.  The
+ *                    contents need no initialisation (the call zeroes what it uses with a
+ *                    memset on `stream`) and are undefined afterwards.  Two GEMMs that may run
+ *                    at the same time (different streams) must not share a workspace; GEMMs on
+ *                    one stream may.  Capturable in a CUDA graph (memset node + kernel node).
+ *
+ * Same reference call site as f8b200_gemm_fp8 (float8_experimental/float8_python_api.py:24-64;
+ * torch._scaled_mm there draws its workspace from cuBLASLt's own allocation).
+ */
+#define F8B200_GEMM_WORKSPACE_BYTES 256
+int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
+                       const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
+                       void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum,
+                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Reads and clears the device error word of the current device (synchronises the
  * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
  * last read; the result of that launch is undefined.  Test and debugging aid.

@@ -265,6 +265,25 @@ def test_gemm_full_size_linearity(gemm_mode):
     assert torch.equal(out2.float(), out.float() * 2)
 
 
+@pytest.mark.parametrize("mnk", [(4096, 8192, 512), (8192, 4096 + 48, 1024 + 16), (2048, 2048, 128)])
+def test_gemm_dynamic_schedule_matches_fixed_stride(mnk, gemm_mode, monkeypatch):
+    """With a workspace the persistent kernels claim tiles from a counter; without one every
+    CTA walks a fixed stride.  Each tile is accumulated the same way in both, so the outputs
+    are bit-identical, call after call (the counter is reset by every call)."""
+    m, n, k = mnk
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    sa, sb = torch.tensor(2.0, device="cuda"), torch.tensor(0.5, device="cuda")
+    monkeypatch.setenv("F8B200_GEMM_WS", "0")
+    fixed = gemm(a, b, sa, sb)
+    monkeypatch.setenv("F8B200_GEMM_WS", "1")
+    for _ in range(3):
+        assert torch.equal(gemm(a, b, sa, sb).view(torch.int16), fixed.view(torch.int16))
+    rows = torch.tensor([0, 255, 256, m - 1], device="cuda")
+    check_gemm(fixed[rows].float(), a[rows].float() @ b.float().t())
+
+
 def test_cast_full_size_properties():
     """Full-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
     size-independent properties: amax equals max|x|; the transposed copy is the transpose;
