@@ -34,6 +34,7 @@ EXPORTS = (
     "f8b200_delayed_sync",
     "f8b200_gemm_fp8",
     "f8b200_gemm_fp8_ws",
+    "f8b200_gemm_fp8_static_scratch",
     "f8b200_read_device_error",
 )
 
@@ -70,6 +71,7 @@ def load() -> ctypes.CDLL:
     lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
     lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
+    lib.f8b200_gemm_fp8_static_scratch.argtypes = lib.f8b200_gemm_fp8.argtypes
     lib.f8b200_gemm_fp8_ws.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp,
                                        i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
@@ -285,6 +287,22 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
                                           ws.numel(), stream),
                 "f8b200_gemm_fp8_ws",
             )
+
+
+def gemm_fp8_static_scratch(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor,
+                            scale_b: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, ldo: int, m: int,
+                            n: int, k: int, use_fast_accum: bool) -> None:
+    """`f8b200_gemm_fp8_static_scratch`: dynamic tile scheduling with the scheduling words in the
+    library's own static device array (at most 16 streams per device)."""
+    _require_cuda(a, b, scale_a, scale_b, bias, out)
+    with _Launch("gemm", a.device):
+        _check(
+            load().f8b200_gemm_fp8_static_scratch(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(),
+                                                  fp8_code(b.dtype), ldb, scale_a.data_ptr(), scale_b.data_ptr(),
+                                                  _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo, m, n, k,
+                                                  int(use_fast_accum), _stream(a)),
+            "f8b200_gemm_fp8_static_scratch",
+        )
 
 
 def read_device_error() -> int:

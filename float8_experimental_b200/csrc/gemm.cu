@@ -1452,6 +1452,63 @@ extern "C" int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const 
                        static_cast<uint32_t*>(workspace), stream);
 }
 
+// ---- scheduling words in static device memory ----------------------------------
+// f8b200_gemm_fp8_static_scratch needs no workspace from the caller: its scheduling words live in a
+// file-scope device array, one 256-byte slot per stream that has called it on this device.
+namespace {
+constexpr int kStaticSlots = F8B200_STATIC_SCRATCH_BYTES / F8B200_GEMM_WORKSPACE_BYTES;
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_scratch[F8B200_STATIC_SCRATCH_BYTES];
+
+struct StaticScratch {
+  std::once_flag once;
+  cudaError_t err = cudaSuccess;
+  unsigned char* base = nullptr;  // address of g_static_scratch on this device
+  std::mutex mu;
+  cudaStream_t owner[kStaticSlots];
+  int used = 0;
+};
+static StaticScratch g_static[kMaxDevices];
+}  // namespace
+
+extern "C" int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t lda, const void* b, int b_kind,
+                                              int64_t ldb, const float* scale_a, const float* scale_b,
+                                              const void* bias, int out_dtype, void* out, int64_t ldo, int64_t m,
+                                              int64_t n, int64_t k, int use_fast_accum, void* stream) {
+  (void)use_fast_accum;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevices) return F8B200_ERR_UNSUPPORTED;
+  StaticScratch& sc = g_static[dev];
+  // set-up, once per device: the symbol's address (this is the call that must not fall inside a
+  // stream capture)
+  std::call_once(sc.once, [&sc] {
+    void* p = nullptr;
+    sc.err = cudaGetSymbolAddress(&p, g_static_scratch);
+    sc.base = static_cast<unsigned char*>(p);
+  });
+  if (sc.err != cudaSuccess) return record_cuda_error(sc.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int slot = -1;
+  {
+    std::lock_guard<std::mutex> lock(sc.mu);
+    for (int i = 0; i < sc.used; ++i)
+      if (sc.owner[i] == st) slot = i;
+    if (slot < 0) {
+      // one more stream needs one more slot: beyond the array's size the request is refused
+      if ((int64_t)(sc.used + 1) * F8B200_GEMM_WORKSPACE_BYTES > (int64_t)F8B200_STATIC_SCRATCH_BYTES)
+        return F8B200_ERR_UNSUPPORTED;
+      slot = sc.used++;
+      sc.owner[slot] = st;
+    }
+  }
+  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k,
+                       reinterpret_cast<uint32_t*>(sc.base + (size_t)slot * F8B200_GEMM_WORKSPACE_BYTES), stream);
+}
+
 extern "C" int f8b200_read_device_error(uint32_t* flags_out) {
   if (flags_out == nullptr) return F8B200_ERR_BAD_ARG;
   int rc = f8b200_device_check();

@@ -181,6 +181,38 @@ int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const void* b, in
                        void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * f8b200_gemm_fp8_ws without the workspace argument: the scheduling words live in a file-scope
+ * `static __device__` array of F8B200_STATIC_SCRATCH_BYTES (4096) bytes inside the library, one
+ * F8B200_GEMM_WORKSPACE_BYTES slot per stream.  This entry point has NO counterpart in the
+ * reference (torch._scaled_mm takes its workspace from cuBLASLt); it exists for callers that
+ * cannot pass device memory of their own.  It allocates and frees nothing, on the host or the
+ * device, and returns the same bits as f8b200_gemm_fp8 / f8b200_gemm_fp8_ws.
+ *
+ *   set-up      The first call on each device looks the array up with cudaGetSymbolAddress and
+ *               keeps the address.  That call must happen outside any stream capture; make one
+ *               call per device before capturing a CUDA graph that contains this entry point.
+ *   size limit  A stream gets its slot at its first call and keeps it for the life of the
+ *               process (slots are not recycled when a stream is destroyed; a new stream that
+ *               happens to get the same handle reuses the old slot, which is safe).  The array
+ *               holds 16 slots: the call that would need a 17th stream on one device returns
+ *               F8B200_ERR_UNSUPPORTED and launches nothing.  Use f8b200_gemm_fp8_ws there.
+ *   sharing     The array is shared by every caller of this entry point in the process (all
+ *               host threads, all users of the library); the slot table is guarded by a mutex.
+ *               Calls on one stream are ordered by the stream and share that stream's slot.
+ *               What is NOT safe is one slot used by two launches that can run at the same
+ *               time: a captured graph holding this call that is replayed on another stream
+ *               while the capture stream issues further calls, or one such graph launched on
+ *               two streams at once.  Both launches would claim tiles from one counter and
+ *               each would skip the tiles the other claimed.  Give such work
+ *               f8b200_gemm_fp8_ws with a workspace of its own.
+ */
+#define F8B200_STATIC_SCRATCH_BYTES 4096
+int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t lda, const void* b, int b_kind,
+                                   int64_t ldb, const float* scale_a, const float* scale_b,
+                                   const void* bias, int out_dtype, void* out, int64_t ldo,
+                                   int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream);
+
+/*
  * Reads and clears the device error word of the current device (synchronises the
  * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
  * last read; the result of that launch is undefined.  Test and debugging aid.
