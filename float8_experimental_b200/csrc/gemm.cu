@@ -211,11 +211,12 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t idx, int tiles_m, int ti
 // tile a few k-blocks before the end of the current one and publishes it to the other roles through
 // a small ring in shared memory: ring.tile[j % RING] holds the (j+1)-th tile of this CTA, or -1 when
 // there is none, and ring.full[j % RING] completes once per publication.  The ring needs no "empty"
-// barrier: when the producer publishes entry j + RING it has issued the last loads of a tile whose
-// predecessor RING - 1 tiles back... more precisely the MMA thread has consumed a k-block at most
-// `stages` tiles back, it started that tile only after the epilogue had drained the tile one or two
-// before it, and every role reads entry j before it works on that tile; with at most 6 stages and
-// 2 accumulators every reader is past entry j + 7 by then, so RING = 16 cannot be lapped.
+// barrier, because the producer cannot lap its readers: it publishes entry j right after issuing the
+// last loads of its j-th tile, and it could issue those only after the MMA thread had consumed a
+// k-block at most `stages` (<= 6) k-blocks, hence at most 6 tiles, earlier.  The MMA thread starts a
+// tile only after the epilogue warps have drained the tile two (one, in the wide kernel) before it,
+// and every role reads entry i straight after its work on tile i.  So when entry j is written every
+// reader has read entry j - 9 or later, and RING = 16 entries are never overwritten unread.
 constexpr int RING = 16;
 struct TileRing {
   uint64_t full[RING];
