@@ -72,8 +72,8 @@ def load() -> ctypes.CDLL:
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
     lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
     lib.f8b200_gemm_fp8_static_scratch.argtypes = lib.f8b200_gemm_fp8.argtypes
-    lib.f8b200_gemm_fp8_ws.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp,
-                                       i64, vp]
+    lib.f8b200_gemm_fp8_ws.argtypes = [vp, i32, i32, i64, vp, i32, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64,
+                                       i32, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
         fn = getattr(lib, name)
@@ -265,13 +265,15 @@ def _gemm_workspace(device: torch.device, stream: int) -> torch.Tensor:
 
 def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor, scale_b: torch.Tensor,
              bias: Optional[torch.Tensor], out: torch.Tensor, ldo: int, m: int, n: int, k: int,
-             use_fast_accum: bool) -> None:
-    """`f8b200_gemm_fp8_ws` with this stream's workspace (dynamic tile scheduling);
-    F8B200_GEMM_WS=0 in the environment selects the workspace-free `f8b200_gemm_fp8`."""
+             use_fast_accum: bool, a_mn_major: bool = False, b_mn_major: bool = False) -> None:
+    """`f8b200_gemm_fp8_ws` with this stream's workspace (dynamic tile scheduling).  `a` is the
+    [m, k] operand stored K-contiguous, or with `a_mn_major` its transpose stored [k, m]; likewise
+    `b` ([n, k], or [k, n] with `b_mn_major`).  F8B200_GEMM_WS=0 in the environment selects the
+    workspace-free `f8b200_gemm_fp8` (K-major operands only)."""
     _require_cuda(a, b, scale_a, scale_b, bias, out)
     stream = _stream(a)
     with _Launch("gemm", a.device):
-        if os.environ.get("F8B200_GEMM_WS", "1") == "0":
+        if os.environ.get("F8B200_GEMM_WS", "1") == "0" and not (a_mn_major or b_mn_major):
             _check(
                 load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
                                        scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
@@ -281,10 +283,10 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
         else:
             ws = _gemm_workspace(a.device, stream)
             _check(
-                load().f8b200_gemm_fp8_ws(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
-                                          scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype),
-                                          out.data_ptr(), ldo, m, n, k, int(use_fast_accum), ws.data_ptr(),
-                                          ws.numel(), stream),
+                load().f8b200_gemm_fp8_ws(a.data_ptr(), fp8_code(a.dtype), int(a_mn_major), lda, b.data_ptr(),
+                                          fp8_code(b.dtype), int(b_mn_major), ldb, scale_a.data_ptr(),
+                                          scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo, m,
+                                          n, k, int(use_fast_accum), ws.data_ptr(), ws.numel(), stream),
                 "f8b200_gemm_fp8_ws",
             )
 

@@ -20,6 +20,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -167,6 +168,29 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
+}
+
+// The same for an MN-major operand tile: the TMA box is [K rows] x [128 bytes of M (or N)], so one
+// 128-byte row holds 128 consecutive M/N positions of one k and eight k rows make one 1024-byte
+// swizzle atom.  Stride byte offset = distance between groups of eight k rows (1024), leading byte
+// offset = distance between blocks of 128 M/N positions (`mn_block_bytes`, one box).  One MMA
+// (K = 32) spans four atoms; the next one starts 32 rows = 4096 bytes further on.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Operand layouts travel in bits 24 (A) and 25 (B) of the packed `raster` word: 0 = K-major
+// (storage [rows, K], K contiguous), 1 = MN-major (storage [K, rows], rows contiguous).
+constexpr int LAYOUT_A_MN_BIT = 24;
+constexpr int LAYOUT_B_MN_BIT = 25;
+// Encoded-address step between consecutive K = 32 MMAs inside one 128-wide k-block.
+__device__ __forceinline__ uint64_t desc_k_step(bool mn_major) {
+  return mn_major ? (uint64_t)((UMMA_K * 128) >> 4) : (uint64_t)(UMMA_K >> 4);
 }
 
 // Instruction descriptor for kind::f8f6f4: fp32 accumulate, A/B formats
@@ -561,9 +585,9 @@ __device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideBa
   return false;
 }
 
-__host__ __device__ constexpr uint32_t make_idesc_wide(int a_kind, int b_kind) {
-  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(WBN >> 3) << 17) |
-         ((uint32_t)(128 >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_wide(int a_kind, int b_kind, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)a_mn << 15) |
+         ((uint32_t)b_mn << 16) | ((uint32_t)(WBN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
 // Like drain_accumulator, with ONE staging box per warp (the previous store of this warp
@@ -652,6 +676,8 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
   const int tiles_m = (m + WBM - 1) / WBM, tiles_n = (n + WBN - 1) / WBN;
   const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
   const int num_kb = (k + BK - 1) / BK;
+  const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
+  const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < WSTAGES; ++s) {
@@ -694,8 +720,18 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           if (!wide_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * WSTAGE_BYTES;
           mbar_expect_tx(&bars->full[stage], WSTAGE_BYTES);
-          tma_load_2d_hint(sa, &tma_a, kb * BK, tc.m * WBM, &bars->full[stage], pol);               // 256 rows
-          tma_load_2d_hint(sa + WA_BYTES, &tma_b, kb * BK, tc.n * WBN, &bars->full[stage], pol);    // 256 rows
+          if (!a_mn) {
+            tma_load_2d_hint(sa, &tma_a, kb * BK, tc.m * WBM, &bars->full[stage], pol);  // one box of 256 rows
+          } else {  // two boxes of [128 k rows] x [128 M positions]
+            tma_load_2d_hint(sa, &tma_a, tc.m * WBM, kb * BK, &bars->full[stage], pol);
+            tma_load_2d_hint(sa + 128 * BK, &tma_a, tc.m * WBM + 128, kb * BK, &bars->full[stage], pol);
+          }
+          if (!b_mn) {
+            tma_load_2d_hint(sa + WA_BYTES, &tma_b, kb * BK, tc.n * WBN, &bars->full[stage], pol);
+          } else {
+            tma_load_2d_hint(sa + WA_BYTES, &tma_b, tc.n * WBN, kb * BK, &bars->full[stage], pol);
+            tma_load_2d_hint(sa + WA_BYTES + 128 * BK, &tma_b, tc.n * WBN + 128, kb * BK, &bars->full[stage], pol);
+          }
           if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -726,14 +762,15 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           if (!wide_wait(&bars->full[stage], phase, bars, 4u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * WSTAGE_BYTES);
-          const uint64_t da0 = make_smem_desc(a_addr), da1 = make_smem_desc(a_addr + 128 * BK);
-          const uint64_t db = make_smem_desc(a_addr + WA_BYTES);
+          const uint64_t da0 = a_mn ? make_smem_desc_mn(a_addr, 128 * BK) : make_smem_desc(a_addr);
+          const uint64_t da1 = a_mn ? make_smem_desc_mn(a_addr + 128 * BK, 128 * BK) : make_smem_desc(a_addr + 128 * BK);
+          const uint64_t db = b_mn ? make_smem_desc_mn(a_addr + WA_BYTES, 128 * BK) : make_smem_desc(a_addr + WA_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint64_t off = (uint64_t)(kk * (UMMA_K >> 4));
+            const uint64_t off_a = (uint64_t)kk * step_a, off_b = (uint64_t)kk * step_b;
             const uint32_t accum = (kb | kk) != 0 ? 1u : 0u;
-            tc_mma_f8(tmem_base, da0 + off, db + off, idesc, accum);
-            tc_mma_f8(tmem_base + 256u, da1 + off, db + off, idesc, accum);
+            tc_mma_f8(tmem_base, da0 + off_a, db + off_b, idesc, accum);
+            tc_mma_f8(tmem_base + 256u, da1 + off_a, db + off_b, idesc, accum);
           }
           tc_commit(&bars->empty[stage]);
           if (++stage == WSTAGES) { stage = 0; phase ^= 1u; }
@@ -900,9 +937,9 @@ __device__ __forceinline__ void tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a,
       : "memory");
 }
 
-__host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind) {
-  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(PBN >> 3) << 17) |
-         ((uint32_t)(PBM >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)a_mn << 15) |
+         ((uint32_t)b_mn << 16) | ((uint32_t)(PBN >> 3) << 17) | ((uint32_t)(PBM >> 4) << 24);
 }
 
 // Bounded wait that also raises the partner's abort flag when it gives up.
@@ -954,6 +991,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
   const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
   const int num_kb = (k + BK - 1) / BK;
   const int64_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
+  const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PSTAGES; ++s) {
@@ -1008,8 +1047,10 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           uint8_t* sa = tiles + stage * PSTAGE_BYTES;
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
           const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
-          tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader, pol_a);
-          tma_load_2d_pair(sa + PA_BYTES, &tma_b, kb * BK, row_b, full_in_leader, pol_b);
+          // K-major box: x = k offset, y = row; MN-major box: x = row (contiguous), y = k offset
+          tma_load_2d_pair(sa, &tma_a, a_mn ? row_a : kb * BK, a_mn ? kb * BK : row_a, full_in_leader, pol_a);
+          tma_load_2d_pair(sa + PA_BYTES, &tma_b, b_mn ? row_b : kb * BK, b_mn ? kb * BK : row_b, full_in_leader,
+                           pol_b);
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -1058,10 +1099,11 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * PSTAGE_BYTES);
-          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + PA_BYTES);
+          const uint64_t da = a_mn ? make_smem_desc_mn(a_addr, PA_BYTES) : make_smem_desc(a_addr);
+          const uint64_t db = b_mn ? make_smem_desc_mn(a_addr + PA_BYTES, PB_BYTES) : make_smem_desc(a_addr + PA_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            tc_mma_f8_pair(tmem_d, da + (uint64_t)(kk * (UMMA_K >> 4)), db + (uint64_t)(kk * (UMMA_K >> 4)), idesc,
+            tc_mma_f8_pair(tmem_d, da + (uint64_t)kk * step_a, db + (uint64_t)kk * step_b, idesc,
                            (kb | kk) != 0 ? 1u : 0u);
           }
           tc_commit_pair(&bars->empty[stage]);
@@ -1145,6 +1187,10 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
+// MN-major operand: 2-D byte tensor [k, rows] with row stride ld (rows contiguous),
+// box = [128 k rows] x [128 bytes of rows], 128B swizzle.
+static int encode_operand_map_mn(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld);
+
 // 2-D byte tensor [rows, k] with row stride ld, box = [box_rows, 128 bytes], 128B swizzle.
 static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
   auto fn = get_encode_fn();
@@ -1152,6 +1198,19 @@ static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, 
   const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t gstride[1] = {(cuuint64_t)ld};
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
+}
+
+static int encode_operand_map_mn(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return F8B200_ERR_DRIVER;
+  const cuuint64_t gdim[2] = {(cuuint64_t)rows, (cuuint64_t)k};
+  const cuuint64_t gstride[1] = {(cuuint64_t)ld};
+  const cuuint32_t box[2] = {128u, (cuuint32_t)BK};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1255,7 +1314,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
 template <typename OutT>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
-                       uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
+                       uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int max_clusters = 0;
@@ -1294,13 +1353,13 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   }
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
-                         choose_raster(m, n, k, pair::PBM, pair::PBN), sched));
+                         choose_raster(m, n, k, pair::PBM, pair::PBN) | layouts, sched));
 }
 
 template <typename OutT>
 static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
-                       uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
+                       uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -1318,7 +1377,7 @@ static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   }
   wide::gemm_fp8_wide_kernel<OutT><<<grid, wide::WTHREADS, wide::WSMEM_BYTES, st>>>(
       ma, mb, mo, sa, sb, static_cast<const OutT*>(bias), static_cast<OutT*>(out), ldo, m, n, k, idesc, vec_ok,
-      use_tma, choose_raster(m, n, k, wide::WBM, wide::WBN), sched);
+      use_tma, choose_raster(m, n, k, wide::WBM, wide::WBN) | layouts, sched);
   return check_launch();
 }
 
@@ -1346,15 +1405,27 @@ static int gemm_mode(int64_t k) {
 
 using namespace f8b200;
 
-static int gemm_fp8_impl(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
-                         const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
-                         int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* sched, void* stream) {
+template <typename Fn>
+static int dispatch_out_dtype(int out_dtype, Fn&& fn) {
+  switch (out_dtype) {
+    case F8B200_BF16: return fn(static_cast<__nv_bfloat16*>(nullptr));
+    case F8B200_FP16: return fn(static_cast<__half*>(nullptr));
+    default: return fn(static_cast<float*>(nullptr));
+  }
+}
+
+// a_layout / b_layout: F8B200_K_MAJOR = storage [rows, K] with K contiguous (ld >= K);
+// F8B200_MN_MAJOR = storage [K, rows] with rows contiguous (ld >= rows).
+static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind, int b_layout,
+                         int64_t ldb, const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
+                         void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* sched, void* stream) {
   if (m < 0 || n < 0 || k < 0) return F8B200_ERR_BAD_ARG;
   if (a_kind < 0 || a_kind > 1 || b_kind < 0 || b_kind > 1 || out_dtype < 0 || out_dtype > 2) return F8B200_ERR_BAD_ARG;
+  if (a_layout < 0 || a_layout > 1 || b_layout < 0 || b_layout > 1) return F8B200_ERR_BAD_ARG;
   if (m == 0 || n == 0) return F8B200_OK;
   if (a == nullptr || b == nullptr || out == nullptr || scale_a == nullptr || scale_b == nullptr) return F8B200_ERR_BAD_ARG;
   if (k == 0) return F8B200_ERR_UNSUPPORTED;
-  if (lda < k || ldb < k || ldo < n) return F8B200_ERR_BAD_ARG;
+  if (lda < (a_layout ? m : k) || ldb < (b_layout ? n : k) || ldo < n) return F8B200_ERR_BAD_ARG;
   if (m > 0x7FFFFFFFLL || n > 0x7FFFFFFFLL || k > 0x7FFFFFFFLL) return F8B200_ERR_UNSUPPORTED;
   if (lda % 16 != 0 || ldb % 16 != 0 || reinterpret_cast<uintptr_t>(a) % 16 != 0 ||
       reinterpret_cast<uintptr_t>(b) % 16 != 0)
@@ -1381,76 +1452,70 @@ static int gemm_fp8_impl(const void* a, int a_kind, int64_t lda, const void* b, 
   } else {
     memset(&mo, 0, sizeof(mo));
   }
-  const int mode = gemm::gemm_mode(k);
-  if (mode == 2) {
-    rc = gemm::encode_operand_map(&ma, a, m, k, lda, 256);
-    if (rc != F8B200_OK) return rc;
-    rc = gemm::encode_operand_map(&mb, b, n, k, ldb, 256);
-    if (rc != F8B200_OK) return rc;
-    const uint32_t idw = gemm::wide::make_idesc_wide(a_kind, b_kind);
-    switch (out_dtype) {
-      case F8B200_BF16:
-        return gemm::launch_wide<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
-      case F8B200_FP16:
-        return gemm::launch_wide<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
-      default:
-        return gemm::launch_wide<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw, vec_ok, sched, st);
-    }
-  }
+  const int layouts = (a_layout << gemm::LAYOUT_A_MN_BIT) | (b_layout << gemm::LAYOUT_B_MN_BIT);
+  // operand maps: K-major boxes are [box_rows] x [128 bytes of K]; MN-major boxes are always
+  // [128 k rows] x [128 bytes of M or N]
+  auto encode_operands = [&](int box_rows) {
+    int r = a_layout ? gemm::encode_operand_map_mn(&ma, a, m, k, lda) : gemm::encode_operand_map(&ma, a, m, k, lda, box_rows);
+    if (r != F8B200_OK) return r;
+    return b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb) : gemm::encode_operand_map(&mb, b, n, k, ldb, box_rows);
+  };
+  int mode = gemm::gemm_mode(k);
   if (mode == 1) {
     // each CTA of a pair fetches 128-row boxes of both operands
-    rc = gemm::encode_operand_map(&ma, a, m, k, lda, 128);
+    rc = encode_operands(128);
     if (rc != F8B200_OK) return rc;
-    rc = gemm::encode_operand_map(&mb, b, n, k, ldb, 128);
-    if (rc != F8B200_OK) return rc;
-    const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind);
-    switch (out_dtype) {
-      case F8B200_BF16:
-        rc = gemm::launch_pair<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
-        break;
-      case F8B200_FP16:
-        rc = gemm::launch_pair<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
-        break;
-      default:
-        rc = gemm::launch_pair<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc2, vec_ok, sched, st);
-        break;
-    }
+    const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind, a_layout, b_layout);
+    rc = dispatch_out_dtype(out_dtype, [&](auto* tag) {
+      using OutT = std::remove_pointer_t<decltype(tag)>;
+      return gemm::launch_pair<OutT>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k,
+                                     idesc2, vec_ok, layouts, sched, st);
+    });
     if (rc != F8B200_ERR_UNSUPPORTED) return rc;
-    // no room for a two-CTA cluster on this device: fall through to the one-CTA kernel
+    mode = 2;  // no room for a two-CTA cluster on this device: the wide kernel needs none
   }
+  if (mode == 2) {
+    rc = encode_operands(256);
+    if (rc != F8B200_OK) return rc;
+    const uint32_t idw = gemm::wide::make_idesc_wide(a_kind, b_kind, a_layout, b_layout);
+    return dispatch_out_dtype(out_dtype, [&](auto* tag) {
+      using OutT = std::remove_pointer_t<decltype(tag)>;
+      return gemm::launch_wide<OutT>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idw,
+                                     vec_ok, layouts, sched, st);
+    });
+  }
+  // one CTA per 128x256 tile (F8B200_GEMM_MODE=1cta): K-major operands, fixed tile stride
+  if (a_layout != 0 || b_layout != 0) return F8B200_ERR_UNSUPPORTED;
   rc = gemm::encode_operand_map(&ma, a, m, k, lda, gemm::BM);
   if (rc != F8B200_OK) return rc;
   rc = gemm::encode_operand_map(&mb, b, n, k, ldb, gemm::BN);
   if (rc != F8B200_OK) return rc;
-
   const uint32_t idesc = gemm::make_idesc(a_kind, b_kind);
-  switch (out_dtype) {
-    case F8B200_BF16:
-      return gemm::launch<__nv_bfloat16>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
-    case F8B200_FP16:
-      return gemm::launch<__half>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
-    default:
-      return gemm::launch<float>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc, vec_ok, st);
-  }
+  return dispatch_out_dtype(out_dtype, [&](auto* tag) {
+    using OutT = std::remove_pointer_t<decltype(tag)>;
+    return gemm::launch<OutT>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k, idesc,
+                              vec_ok, st);
+  });
 }
 
 extern "C" int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
                                const float* scale_a, const float* scale_b, const void* bias, int out_dtype, void* out,
                                int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream) {
   (void)use_fast_accum;  // tcgen05 accumulates in fp32 tensor memory either way
-  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k, nullptr,
-                       stream);
+  return gemm_fp8_impl(a, a_kind, F8B200_K_MAJOR, lda, b, b_kind, F8B200_K_MAJOR, ldb, scale_a, scale_b, bias, out_dtype,
+                       out, ldo, m, n, k, nullptr, stream);
 }
 
-extern "C" int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
-                                  const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
-                                  void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum,
-                                  void* workspace, int64_t workspace_bytes, void* stream) {
+extern "C" int f8b200_gemm_fp8_ws(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
+                                  int b_layout, int64_t ldb, const float* scale_a, const float* scale_b,
+                                  const void* bias, int out_dtype, void* out, int64_t ldo, int64_t m, int64_t n,
+                                  int64_t k, int use_fast_accum, void* workspace, int64_t workspace_bytes,
+                                  void* stream) {
   (void)use_fast_accum;
   if (workspace == nullptr || workspace_bytes < F8B200_GEMM_WORKSPACE_BYTES) return F8B200_ERR_BAD_ARG;
   if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0) return F8B200_ERR_ALIGNMENT;
-  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k,
-                       static_cast<uint32_t*>(workspace), stream);
+  return gemm_fp8_impl(a, a_kind, a_layout, lda, b, b_kind, b_layout, ldb, scale_a, scale_b, bias, out_dtype, out, ldo,
+                       m, n, k, static_cast<uint32_t*>(workspace), stream);
 }
 
 // ---- scheduling words in static device memory ----------------------------------
@@ -1506,7 +1571,8 @@ extern "C" int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t
       sc.owner[slot] = st;
     }
   }
-  return gemm_fp8_impl(a, a_kind, lda, b, b_kind, ldb, scale_a, scale_b, bias, out_dtype, out, ldo, m, n, k,
+  return gemm_fp8_impl(a, a_kind, F8B200_K_MAJOR, lda, b, b_kind, F8B200_K_MAJOR, ldb, scale_a, scale_b, bias, out_dtype,
+                       out, ldo, m, n, k,
                        reinterpret_cast<uint32_t*>(sc.base + (size_t)slot * F8B200_GEMM_WORKSPACE_BYTES), stream);
 }
 

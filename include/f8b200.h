@@ -171,14 +171,25 @@ int f8b200_gemm_fp8(const void* a, int a_kind, int64_t lda, const void* b, int b
  *                    at the same time (different streams) must not share a workspace; GEMMs on
  *                    one stream may.  Capturable in a CUDA graph (memset node + kernel node).
  *
+ *   a_layout,        F8B200_K_MAJOR: as in f8b200_gemm_fp8.  F8B200_MN_MAJOR: the operand is the
+ *   b_layout         TRANSPOSE of that storage, a [K, M] (b [K, N]) byte matrix with M (N)
+ *                    contiguous and lda (ldb) its row pitch.  The tensor cores read such a
+ *                    tile through an MN-major shared-memory descriptor, so the backward GEMMs
+ *                    take grad_output, the input and the weight as they lie in memory and the
+ *                    transposed fp8 copies of float8_experimental/float8_ops.py:150-153 are
+ *                    never made.  Same alignment rules (base and pitch multiples of 16).
+ *
  * Same reference call site as f8b200_gemm_fp8 (float8_experimental/float8_python_api.py:24-64;
  * torch._scaled_mm there draws its workspace from cuBLASLt's own allocation).
  */
 #define F8B200_GEMM_WORKSPACE_BYTES 256
-int f8b200_gemm_fp8_ws(const void* a, int a_kind, int64_t lda, const void* b, int b_kind, int64_t ldb,
-                       const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
-                       void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int use_fast_accum,
-                       void* workspace, int64_t workspace_bytes, void* stream);
+#define F8B200_K_MAJOR 0  /* operand stored [rows, K], K contiguous, ld >= K  */
+#define F8B200_MN_MAJOR 1 /* operand stored [K, rows], rows contiguous, ld >= rows */
+int f8b200_gemm_fp8_ws(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
+                       int b_layout, int64_t ldb, const float* scale_a, const float* scale_b,
+                       const void* bias, int out_dtype, void* out, int64_t ldo, int64_t m, int64_t n,
+                       int64_t k, int use_fast_accum, void* workspace, int64_t workspace_bytes,
+                       void* stream);
 
 /*
  * f8b200_gemm_fp8_ws without the workspace argument: the scheduling words live in a file-scope

@@ -40,8 +40,8 @@ def test_status_strings_and_argument_validation():
     assert lib.f8b200_gemm_fp8(ctypes.c_void_p(16), 0, 24, ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(4),
                                ctypes.c_void_p(4), None, 0, ctypes.c_void_p(16), 16, 4, 4, 16, 0, None) == -2
     # the workspace entry wants an aligned workspace of at least F8B200_GEMM_WORKSPACE_BYTES
-    args = (ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(4), ctypes.c_void_p(4), None, 0,
-            ctypes.c_void_p(16), 16, 4, 4, 16, 0)
+    args = (ctypes.c_void_p(16), 0, 0, 16, ctypes.c_void_p(16), 0, 0, 16, ctypes.c_void_p(4), ctypes.c_void_p(4), None,
+            0, ctypes.c_void_p(16), 16, 4, 4, 16, 0)
     assert lib.f8b200_gemm_fp8_ws(*args, None, 256, None) == -1
     assert lib.f8b200_gemm_fp8_ws(*args, ctypes.c_void_p(256), 8, None) == -1
     assert lib.f8b200_gemm_fp8_ws(*args, ctypes.c_void_p(260), 256, None) == -2

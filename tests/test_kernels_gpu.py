@@ -284,6 +284,32 @@ def test_gemm_dynamic_schedule_matches_fixed_stride(mnk, gemm_mode, monkeypatch)
     check_gemm(fixed[rows].float(), a[rows].float() @ b.float().t())
 
 
+@pytest.mark.parametrize("layouts", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mnk", [(512, 768, 256), (4096, 2048 + 16, 1024 + 48), (8192, 4096, 16384 + 128)])
+@pytest.mark.parametrize("mode", ["2cta", "wide"])
+def test_gemm_mn_major_operands(mnk, layouts, mode, monkeypatch):
+    """An operand may be handed over as the transpose of the usual storage ([K, rows], rows
+    contiguous): the result has to be bit-identical to the K-major call on the same values."""
+    monkeypatch.setenv("F8B200_GEMM_MODE", mode)
+    m, n, k = mnk
+    a_mn, b_mn = layouts
+    g = torch.Generator(device="cuda").manual_seed(m * 3 + n + k)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e5m2)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    sa, sb = torch.tensor(2.0, device="cuda"), torch.tensor(0.5, device="cuda")
+    want = gemm(a, b, sa, sb)
+    a_arg = a.view(torch.uint8).t().contiguous().view(torch.float8_e5m2) if a_mn else a      # [k, m]
+    b_arg = b.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn) if b_mn else b    # [k, n]
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    N.gemm_fp8(a_arg, a_arg.stride(0), b_arg, b_arg.stride(0), sa, sb, None, out, n, m, n, k, False,
+               a_mn_major=a_mn, b_mn_major=b_mn)
+    torch.cuda.synchronize()
+    assert N.read_device_error() == 0
+    rows = torch.tensor([0, 127, 128, 255, 256, m - 1], device="cuda")
+    check_gemm(out[rows].float(), a[rows].float() @ b.float().t() / (2.0 * 0.5))
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
 def test_cast_full_size_properties():
     """Full-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
     size-independent properties: amax equals max|x|; the transposed copy is the transpose;
