@@ -30,6 +30,11 @@ SHAPES = [("wqkv", 8192, 10240), ("wo", 8192, 8192), ("w13", 8192, 57344), ("w2"
 METRIC = "Float8Linear fwd+bwd TFLOP/s (LLaMa-2-70B shapes); amax+cast HBM GB/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
+# casts also write a transposed fp8 copy only when asked to (the GEMMs read either memory order)
+TRANSPOSED_COPIES = os.environ.get("F8B200_CAST_TRANSPOSED", "0") == "1"
+# dram__bytes_write of the cast kernel on a 16384x8192 bf16 tensor without the transposed copy
+# (profiles/cast_tile8_kernel_16384x8192_bf16.md)
+CAST_WRITE_TRAFFIC_1COPY = 134.2e6
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -200,8 +205,10 @@ def measure_delayed(torch, f8, _native, dev, x):
     cast_ms = s0.elapsed_time(s1) / 20
     return {"sync_rows": 960, "sync_kernel_us": ev[0] / max(ev[1], 1) * 1e3, "sync_launches_per_call": 1,
             "sync_wall_us_per_call": wall_us,
-            "delayed_cast_ms_16384x8192": cast_ms, "delayed_cast_gbs": 4.0 * x.numel() / (cast_ms * 1e-3) / 1e9,
-            "delayed_cast_bytes": "4 B per element: 2 read + 1 fp8 + 1 transposed fp8, amax from the same read"}
+            "delayed_cast_ms_16384x8192": cast_ms,
+            "delayed_cast_gbs": (4.0 if TRANSPOSED_COPIES else 3.0) * x.numel() / (cast_ms * 1e-3) / 1e9,
+            "delayed_cast_bytes": ("4 B per element: 2 read + 1 fp8 + 1 transposed fp8, amax from the same read"
+                                   if TRANSPOSED_COPIES else "3 B per element: 2 read + 1 fp8, amax from the same read")}
 
 
 # ---------------------------------------------------------------------------
@@ -404,12 +411,14 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     gemm_flops = args.steps * flops_per_step
     gemm_tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-    # dynamic amax+cast of n bf16 elements with the transposed copy: 2n + 2n + n + n bytes
-    # (under FSDP2 each rank casts 1/world of every weight, without the transposed copy, and
-    # the weight amaxes come from one multi-tensor launch)
+    # dynamic amax+cast of n bf16 elements: 2n (amax read) + 2n (cast read) + n (fp8) bytes, + n when the
+    # transposed copy is emitted too (F8B200_CAST_TRANSPOSED=1; off by default: the GEMMs read
+    # operands in either memory order).  Under FSDP2 each rank casts 1/world of every weight and
+    # the weight amaxes come from one multi-tensor launch.
+    per_elem = 6.0 if TRANSPOSED_COPIES else 5.0
     act_elems = sum(M_TOKENS * k + M_TOKENS * n for _, k, n in shapes)
     w_elems = sum(n * k for _, k, n in shapes)
-    cast_bytes = args.steps * (6.0 * act_elems + (5.0 * w_elems / world if fsdp else 6.0 * w_elems))
+    cast_bytes = args.steps * (per_elem * act_elems + (5.0 * w_elems / world if fsdp else per_elem * w_elems))
     if fsdp:
         cast_bytes += args.steps * 2.0 * w_elems / world  # forward + backward all-gather each re-cast the shard
     cast_gbs = cast_bytes / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
@@ -456,10 +465,13 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "achieved": cast_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": (cast_gbs / peaks["hbm_gbs"]) if cast_gbs else None,
             "frac_of_nominal_8000": (cast_gbs / NOMINAL_HBM_GBS) if cast_gbs else None,
-            "algorithmic_bytes": "6 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8 + 1 transposed fp8)",
+            "algorithmic_bytes": ("6 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8 + 1 transposed fp8)"
+                                  if TRANSPOSED_COPIES else
+                                  "5 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8; no transposed copy)"),
             "launches": cast_calls + amax_calls,
             # one 16384x8192 bf16 tensor, amax + cast launches, from profiles/cast_tile8_kernel_16384x8192_bf16.md
-            "traffic": 268.4e6 + 268.5e6 + 211.9e6, "traffic_algorithmic": 6 * 134.2e6,
+            "traffic": 268.4e6 + 268.5e6 + (211.9e6 if TRANSPOSED_COPIES else CAST_WRITE_TRAFFIC_1COPY),
+            "traffic_algorithmic": (6 if TRANSPOSED_COPIES else 5) * 134.2e6,
         },
         "time_share_ms_per_step": {"gemm": gemm_ms / args.steps, "cast": cast_ms / args.steps,
                                    "amax": amax_ms / args.steps},

@@ -129,19 +129,33 @@ def _delayed_sync_cuda(amax, hist, n_e4m3: int, orig_dtype: int, scale_out, hist
     N.delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out, hist_out)
 
 
+def _gemm_operand(x: torch.Tensor):
+    """How the GEMM can read the logical [rows, K] operand `x` where it lies: (tensor, pitch,
+    mn_major).  K contiguous = K-major; rows contiguous (a transposed view of a [K, rows]
+    buffer) = MN-major, which the tensor cores read through an MN-major descriptor.  Anything
+    else, or a pitch / base address that TMA cannot take, is copied to a K-major buffer."""
+    rows, k = x.shape
+    if x.stride(1) == 1 and (rows == 1 or (x.stride(0) >= k and x.stride(0) % 16 == 0)) and x.data_ptr() % 16 == 0:
+        return x, (x.stride(0) if rows > 1 else -(-k // 16) * 16), False
+    if x.stride(0) == 1 and k > 1 and x.stride(1) >= rows and x.stride(1) % 16 == 0 and x.data_ptr() % 16 == 0:
+        return x, x.stride(1), True
+    x = x.contiguous()
+    return x, x.stride(0), False
+
+
 def _scaled_mm_cuda(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum: bool):
     m, k = a.shape
     n, k2 = b_t.shape
     if k != k2:
         raise RuntimeError(f"scaled_mm: inner dimensions differ ({k} vs {k2})")
-    if a.stride(1) != 1 or b_t.stride(1) != 1:
-        raise RuntimeError("scaled_mm: both operands must have the contraction dimension contiguous")
+    a, lda, a_mn = _gemm_operand(a)
+    b_t, ldb, b_mn = _gemm_operand(b_t)
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if bias is not None and bias.dtype != out_dtype:
         bias = bias.to(out_dtype)
     sa = scale_a if scale_a.dtype == torch.float32 else scale_a.float()
     sb = scale_b if scale_b.dtype == torch.float32 else scale_b.float()
-    N.gemm_fp8(a, a.stride(0), b_t, b_t.stride(0), sa, sb, bias, out, n, m, n, k, use_fast_accum)
+    N.gemm_fp8(a, lda, b_t, ldb, sa, sb, bias, out, n, m, n, k, use_fast_accum, a_mn_major=a_mn, b_mn_major=b_mn)
     return out
 
 

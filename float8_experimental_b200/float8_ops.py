@@ -1,9 +1,10 @@
 """Operator table of `Float8Tensor` (`__torch_dispatch__` handlers).
 
 Covers the same aten / c10d ops as float8_experimental/float8_ops.py:33-363.  The
-matrix products go to the tcgen05 GEMM (`f8b200::scaled_mm`); when an operand is not
-K-major its pre-emitted transposed copy (`Float8Tensor._alt`) is used, and only if
-there is none the fp8 transpose kernel runs.
+matrix products go to the tcgen05 GEMM (`f8b200::scaled_mm`), which reads an operand in
+either memory order (K contiguous or rows contiguous), so the transposed fp8 copies of the
+reference's `preprocess_addmm` are not made; only an operand that is contiguous in neither
+order, or misaligned for TMA, is copied.
 """
 from __future__ import annotations
 
@@ -129,27 +130,37 @@ def _k_major(data: torch.Tensor) -> bool:
     return data.dim() == 2 and data.stride(1) == 1 and data.stride(0) >= data.shape[1]
 
 
+def _mn_major(data: torch.Tensor) -> bool:
+    """A transposed view of a row-major [K, rows] buffer that TMA can address."""
+    return (
+        data.dim() == 2
+        and data.stride(0) == 1
+        and data.shape[1] > 1
+        and data.stride(1) >= data.shape[0]
+        and data.stride(1) % 16 == 0
+        and data.data_ptr() % 16 == 0
+    )
+
+
+def _gemm_readable(t: Float8Tensor, logical: torch.Tensor, alt: Optional[torch.Tensor]) -> torch.Tensor:
+    """`logical` is the [rows, K] operand as a view of `t._data`.  Returned as it lies when
+    the GEMM can read it (K contiguous, or rows contiguous: the kernels take both), else the
+    pre-emitted copy in the other memory order when there is one, else a K-major copy."""
+    if _k_major(logical) or _mn_major(logical):
+        return logical
+    if alt is not None and (_k_major(alt) or _mn_major(alt)):
+        return alt
+    return logical.contiguous()
+
+
 def _row_major_operand(t: Float8Tensor) -> torch.Tensor:
-    """[M, K] bytes with K contiguous."""
-    if _k_major(t._data):
-        return t._data
-    if t._alt is not None and _k_major(t._alt):
-        return t._alt
-    if _k_major(t._data.t()):
-        return ops.transpose_fp8(t._data.t())
-    return t._data.contiguous()
+    """The [M, K] operand."""
+    return _gemm_readable(t, t._data, t._alt)
 
 
 def _col_major_operand_as_nk(t: Float8Tensor) -> torch.Tensor:
-    """The [K, N] operand returned as its transpose [N, K] with K contiguous."""
-    bt = t._data.t()
-    if _k_major(bt):
-        return bt
-    if t._alt is not None and _k_major(t._alt.t()):
-        return t._alt.t()
-    if _k_major(t._data):
-        return ops.transpose_fp8(t._data)
-    return bt.contiguous()
+    """The [K, N] operand returned as its transpose [N, K]."""
+    return _gemm_readable(t, t._data.t(), t._alt.t() if t._alt is not None else None)
 
 
 def preprocess_addmm(a: Float8Tensor, b: Float8Tensor):
@@ -163,8 +174,8 @@ def preprocess_addmm(a: Float8Tensor, b: Float8Tensor):
         assert a._data.size(1) == b._data.size(
             0
         ), f"Inner dims must match for mm, got {a._data.size(1)} and {b._data.size(0)}"
-    if a_data.shape[1] % 16 != 0 or a_data.stride(0) % 16 != 0 or b_nk.stride(0) % 16 != 0:
-        if not cfg.pad_inner_dim and a_data.shape[1] % 16 != 0:
+    if a_data.shape[1] % 16 != 0:
+        if not cfg.pad_inner_dim:
             raise RuntimeError(
                 f"float8 GEMM needs the inner dimension to be a multiple of 16, got {a_data.shape[1]}; "
                 "set Float8LinearConfig.pad_inner_dim=True"

@@ -105,7 +105,7 @@ class NoopFwToFloat8E5M2BwDelayed(torch.autograd.Function):
         )
         res = hp_tensor_and_scale_to_float8(
             go, scale_buf, e5m2_dtype, ctx.linear_mm_config, GemmInputRole.GRAD_OUTPUT, amax_out=amax_buf,
-            with_transpose=True,  # the weight-gradient GEMM consumes grad_output transposed
+            with_transpose=_want_transposed_copy(),
         )
         return res, None, None, None, None, None, None
 
@@ -124,8 +124,7 @@ class NoopFwToFloat8E5M2BwDynamic(torch.autograd.Function):
     def backward(ctx, gradY):
         if tensor_already_casted_to_fp8(gradY):
             return gradY, None
-        # with the transposed copy: the weight-gradient GEMM consumes grad_output transposed
         fp8 = _DynamicToFloat8Func.apply(
-            gradY, e5m2_dtype, ctx.linear_mm_config, GemmInputRole.GRAD_OUTPUT, False, True
+            gradY, e5m2_dtype, ctx.linear_mm_config, GemmInputRole.GRAD_OUTPUT, False, _want_transposed_copy()
         )
         return fp8, None

@@ -9,6 +9,8 @@ the transpose copies the reference makes in float8_ops.py:150-153.
 """
 from __future__ import annotations
 
+import os
+
 import enum
 from collections import namedtuple
 from typing import Dict, Optional
@@ -83,9 +85,11 @@ def tensor_already_casted_to_fp8(tensor: torch.Tensor) -> bool:
 
 
 def _want_transposed_copy() -> bool:
-    """The transposed copy only feeds the backward GEMMs.  Must be asked OUTSIDE an
-    autograd.Function.forward (grad mode is always off inside one)."""
-    return torch.is_grad_enabled()
+    """Whether casts also emit the transposed fp8 copy (`Float8Tensor._alt`).  The GEMM reads
+    an operand in either memory order, so nothing needs that copy any more and the default is
+    no; F8B200_CAST_TRANSPOSED=1 in the environment brings the copies back (the backward GEMMs
+    then run on K-major operands only) for comparisons."""
+    return os.environ.get("F8B200_CAST_TRANSPOSED", "0") == "1"
 
 
 def _wrap_cast_result(data, data_t, scale, orig_dtype, linear_mm_config, gemm_input_role):
@@ -197,7 +201,7 @@ def hp_tensor_and_scale_to_float8(
 
     `amax_out` (an fp32 buffer) additionally receives max|hp_tensor| from the same read;
     delayed scaling uses it to record the current amax while casting.  `with_transpose`
-    asks for the second (transposed) layout; default: whenever autograd is recording."""
+    asks for the second (transposed) layout; default: `_want_transposed_copy()`."""
     if with_transpose is None:
         with_transpose = _want_transposed_copy()
     return _ToFloat8ConstrFunc.apply(

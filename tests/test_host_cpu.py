@@ -249,7 +249,8 @@ def test_buffers_stay_fp32_and_state_dict_roundtrip():
     assert torch.equal(m2.fp8_amax_history_weight, m.fp8_amax_history_weight)
 
 
-def test_float8_tensor_ops():
+def test_float8_tensor_ops(monkeypatch):
+    monkeypatch.setenv("F8B200_CAST_TRANSPOSED", "1")  # casts emit the second layout, which the ops must carry along
     cfg = LinearMMConfig()
     x = torch.randn(16, 32, dtype=torch.bfloat16)
     a = hp_tensor_to_float8_dynamic(x, e4m3_dtype, cfg)

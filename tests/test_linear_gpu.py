@@ -82,9 +82,14 @@ def test_small_linear_delayed_three_iterations(golden_dir):
         assert getattr(m, f"fp8_scale_{n}").item() == g[f"{dname}_del3_scale_{n}"][0]
 
 
-def test_config1_bit_exact_casts_and_gemm_tolerance(golden_dir):
-    """The small reference configuration: M=2048, K=N=4096, dynamic scaling, outliers in x."""
+@pytest.mark.parametrize("transposed_copies", ["0", "1"])
+def test_config1_bit_exact_casts_and_gemm_tolerance(golden_dir, transposed_copies, monkeypatch):
+    """The small reference configuration: M=2048, K=N=4096, dynamic scaling, outliers in x.
+    Run both ways: the backward GEMMs reading grad_output, x and W where they lie (MN-major
+    operands, the default) and reading transposed fp8 copies emitted by the casts."""
     from golden_inputs import config1_inputs, sha256
+
+    monkeypatch.setenv("F8B200_CAST_TRANSPOSED", transposed_copies)
 
     g = np.load(os.path.join(golden_dir, "config1.npz"))
     x, w, go = config1_inputs()
@@ -99,7 +104,10 @@ def test_config1_bit_exact_casts_and_gemm_tolerance(golden_dir):
         assert isinstance(t8, Float8Tensor)
         assert t8._scale.item() == g[f"scale_{key}"], key
         assert sha256(bits(t8._data)) == str(g[f"sha_{key}8"]), key
-        assert torch.equal(t8._alt.contiguous().view(torch.uint8), t8._data.view(torch.uint8))
+        if transposed_copies == "1":
+            assert torch.equal(t8._alt.contiguous().view(torch.uint8), t8._data.view(torch.uint8))
+        else:
+            assert t8._alt is None
     m = make_linear(wc, f8.Float8LinearConfig())
     xr = xc.clone().requires_grad_(True)
     y = m(xr)
