@@ -419,8 +419,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     act_elems = sum(M_TOKENS * k + M_TOKENS * n for _, k, n in shapes)
     w_elems = sum(n * k for _, k, n in shapes)
     cast_bytes = args.steps * (per_elem * act_elems + (5.0 * w_elems / world if fsdp else per_elem * w_elems))
-    if fsdp:
-        cast_bytes += args.steps * 2.0 * w_elems / world  # forward + backward all-gather each re-cast the shard
+    if fsdp and args.fsdp_root:
+        # non-root FSDP2 modules reshard after forward: the shard is cast again for the backward all-gather
+        cast_bytes += args.steps * 3.0 * w_elems / world
     cast_gbs = cast_bytes / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
 
     # bounded CPU sample (rank 0, N = 1 only)
@@ -440,8 +441,12 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                         "dynamic scaling, bf16 in/out",
             "shapes_KN": {name: [k, n] for name, k, n in shapes},
             "l2": "inputs larger than L2 (smallest tensor cast per layer is 134 MB; L2 is 126 MB)",
-            "parallelism": f"fsdp2 x{world}: fp8 weight all-gather (1 B/elem) fwd+bwd, bf16 grad reduce-scatter, "
-                           "one amax all-reduce per step" if fsdp else "single GPU",
+            "parallelism": (f"fsdp2 x{world}: " + (
+                "one root, fp8 weight all-gather (1 B/elem) before forward and again before backward, "
+                if args.fsdp_root else
+                "each layer its own FSDP2 root (a root keeps its gathered weight for backward): one fp8 weight "
+                "all-gather (1 B/elem) per layer and step, ") + "bf16 grad reduce-scatter, one amax all-reduce per step")
+            if fsdp else "single GPU",
         },
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
