@@ -35,6 +35,8 @@ EXPORTS = (
     "f8b200_gemm_fp8",
     "f8b200_gemm_fp8_ws",
     "f8b200_gemm_fp8_static_scratch",
+    "f8b200_rmsnorm_amax",
+    "f8b200_rmsnorm_cast",
     "f8b200_read_device_error",
 )
 
@@ -74,6 +76,8 @@ def load() -> ctypes.CDLL:
     lib.f8b200_gemm_fp8_static_scratch.argtypes = lib.f8b200_gemm_fp8.argtypes
     lib.f8b200_gemm_fp8_ws.argtypes = [vp, i32, i32, i64, vp, i32, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64,
                                        i32, vp, i64, vp]
+    lib.f8b200_rmsnorm_amax.argtypes = [vp, i32, i64, i64, i64, vp, ctypes.c_float, vp, vp, vp]
+    lib.f8b200_rmsnorm_cast.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
         fn = getattr(lib, name)
@@ -304,6 +308,31 @@ def gemm_fp8_static_scratch(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int
                                                   _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo, m, n, k,
                                                   int(use_fast_accum), _stream(a)),
             "f8b200_gemm_fp8_static_scratch",
+    "f8b200_rmsnorm_amax",
+    "f8b200_rmsnorm_cast",
+        )
+
+
+def rmsnorm_amax(x: torch.Tensor, rows: int, cols: int, ld: int, weight: torch.Tensor, eps: float,
+                 rstd_out: torch.Tensor, amax_out: torch.Tensor) -> None:
+    _require_cuda(x, weight, rstd_out, amax_out)
+    with _Launch("norm_amax", x.device):
+        _check(
+            load().f8b200_rmsnorm_amax(x.data_ptr(), hp_code(x.dtype), rows, cols, ld, weight.data_ptr(), float(eps),
+                                       rstd_out.data_ptr(), amax_out.data_ptr(), _stream(x)),
+            "f8b200_rmsnorm_amax",
+        )
+
+
+def rmsnorm_cast(x: torch.Tensor, rows: int, cols: int, ld: int, weight: torch.Tensor, rstd: torch.Tensor,
+                 amax: torch.Tensor, scale_out: Optional[torch.Tensor], out: torch.Tensor, ld_out: int) -> None:
+    _require_cuda(x, weight, rstd, amax, scale_out, out)
+    with _Launch("norm_cast", x.device):
+        _check(
+            load().f8b200_rmsnorm_cast(x.data_ptr(), hp_code(x.dtype), rows, cols, ld, weight.data_ptr(),
+                                       rstd.data_ptr(), amax.data_ptr(), fp8_code(out.dtype), _ptr(scale_out),
+                                       out.data_ptr(), ld_out, _stream(x)),
+            "f8b200_rmsnorm_cast",
         )
 
 

@@ -14,6 +14,8 @@ Ops (namespace `f8b200`):
   transpose_fp8(x) -> x^T contiguous                      f8b200_transpose_u8
   delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out!, hist_out!)
   scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum) -> out
+  rmsnorm_amax(x, weight, eps) -> (rstd fp32 [rows], amax fp32 0-dim)      f8b200_rmsnorm_amax
+  rmsnorm_cast(x, weight, rstd, amax, kind) -> (data, scale)               f8b200_rmsnorm_cast
 """
 from __future__ import annotations
 
@@ -42,6 +44,8 @@ _lib.define(
     "scaled_mm(Tensor a, Tensor b_t, Tensor scale_a, Tensor scale_b, Tensor? bias, ScalarType out_dtype, "
     "bool use_fast_accum) -> Tensor"
 )
+_lib.define("rmsnorm_amax(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
+_lib.define("rmsnorm_cast(Tensor x, Tensor weight, Tensor rstd, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 
 
 def _as_matrix(x: torch.Tensor) -> Tuple[torch.Tensor, int, int, int]:
@@ -159,6 +163,28 @@ def _scaled_mm_cuda(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum: b
     return out
 
 
+def _rmsnorm_amax_cuda(x, weight, eps: float):
+    xm, rows, cols, ld = _as_matrix(x)
+    weight = weight.contiguous()
+    if weight.dtype != x.dtype or weight.numel() != cols:
+        raise RuntimeError("rmsnorm_amax: the weight must have x's dtype and one element per column")
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    amax = torch.empty((), dtype=torch.float32, device=x.device)
+    N.rmsnorm_amax(xm, rows, cols, ld, weight, eps, rstd, amax)
+    return rstd, amax
+
+
+def _rmsnorm_cast_cuda(x, weight, rstd, amax, fp8_kind: int):
+    xm, rows, cols, ld = _as_matrix(x)
+    weight = weight.contiguous()
+    data = _empty_like_shape(x, N.FP8_DTYPE[fp8_kind])
+    scale = torch.empty((), dtype=torch.float32, device=x.device)
+    N.rmsnorm_cast(xm, rows, cols, ld, weight, rstd, amax, scale, data, cols)
+    return data, scale
+
+
+_lib.impl("rmsnorm_amax", _rmsnorm_amax_cuda, "CUDA")
+_lib.impl("rmsnorm_cast", _rmsnorm_cast_cuda, "CUDA")
 _lib.impl("amax", _amax_cuda, "CUDA")
 _lib.impl("multi_amax", _multi_amax_cuda, "CUDA")
 _lib.impl("amax_to_scale", _amax_to_scale_cuda, "CUDA")
@@ -173,6 +199,17 @@ _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 # fake (meta) implementations: shapes and dtypes only, so torch.compile can trace
 # around the opaque ops
 # ---------------------------------------------------------------------------
+@torch.library.register_fake("f8b200::rmsnorm_amax")
+def _rmsnorm_amax_fake(x, weight, eps):
+    cols = x.shape[-1]
+    return x.new_empty((x.numel() // max(cols, 1),), dtype=torch.float32), x.new_empty((), dtype=torch.float32)
+
+
+@torch.library.register_fake("f8b200::rmsnorm_cast")
+def _rmsnorm_cast_fake(x, weight, rstd, amax, fp8_kind):
+    return x.new_empty(x.shape, dtype=N.FP8_DTYPE[fp8_kind]), x.new_empty((), dtype=torch.float32)
+
+
 @torch.library.register_fake("f8b200::amax")
 def _amax_fake(x):
     return x.new_empty((), dtype=torch.float32)

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libf8b200.so")
-SOURCES = ["capi.cu", "cast.cu", "gemm.cu"]
+SOURCES = ["capi.cu", "cast.cu", "gemm.cu", "norm.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "f8b200.h")]
 
 

@@ -1,0 +1,239 @@
+// RMSNorm fused into the dynamic fp8 cast of its output (the producer of a Float8Linear
+// input).  Unfused, the norm reads x and writes y (2 + 2 bytes per element) and the cast then
+// reads y twice and writes fp8 (2 + 2 + 1): 9 bytes per element.  Here pass A reads x and
+// produces the per-row 1/rms and the amax of y without writing y, pass B reads x again and
+// writes fp8: 5 bytes per element, and y never exists in memory.
+//
+// Arithmetic (T = dtype of x and of the weight), every step one IEEE operation so that a
+// CPU restatement gives the same bits:
+//   ss_t   = per-thread sum of fl(x*x) in fp32, thread t owning the 8-element chunks
+//            c with (c mod 256) == t, in increasing order
+//   total  = butterfly sum over the 32 lanes of each warp, then over the 8 warp sums
+//   rstd   = fl(1 / fl(sqrt(fl(fl(total / cols) + eps))))
+//   y      = RN_T(float(RN_T(fl(x * rstd))) * float(w))
+// which is RMSNorm.forward of float8_experimental/benchmarks/profile_linear_float8.py:69-74
+// with the reduction order fixed.  The cast of y is the dynamic cast of cast.cu
+// (float8_experimental/float8_scaling_utils.py:33-62).
+#include "common.cuh"
+
+namespace f8b200 {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+template <int HP>
+__device__ __forceinline__ float load_hp(const void* base, int64_t i) {
+  if constexpr (HP == F8B200_BF16) {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+  } else if constexpr (HP == F8B200_FP16) {
+    return __half2float(reinterpret_cast<const __half*>(base)[i]);
+  } else {
+    return reinterpret_cast<const float*>(base)[i];
+  }
+}
+
+// Widens the eight 16-bit values of a 16-byte word.
+template <int HP>
+__device__ __forceinline__ void widen8(const uint4& q, float (&v)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (HP == F8B200_BF16) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    } else {
+      v[2 * i] = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xFFFFu)));
+      v[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16)));
+    }
+  }
+}
+
+// Loads chunk `c` (elements 8c .. 8c+7) of a row; `n` of them exist.
+template <int HP, bool VEC>
+__device__ __forceinline__ void load_chunk(const char* row, int64_t c, int n, float (&v)[8]) {
+  if constexpr (VEC) {
+    widen8<HP>(__ldg(reinterpret_cast<const uint4*>(row) + c), v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = j < n ? load_hp<HP>(row, c * 8 + j) : 0.0f;
+  }
+}
+
+// Sum over the CTA in a fixed order: xor butterfly inside each warp, then over the warp sums.
+__device__ __forceinline__ float block_sum_fixed(float v, float* smem) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+  if (lane == 0) smem[w] = v;
+  __syncthreads();
+  float t = lane < (kNormThreads / 32) ? smem[lane] : 0.0f;
+#pragma unroll
+  for (int off = (kNormThreads / 64); off > 0; off >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, off));
+  t = __shfl_sync(0xFFFFFFFFu, t, 0);
+  __syncthreads();  // smem is reused by the next row
+  return t;
+}
+
+template <int HP>
+__device__ __forceinline__ float norm_value(float x, float rstd, float w) {
+  const float o = round_hp<HP>(__fmul_rn(x, rstd));
+  return round_hp<HP>(__fmul_rn(o, w));
+}
+
+__device__ __forceinline__ uint32_t abs_bits(float y) { return __float_as_uint(y) & 0x7FFFFFFFu; }
+
+// Pass A: rstd per row and the amax of y over the whole tensor.
+template <int HP, bool VEC>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_amax_kernel(const char* __restrict__ x, int64_t ld_bytes, int64_t rows, int64_t cols,
+                    const char* __restrict__ weight, float eps, float* __restrict__ rstd_out,
+                    uint32_t* __restrict__ amax_bits) {
+  __shared__ float red[kNormThreads / 32];
+  __shared__ uint32_t redu[kNormThreads / 32];
+  const int64_t chunks = (cols + 7) / 8;
+  uint32_t amax = 0;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const char* row = x + r * ld_bytes;
+    float ss = 0.0f;
+    for (int64_t c = threadIdx.x; c < chunks; c += kNormThreads) {
+      float v[8];
+      const int n = (int)min((int64_t)8, cols - c * 8);
+      load_chunk<HP, VEC>(row, c, n, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(v[j], v[j]));
+    }
+    const float total = block_sum_fixed(ss, red);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)cols), eps)));
+    if (threadIdx.x == 0) rstd_out[r] = rstd;
+    // second sweep over the row (16 KB for 8192 bf16 columns: served from L1/L2)
+    for (int64_t c = threadIdx.x; c < chunks; c += kNormThreads) {
+      float v[8], w[8];
+      const int n = (int)min((int64_t)8, cols - c * 8);
+      load_chunk<HP, VEC>(row, c, n, v);
+      load_chunk<HP, VEC>(weight, c, n, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < n) amax = max(amax, abs_bits(norm_value<HP>(v[j], rstd, w[j])));
+    }
+  }
+  amax = warp_max_u32(amax);
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  if (lane == 0) redu[wp] = amax;
+  __syncthreads();
+  if (wp == 0) {
+    amax = lane < (kNormThreads / 32) ? redu[lane] : 0u;
+    amax = warp_max_u32(amax);
+    if (lane == 0 && amax > *reinterpret_cast<volatile uint32_t*>(amax_bits)) atomicMax(amax_bits, amax);
+  }
+}
+
+// Pass B: y again from x, rstd and the weight; scale from the amax; saturating RNE cast.
+template <int HP, int KIND, bool VEC>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_cast_kernel(const char* __restrict__ x, int64_t ld_bytes, int64_t rows, int64_t cols,
+                    const char* __restrict__ weight, const float* __restrict__ rstd_in,
+                    const float* __restrict__ amax_in, float* __restrict__ scale_out, uint8_t* __restrict__ out,
+                    int64_t ld_out) {
+  const float scale = amax_to_scale_dev(__ldg(amax_in), fp8_max_of(KIND), HP, HP == F8B200_FP16);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) *scale_out = scale;
+  const int64_t chunks = (cols + 7) / 8;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const char* row = x + r * ld_bytes;
+    const float rstd = __ldg(rstd_in + r);
+    uint8_t* orow = out + r * ld_out;
+    for (int64_t c = threadIdx.x; c < chunks; c += kNormThreads) {
+      float v[8], w[8], q[8];
+      const int n = (int)min((int64_t)8, cols - c * 8);
+      load_chunk<HP, VEC>(row, c, n, v);
+      load_chunk<HP, VEC>(weight, c, n, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = __fmul_rn(norm_value<HP>(v[j], rstd, w[j]), scale);
+      // the product with a 0-dim scale is rounded to T before the clamp (fp32 input: no rounding)
+      const uint32_t lo = cast4<HP, KIND>(q[0], q[1], q[2], q[3], HP != F8B200_FP32);
+      const uint32_t hi = cast4<HP, KIND>(q[4], q[5], q[6], q[7], HP != F8B200_FP32);
+      if (VEC && n == 8) {
+        *reinterpret_cast<uint2*>(orow + c * 8) = make_uint2(lo, hi);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < n) orow[c * 8 + j] = (uint8_t)(((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu);
+      }
+    }
+  }
+}
+
+int norm_grid(int64_t rows) {
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (int)(rows < cap ? rows : cap);
+}
+
+}  // namespace
+}  // namespace f8b200
+
+using namespace f8b200;
+
+extern "C" int f8b200_rmsnorm_amax(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                                   const void* weight, float eps, float* rstd_out, float* amax_out, void* stream) {
+  if (x == nullptr || weight == nullptr || rstd_out == nullptr || amax_out == nullptr) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2 || rows <= 0 || cols <= 0 || ld_x < cols) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int es = hp_size_of(hp_dtype);
+  const bool vec = es == 2 && cols % 8 == 0 && ld_x % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(weight) % 16 == 0;
+  cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), st);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const char* xp = static_cast<const char*>(x);
+  const char* wp = static_cast<const char*>(weight);
+  uint32_t* ab = reinterpret_cast<uint32_t*>(amax_out);
+  const int grid = norm_grid(rows);
+#define F8_LAUNCH_A(HP, VEC) \
+  rmsnorm_amax_kernel<HP, VEC><<<grid, kNormThreads, 0, st>>>(xp, ld_x * es, rows, cols, wp, eps, rstd_out, ab)
+  if (hp_dtype == F8B200_BF16) {
+    if (vec) F8_LAUNCH_A(F8B200_BF16, true); else F8_LAUNCH_A(F8B200_BF16, false);
+  } else if (hp_dtype == F8B200_FP16) {
+    if (vec) F8_LAUNCH_A(F8B200_FP16, true); else F8_LAUNCH_A(F8B200_FP16, false);
+  } else {
+    F8_LAUNCH_A(F8B200_FP32, false);
+  }
+#undef F8_LAUNCH_A
+  return check_launch();
+}
+
+extern "C" int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                                   const void* weight, const float* rstd, const float* amax, int fp8_kind,
+                                   float* scale_out, void* out, int64_t ld_out, void* stream) {
+  if (x == nullptr || weight == nullptr || rstd == nullptr || amax == nullptr || out == nullptr) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2 || fp8_kind < 0 || fp8_kind > 1) return F8B200_ERR_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ld_x < cols || ld_out < cols) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int es = hp_size_of(hp_dtype);
+  const bool vec = es == 2 && cols % 8 == 0 && ld_x % 8 == 0 && ld_out % 8 == 0 &&
+                   reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 8 == 0;
+  const char* xp = static_cast<const char*>(x);
+  const char* wp = static_cast<const char*>(weight);
+  uint8_t* op = static_cast<uint8_t*>(out);
+  const int grid = norm_grid(rows);
+#define F8_LAUNCH_B(HP, KIND, VEC)                                                                                 \
+  rmsnorm_cast_kernel<HP, KIND, VEC><<<grid, kNormThreads, 0, st>>>(xp, ld_x * es, rows, cols, wp, rstd, amax, \
+                                                                     scale_out, op, ld_out)
+#define F8_DISPATCH_B(HP, VEC)                                     \
+  do {                                                             \
+    if (fp8_kind == F8B200_E4M3) F8_LAUNCH_B(HP, F8B200_E4M3, VEC); \
+    else F8_LAUNCH_B(HP, F8B200_E5M2, VEC);                         \
+  } while (0)
+  if (hp_dtype == F8B200_BF16) {
+    if (vec) F8_DISPATCH_B(F8B200_BF16, true); else F8_DISPATCH_B(F8B200_BF16, false);
+  } else if (hp_dtype == F8B200_FP16) {
+    if (vec) F8_DISPATCH_B(F8B200_FP16, true); else F8_DISPATCH_B(F8B200_FP16, false);
+  } else {
+    F8_DISPATCH_B(F8B200_FP32, false);
+  }
+#undef F8_DISPATCH_B
+#undef F8_LAUNCH_B
+  return check_launch();
+}

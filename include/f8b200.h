@@ -224,6 +224,30 @@ int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t lda, const
                                    int64_t m, int64_t n, int64_t k, int use_fast_accum, void* stream);
 
 /*
+ * RMSNorm fused into the dynamic fp8 cast of its output, in two launches that never write the
+ * normalised tensor: 5 bytes of HBM traffic per element instead of 9 (norm 2 + 2, cast 2 + 2 + 1).
+ *
+ *   y = RN_T( float(RN_T(x * rstd)) * w ),   rstd = 1 / sqrt(mean(x^2 over the row) + eps)
+ *
+ * with T = hp_dtype (x and weight share it) and the mean accumulated in fp32: RMSNorm.forward
+ * of float8_experimental/benchmarks/profile_linear_float8.py:69-74, the producer that the
+ * reference leaves to torch.compile to fuse with the cast (same file :129-149).
+ *
+ * f8b200_rmsnorm_amax  pass A: rstd_out[rows] (fp32) and amax_out[0] = max |y| (fp32; zeroed by
+ *                      the call).  Reads x once.
+ * f8b200_rmsnorm_cast  pass B: out = fp8(clamp(RN_T(y * scale))) with the scale derived from
+ *                      `amax` as in f8b200_cast(scale_src = 1); scale_out (optional) receives
+ *                      it.  Reads x once, writes the fp8 bytes (row stride ld_out).
+ * Between the two the caller may all-reduce amax (tensor / sequence parallel inputs).
+ */
+int f8b200_rmsnorm_amax(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                        const void* weight, float eps, float* rstd_out, float* amax_out,
+                        void* stream);
+int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                        const void* weight, const float* rstd, const float* amax, int fp8_kind,
+                        float* scale_out, void* out, int64_t ld_out, void* stream);
+
+/*
  * Reads and clears the device error word of the current device (synchronises the
  * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
  * last read; the result of that launch is undefined.  Test and debugging aid.

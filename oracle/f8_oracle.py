@@ -241,6 +241,62 @@ def dequant(bits: np.ndarray, fp8: str, scale, orig_dtype: str) -> np.ndarray:
 
 
 # ---------------------------------------------------------------------------
+# RMSNorm as the producer of a cast input
+# ---------------------------------------------------------------------------
+_NORM_THREADS = 256  # summation order of the row's sum of squares: 256 partial sums of 8-element chunks
+
+
+def rmsnorm_rstd(x: np.ndarray, dtype: str, eps: float) -> np.ndarray:
+    """1 / sqrt(mean(x^2) + eps) per row in fp32 with a FIXED summation order, so that the
+    result is reproducible to the bit: partial sum t adds fl(x*x) of the 8-element chunks c with
+    c % 256 == t in increasing order, the 256 partial sums are combined by xor butterflies
+    (offsets 16, 8, 4, 2, 1 inside each group of 32, then 4, 2, 1 over the 8 group sums).
+    `_norm` of float8_experimental/benchmarks/profile_linear_float8.py:69-70 with the
+    reduction order pinned."""
+    v = to_f32(x, dtype)
+    rows, cols = v.shape
+    chunks = -(-cols // 8)
+    iters = -(-chunks // _NORM_THREADS)
+    padded = np.zeros((rows, iters * _NORM_THREADS * 8), dtype=np.float32)
+    padded[:, :cols] = v
+    sq = (padded * padded).reshape(rows, iters, _NORM_THREADS, 8)  # fl(x*x)
+    part = np.zeros((rows, _NORM_THREADS), dtype=np.float32)
+    for it in range(iters):
+        for j in range(8):
+            part = part + sq[:, it, :, j]  # fp32 add, one element per partial sum at a time
+    lanes = part.reshape(rows, _NORM_THREADS // 32, 32)
+    idx = np.arange(32)
+    for off in (16, 8, 4, 2, 1):
+        lanes = lanes + lanes[:, :, idx ^ off]
+    warp = lanes[:, :, 0]  # every lane of a group holds the same sum
+    idx8 = np.arange(_NORM_THREADS // 32)
+    for off in (4, 2, 1):
+        warp = warp + warp[:, idx8 ^ off]
+    total = warp[:, 0]
+    mean = total / np.float32(cols)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return (np.float32(1.0) / np.sqrt(mean + np.float32(eps))).astype(np.float32)
+
+
+def rmsnorm(x: np.ndarray, dtype: str, weight: np.ndarray, eps: float):
+    """y = RN_T(float(RN_T(x * rstd)) * w): RMSNorm.forward of
+    float8_experimental/benchmarks/profile_linear_float8.py:72-74 for x and weight of one
+    dtype T.  Returns (y widened to float32, rstd)."""
+    rstd = rmsnorm_rstd(x, dtype, eps)
+    o = round_f32_to(to_f32(x, dtype) * rstd[:, None], dtype)
+    y = round_f32_to(o * to_f32(weight, dtype)[None, :], dtype)
+    return y, rstd
+
+
+def rmsnorm_cast_dynamic(x: np.ndarray, dtype: str, weight: np.ndarray, eps: float, fp8: str):
+    """The dynamic cast (float8_experimental/float8_scaling_utils.py:33-62) applied to the
+    RMSNorm output without materialising it.  Returns (bits, scale, amax, rstd)."""
+    y, rstd = rmsnorm(x, dtype, weight, eps)
+    bits, scale, amax = cast_dynamic(from_f32(y, dtype), dtype, fp8)
+    return bits, scale, amax, rstd
+
+
+# ---------------------------------------------------------------------------
 # delayed-scaling bookkeeping
 # ---------------------------------------------------------------------------
 def init_amax_history(amax: np.float32, history: np.ndarray, fp8: str, x_dtype: str):

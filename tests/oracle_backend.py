@@ -105,6 +105,25 @@ def _scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum):
     return res.to(out_dtype)
 
 
+def _rmsnorm_amax(x, weight, eps):
+    name = _HP[x.dtype]
+    cols = x.shape[-1]
+    y, rstd = O.rmsnorm(to_np(x).reshape(-1, cols), name, to_np(weight), eps)
+    amax = np.float32(np.nan) if np.isnan(y).any() else np.float32(np.abs(y).max())
+    return torch.from_numpy(rstd.copy()), torch.tensor(float(amax), dtype=torch.float32)
+
+
+def _rmsnorm_cast(x, weight, rstd, amax, fp8_kind):
+    name = _HP[x.dtype]
+    cols = x.shape[-1]
+    xf = O.to_f32(to_np(x).reshape(-1, cols), name)
+    o = O.round_f32_to(xf * rstd.numpy()[:, None], name)
+    y = O.round_f32_to(o * O.to_f32(to_np(weight), name)[None, :], name)
+    scale = np.float32(O.amax_to_scale(np.float32(amax.item()), _F8[fp8_kind], name, name))
+    bits = O.cast_to_fp8(O.from_f32(y, name), name, scale, _F8[fp8_kind], name)
+    return from_np(bits.reshape(tuple(x.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
+
+
 def install() -> None:
     """Registers the CPU stand-ins once per process."""
     global _installed
@@ -119,5 +138,7 @@ def install() -> None:
     lib.impl("transpose_fp8", _transpose_fp8, "CPU")
     lib.impl("delayed_sync", _delayed_sync, "CPU")
     lib.impl("scaled_mm", _scaled_mm, "CPU")
+    lib.impl("rmsnorm_amax", _rmsnorm_amax, "CPU")
+    lib.impl("rmsnorm_cast", _rmsnorm_cast, "CPU")
     install._lib = lib  # keep the registrations alive
     _installed = True

@@ -1,0 +1,82 @@
+"""The fused RMSNorm -> fp8 cast kernels against the oracle (bit-exact: 1/rms, amax, scale and
+every fp8 byte) and, at full size, against the unfused composition on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+from float8_experimental_b200._ops import ops
+from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic
+from float8_experimental_b200.float8_tensor import LinearMMConfig
+from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic
+from oracle import f8_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+_HP = {torch.bfloat16: O.BF16, torch.float16: O.FP16, torch.float32: O.FP32}
+
+
+def host_bits(t):
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.float32:
+        return t.numpy()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.view(torch.uint8).numpy()
+
+
+def reference_rmsnorm(x, weight, eps):
+    xf = x.float()
+    n = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return n.type_as(x) * weight
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(64, 8192), (7, 4096), (33, 520), (5, 7), (3, 4, 264), (300, 2048 + 8), (2, 16384 + 24)])
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fused_norm_kernels_match_oracle_bit_for_bit(dtype, shape, fp8):
+    g = torch.Generator().manual_seed(shape[-1] * 3 + shape[0])
+    x = (torch.randn(shape, generator=g) * 3).to(dtype)
+    x.view(-1)[::97] *= 40  # outliers: the amax sits on few elements
+    w = (1 + 0.2 * torch.randn(shape[-1], generator=g)).to(dtype)
+    name, kind = _HP[dtype], (O.E4M3 if fp8 == torch.float8_e4m3fn else O.E5M2)
+    bits, scale, amax, rstd = O.rmsnorm_cast_dynamic(host_bits(x).reshape(-1, shape[-1]), name, host_bits(w), 1e-6, kind)
+    xc, wc = x.cuda(), w.cuda()
+    rstd_g, amax_g = ops.rmsnorm_amax(xc, wc, 1e-6)
+    assert np.array_equal(rstd_g.cpu().numpy().view(np.uint32), rstd.view(np.uint32))
+    assert amax_g.item() == float(amax)
+    out = rms_norm_to_float8_dynamic(xc, wc, 1e-6, fp8)
+    assert out._scale.item() == float(scale)
+    assert out._data.shape == x.shape
+    assert np.array_equal(host_bits(out._data).reshape(-1), bits.reshape(-1))
+
+
+def test_fused_norm_strided_rows_and_nan():
+    base = torch.randn(40, 1024 + 64, device="cuda").to(torch.bfloat16)
+    x = base[:, :1024]  # row pitch 1088 elements
+    w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    a = rms_norm_to_float8_dynamic(x, w, 1e-6)
+    b = rms_norm_to_float8_dynamic(x.contiguous(), w, 1e-6)
+    assert torch.equal(a._data.view(torch.uint8), b._data.view(torch.uint8)) and a._scale.item() == b._scale.item()
+    x2 = x.contiguous().clone()
+    x2[3, 5] = float("nan")
+    c = rms_norm_to_float8_dynamic(x2, w, 1e-6)
+    assert torch.isnan(c._scale).item()  # NaN amax -> NaN scale, as in the unfused path
+    assert (c._data.view(torch.uint8)[3] & 0x7F == 0x7F).all().item()
+
+
+def test_fused_norm_full_size_against_unfused_composition():
+    """16384 x 8192 bf16 (the activation of the LLaMa-2-70B shapes): the oracle is too slow, so
+    compare with RMSNorm in eager mode followed by the unfused dynamic cast.  The two differ only
+    through the last bit of 1/rms."""
+    torch.manual_seed(11)
+    x = torch.randn(16384, 8192, device="cuda", dtype=torch.bfloat16) * 1.7
+    w = (1 + 0.1 * torch.randn(8192, device="cuda")).to(torch.bfloat16)
+    fused = rms_norm_to_float8_dynamic(x, w, 1e-6)
+    unfused = hp_tensor_to_float8_dynamic(reference_rmsnorm(x, w, 1e-6), torch.float8_e4m3fn, LinearMMConfig())
+    a, b = fused._data.view(torch.uint8), unfused._data.view(torch.uint8)
+    assert fused._scale.item() == unfused._scale.item()
+    assert (a != b).float().mean().item() <= 1e-3
+    assert (a.int() - b.int()).abs().max().item() <= 1
+    # idempotence of the cast half: casting the dequantised result with the same scale returns the bytes
+    again = hp_tensor_to_float8_dynamic(fused.to_original_precision(), torch.float8_e4m3fn, LinearMMConfig())
+    assert again._scale.item() == fused._scale.item()
