@@ -211,6 +211,40 @@ def measure_delayed(torch, f8, _native, dev, x):
                                    if TRANSPOSED_COPIES else "3 B per element: 2 read + 1 fp8, amax from the same read")}
 
 
+def measure_fused_norm(torch, dev, x):
+    """RMSNorm fused into the dynamic cast (two launches, 5 B per element: x read twice, fp8
+    written once) against the unfused sequence on the same [16384, 8192] bf16 activation: RMSNorm
+    in eager mode, then this library's amax and cast kernels."""
+    from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic
+    from float8_experimental_b200.float8_tensor import LinearMMConfig
+    from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic
+
+    w = torch.ones(x.shape[-1], device=dev, dtype=x.dtype)
+    cfg = LinearMMConfig()
+
+    def unfused():
+        xf = x.float()
+        y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(x) * w
+        return hp_tensor_to_float8_dynamic(y, torch.float8_e4m3fn, cfg)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(20):
+            fn()
+        s1.record()
+        torch.cuda.synchronize()
+        return s0.elapsed_time(s1) / 20
+
+    fused_ms = timed(lambda: rms_norm_to_float8_dynamic(x, w, 1e-6))
+    unfused_ms = timed(unfused)
+    return {"shape": list(x.shape), "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
+            "fused_bytes": "5 B per element: 2 read (1/rms + amax pass) + 2 read + 1 fp8 written (cast pass)",
+            "unfused_eager_norm_then_cast_ms": unfused_ms}
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -376,6 +410,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     delayed = None
     if rank == 0 and world == 1:
         delayed = measure_delayed(torch, f8, _native, dev, xs[0].detach())
+    fused_norm = None
+    if rank == 0 and world == 1 and shapes[0][1] == 8192:
+        fused_norm = measure_fused_norm(torch, dev, xs[0].detach())
 
     # ---- library kernel to beat, outside every timed region -----------------
     cublaslt = None
@@ -482,6 +519,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                                    "amax": amax_ms / args.steps},
         "cublaslt_fp8_tflops_wo_fwd": cublaslt,
         "delayed_scaling": delayed,
+        "fused_rmsnorm_cast": fused_norm,
         "cpu_baseline": cpu_baseline,
     }
     print(json.dumps(line), flush=True)

@@ -162,6 +162,166 @@ rmsnorm_cast_kernel(const char* __restrict__ x, int64_t ld_bytes, int64_t rows, 
   }
 }
 
+// ---- fast path: 16-bit dtypes, rows of at most CH * 2048 elements held in registers --------
+// Same arithmetic as above with fewer instructions: x*x is exact in fp32 for 16-bit inputs, so
+// fma(x, x, ss) equals fl(ss + fl(x*x)); RN_T of two products is one packed convert; the product of
+// two T values rounded to T is one packed multiply (the exact product fits fp32), which covers both
+// "* w" and "* scale" (the scale is derived in T arithmetic, hence representable in T).
+template <int HP>
+__device__ __forceinline__ uint32_t pack_round2(float a, float b) {
+  if constexpr (HP == F8B200_BF16) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&p);
+  } else {
+    const __half2 p = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&p);
+  }
+}
+template <int HP>
+__device__ __forceinline__ uint32_t mul2(uint32_t a2, uint32_t b2) {
+  if constexpr (HP == F8B200_BF16) {
+    const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a2),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b2));
+    return *reinterpret_cast<const uint32_t*>(&p);
+  } else {
+    const __half2 p = __hmul2(*reinterpret_cast<const __half2*>(&a2), *reinterpret_cast<const __half2*>(&b2));
+    return *reinterpret_cast<const uint32_t*>(&p);
+  }
+}
+template <int HP>
+__device__ __forceinline__ void unpack_pair(uint32_t x2, float& a, float& b) {
+  if constexpr (HP == F8B200_BF16) {
+    a = __uint_as_float(x2 << 16);
+    b = __uint_as_float(x2 & 0xFFFF0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x2));
+    a = f.x;
+    b = f.y;
+  }
+}
+// y (two packed T values) of two packed x values
+template <int HP>
+__device__ __forceinline__ uint32_t norm_pair(uint32_t x2, float rstd, uint32_t w2) {
+  float a, b;
+  unpack_pair<HP>(x2, a, b);
+  return mul2<HP>(pack_round2<HP>(__fmul_rn(a, rstd), __fmul_rn(b, rstd)), w2);
+}
+template <int HP>
+__device__ __forceinline__ float sumsq_word(uint32_t x2, float ss) {
+  float a, b;
+  unpack_pair<HP>(x2, a, b);
+  return fmaf(b, b, fmaf(a, a, ss));
+}
+template <int HP, int KIND>
+__device__ __forceinline__ uint32_t pair_to_fp8(uint32_t y2, uint32_t s2) {
+  const uint32_t p = mul2<HP>(y2, s2);
+  if constexpr (HP == F8B200_BF16) {
+    return cvt_pair_raw<KIND>(__uint_as_float(p << 16), __uint_as_float(p & 0xFFFF0000u));
+  } else {
+    const __nv_fp8_interpretation_t interp = (KIND == F8B200_E4M3) ? __NV_E4M3 : __NV_E5M2;
+    __half2_raw r;
+    r.x = (unsigned short)(p & 0xFFFFu);
+    r.y = (unsigned short)(p >> 16);
+    return __nv_cvt_halfraw2_to_fp8x2(r, __NV_SATFINITE, interp);
+  }
+}
+
+template <int HP, int CH>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_amax_fast_kernel(const char* __restrict__ x, int64_t ld_bytes, int64_t rows, int64_t cols,
+                         const char* __restrict__ weight, float eps, float* __restrict__ rstd_out,
+                         uint32_t* __restrict__ amax_bits) {
+  __shared__ float red[kNormThreads / 32];
+  __shared__ uint32_t redu[kNormThreads / 32];
+  const int chunks = (int)(cols / 8);
+  uint4 wq[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    wq[i] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(weight) + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  uint32_t amax2 = 0;  // packed unsigned max over |y| bit patterns
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + r * ld_bytes);
+    uint4 q[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      q[i] = c < chunks ? __ldcs(row + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      ss = sumsq_word<HP>(q[i].x, ss);
+      ss = sumsq_word<HP>(q[i].y, ss);
+      ss = sumsq_word<HP>(q[i].z, ss);
+      ss = sumsq_word<HP>(q[i].w, ss);
+    }
+    const float total = block_sum_fixed(ss, red);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)cols), eps)));
+    if (threadIdx.x == 0) rstd_out[r] = rstd;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      amax2 = __vmaxu2(amax2, norm_pair<HP>(q[i].x, rstd, wq[i].x) & 0x7FFF7FFFu);
+      amax2 = __vmaxu2(amax2, norm_pair<HP>(q[i].y, rstd, wq[i].y) & 0x7FFF7FFFu);
+      amax2 = __vmaxu2(amax2, norm_pair<HP>(q[i].z, rstd, wq[i].z) & 0x7FFF7FFFu);
+      amax2 = __vmaxu2(amax2, norm_pair<HP>(q[i].w, rstd, wq[i].w) & 0x7FFF7FFFu);
+    }
+  }
+  // widen the larger 16-bit pattern to fp32 bits (order-preserving for |y|, NaN stays NaN)
+  const uint32_t h = max(amax2 & 0xFFFFu, amax2 >> 16);
+  uint32_t amax = HP == F8B200_BF16 ? (h << 16) : __float_as_uint(__half2float(__ushort_as_half((unsigned short)h)));
+  amax = warp_max_u32(amax);
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  if (lane == 0) redu[wp] = amax;
+  __syncthreads();
+  if (wp == 0) {
+    amax = lane < (kNormThreads / 32) ? redu[lane] : 0u;
+    amax = warp_max_u32(amax);
+    if (lane == 0 && amax > *reinterpret_cast<volatile uint32_t*>(amax_bits)) atomicMax(amax_bits, amax);
+  }
+}
+
+template <int HP, int KIND, int CH>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_cast_fast_kernel(const char* __restrict__ x, int64_t ld_bytes, int64_t rows, int64_t cols,
+                         const char* __restrict__ weight, const float* __restrict__ rstd_in,
+                         const float* __restrict__ amax_in, float* __restrict__ scale_out,
+                         uint8_t* __restrict__ out, int64_t ld_out) {
+  const float scale = amax_to_scale_dev(__ldg(amax_in), fp8_max_of(KIND), HP, HP == F8B200_FP16);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) *scale_out = scale;
+  const uint32_t s2 = pack_round2<HP>(scale, scale);  // exact: the scale is a value of T
+  const int chunks = (int)(cols / 8);
+  uint4 wq[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    wq[i] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(weight) + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + r * ld_bytes);
+    const float rstd = __ldg(rstd_in + r);
+    uint2* orow = reinterpret_cast<uint2*>(out + r * ld_out);
+    uint4 q[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      q[i] = c < chunks ? __ldcs(row + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      if (c < chunks) {
+        const uint32_t lo = pair_to_fp8<HP, KIND>(norm_pair<HP>(q[i].x, rstd, wq[i].x), s2) |
+                            (pair_to_fp8<HP, KIND>(norm_pair<HP>(q[i].y, rstd, wq[i].y), s2) << 16);
+        const uint32_t hi = pair_to_fp8<HP, KIND>(norm_pair<HP>(q[i].z, rstd, wq[i].z), s2) |
+                            (pair_to_fp8<HP, KIND>(norm_pair<HP>(q[i].w, rstd, wq[i].w), s2) << 16);
+        orow[c] = make_uint2(lo, hi);
+      }
+    }
+  }
+}
+
 int norm_grid(int64_t rows) {
   const int64_t cap = (int64_t)sm_count() * 8;
   return (int)(rows < cap ? rows : cap);
@@ -188,6 +348,21 @@ extern "C" int f8b200_rmsnorm_amax(const void* x, int hp_dtype, int64_t rows, in
   const char* wp = static_cast<const char*>(weight);
   uint32_t* ab = reinterpret_cast<uint32_t*>(amax_out);
   const int grid = norm_grid(rows);
+  if (vec && cols <= 4 * 2048) {
+    const int64_t ldb = ld_x * es;
+#define F8_FAST_A(HP, CH) \
+  rmsnorm_amax_fast_kernel<HP, CH><<<grid, kNormThreads, 0, st>>>(xp, ldb, rows, cols, wp, eps, rstd_out, ab)
+#define F8_FAST_A_CH(HP)                        \
+  do {                                          \
+    if (cols <= 2048) F8_FAST_A(HP, 1);         \
+    else if (cols <= 4096) F8_FAST_A(HP, 2);    \
+    else F8_FAST_A(HP, 4);                      \
+  } while (0)
+    if (hp_dtype == F8B200_BF16) F8_FAST_A_CH(F8B200_BF16); else F8_FAST_A_CH(F8B200_FP16);
+#undef F8_FAST_A_CH
+#undef F8_FAST_A
+    return check_launch();
+  }
 #define F8_LAUNCH_A(HP, VEC) \
   rmsnorm_amax_kernel<HP, VEC><<<grid, kNormThreads, 0, st>>>(xp, ld_x * es, rows, cols, wp, eps, rstd_out, ab)
   if (hp_dtype == F8B200_BF16) {
@@ -218,6 +393,26 @@ extern "C" int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, in
   const char* wp = static_cast<const char*>(weight);
   uint8_t* op = static_cast<uint8_t*>(out);
   const int grid = norm_grid(rows);
+  if (vec && cols <= 4 * 2048) {
+    const int64_t ldb = ld_x * es;
+#define F8_FAST_B(HP, KIND, CH)                                                                                   \
+  rmsnorm_cast_fast_kernel<HP, KIND, CH><<<grid, kNormThreads, 0, st>>>(xp, ldb, rows, cols, wp, rstd, amax, \
+                                                                         scale_out, op, ld_out)
+#define F8_FAST_B_CH(HP, KIND)                      \
+  do {                                              \
+    if (cols <= 2048) F8_FAST_B(HP, KIND, 1);       \
+    else if (cols <= 4096) F8_FAST_B(HP, KIND, 2);  \
+    else F8_FAST_B(HP, KIND, 4);                    \
+  } while (0)
+    if (hp_dtype == F8B200_BF16) {
+      if (fp8_kind == F8B200_E4M3) F8_FAST_B_CH(F8B200_BF16, F8B200_E4M3); else F8_FAST_B_CH(F8B200_BF16, F8B200_E5M2);
+    } else {
+      if (fp8_kind == F8B200_E4M3) F8_FAST_B_CH(F8B200_FP16, F8B200_E4M3); else F8_FAST_B_CH(F8B200_FP16, F8B200_E5M2);
+    }
+#undef F8_FAST_B_CH
+#undef F8_FAST_B
+    return check_launch();
+  }
 #define F8_LAUNCH_B(HP, KIND, VEC)                                                                                 \
   rmsnorm_cast_kernel<HP, KIND, VEC><<<grid, kNormThreads, 0, st>>>(xp, ld_x * es, rows, cols, wp, rstd, amax, \
                                                                      scale_out, op, ld_out)
