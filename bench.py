@@ -535,10 +535,12 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", default=None, help="comma list out of wqkv,wo,w13,w2 (default: all four)")
-    ap.add_argument("--fsdp-root", type=int, default=0,
-                    help="N > 1: 0 = each layer is its own FSDP2 root (collectives run between the GEMMs), 1 = the "
-                         "four layers share one root (all-gather prefetch overlaps the GEMMs).  Measured on 2 and 8 "
-                         "GPUs the overlap does not pay on a power-capped part: 43.8 against 46.6 ms/step at N=8.")
+    ap.add_argument("--fsdp-root", type=int, default=1,
+                    help="N > 1: 1 = the four layers are children of one FSDP2 root (they reshard after forward, so "
+                         "every weight is cast and all-gathered before forward and again before backward, and the "
+                         "next layer's all-gather is prefetched under the current layer's GEMMs); 0 = each layer is "
+                         "its own root (a root keeps its gathered weight: one all-gather per layer and step, nothing "
+                         "overlaps).  Measured at N=8: 41.0 against 41.2 ms/step.")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed part only, short JSON; for profiler captures of a small case")
     args = ap.parse_args()
