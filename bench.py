@@ -240,9 +240,19 @@ def measure_fused_norm(torch, dev, x):
 
     fused_ms = timed(lambda: rms_norm_to_float8_dynamic(x, w, 1e-6))
     unfused_ms = timed(unfused)
+    # SwiGLU gate of the LLaMa-2-70B FFN: a, b = halves of the fused w1|w3 output [16384, 57344]
+    from float8_experimental_b200.fused_norm import swiglu_to_float8_dynamic
+
+    h = torch.randn(x.shape[0], 57344, device=dev, dtype=x.dtype)
+    a, b = h[:, :28672], h[:, 28672:]
+    glu_ms = timed(lambda: swiglu_to_float8_dynamic(a, b))
+    glu_unfused_ms = timed(lambda: hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, cfg))
     return {"shape": list(x.shape), "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
             "fused_bytes": "5 B per element: 2 read (1/rms + amax pass) + 2 read + 1 fp8 written (cast pass)",
-            "unfused_eager_norm_then_cast_ms": unfused_ms}
+            "unfused_eager_norm_then_cast_ms": unfused_ms,
+            "swiglu": {"shape": list(a.shape), "fused_ms": glu_ms, "fused_gbs": 9.0 * a.numel() / (glu_ms * 1e-3) / 1e9,
+                       "fused_bytes": "9 B per element: a and b read by both passes (4 + 4), fp8 written once",
+                       "unfused_eager_silu_mul_then_cast_ms": glu_unfused_ms}}
 
 
 # ---------------------------------------------------------------------------

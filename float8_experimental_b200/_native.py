@@ -37,6 +37,8 @@ EXPORTS = (
     "f8b200_gemm_fp8_static_scratch",
     "f8b200_rmsnorm_amax",
     "f8b200_rmsnorm_cast",
+    "f8b200_swiglu_amax",
+    "f8b200_swiglu_cast",
     "f8b200_read_device_error",
 )
 
@@ -78,6 +80,8 @@ def load() -> ctypes.CDLL:
                                        i32, vp, i64, vp]
     lib.f8b200_rmsnorm_amax.argtypes = [vp, i32, i64, i64, i64, vp, ctypes.c_float, vp, vp, vp]
     lib.f8b200_rmsnorm_cast.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.f8b200_swiglu_amax.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, vp]
+    lib.f8b200_swiglu_cast.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i32, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
         fn = getattr(lib, name)
@@ -308,8 +312,6 @@ def gemm_fp8_static_scratch(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int
                                                   _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo, m, n, k,
                                                   int(use_fast_accum), _stream(a)),
             "f8b200_gemm_fp8_static_scratch",
-    "f8b200_rmsnorm_amax",
-    "f8b200_rmsnorm_cast",
         )
 
 
@@ -333,6 +335,29 @@ def rmsnorm_cast(x: torch.Tensor, rows: int, cols: int, ld: int, weight: torch.T
                                        rstd.data_ptr(), amax.data_ptr(), fp8_code(out.dtype), _ptr(scale_out),
                                        out.data_ptr(), ld_out, _stream(x)),
             "f8b200_rmsnorm_cast",
+        )
+
+
+def swiglu_amax(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int,
+                amax_out: torch.Tensor) -> None:
+    _require_cuda(a, b, amax_out)
+    with _Launch("glu_amax", a.device):
+        _check(
+            load().f8b200_swiglu_amax(a.data_ptr(), b.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b,
+                                      amax_out.data_ptr(), _stream(a)),
+            "f8b200_swiglu_amax",
+        )
+
+
+def swiglu_cast(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int, amax: torch.Tensor,
+                scale_out: Optional[torch.Tensor], out: torch.Tensor, ld_out: int) -> None:
+    _require_cuda(a, b, amax, scale_out, out)
+    with _Launch("glu_cast", a.device):
+        _check(
+            load().f8b200_swiglu_cast(a.data_ptr(), b.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b,
+                                      amax.data_ptr(), fp8_code(out.dtype), _ptr(scale_out), out.data_ptr(), ld_out,
+                                      _stream(a)),
+            "f8b200_swiglu_cast",
         )
 
 

@@ -16,6 +16,8 @@ Ops (namespace `f8b200`):
   scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum) -> out
   rmsnorm_amax(x, weight, eps) -> (rstd fp32 [rows], amax fp32 0-dim)      f8b200_rmsnorm_amax
   rmsnorm_cast(x, weight, rstd, amax, kind) -> (data, scale)               f8b200_rmsnorm_cast
+  swiglu_amax(a, b) -> amax fp32 0-dim                                     f8b200_swiglu_amax
+  swiglu_cast(a, b, amax, kind) -> (data, scale)                           f8b200_swiglu_cast
 """
 from __future__ import annotations
 
@@ -46,6 +48,8 @@ _lib.define(
 )
 _lib.define("rmsnorm_amax(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _lib.define("rmsnorm_cast(Tensor x, Tensor weight, Tensor rstd, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
+_lib.define("swiglu_amax(Tensor a, Tensor b) -> Tensor")
+_lib.define("swiglu_cast(Tensor a, Tensor b, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 
 
 def _as_matrix(x: torch.Tensor) -> Tuple[torch.Tensor, int, int, int]:
@@ -183,6 +187,31 @@ def _rmsnorm_cast_cuda(x, weight, rstd, amax, fp8_kind: int):
     return data, scale
 
 
+def _glu_operands(a, b):
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise RuntimeError("swiglu: a and b must have one shape and dtype")
+    am, rows, cols, lda = _as_matrix(a)
+    bm, _, _, ldb = _as_matrix(b)
+    return am, bm, rows, cols, lda, ldb
+
+
+def _swiglu_amax_cuda(a, b):
+    am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
+    amax = torch.empty((), dtype=torch.float32, device=a.device)
+    N.swiglu_amax(am, bm, rows, cols, lda, ldb, amax)
+    return amax
+
+
+def _swiglu_cast_cuda(a, b, amax, fp8_kind: int):
+    am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
+    data = _empty_like_shape(a, N.FP8_DTYPE[fp8_kind])
+    scale = torch.empty((), dtype=torch.float32, device=a.device)
+    N.swiglu_cast(am, bm, rows, cols, lda, ldb, amax, scale, data, cols)
+    return data, scale
+
+
+_lib.impl("swiglu_amax", _swiglu_amax_cuda, "CUDA")
+_lib.impl("swiglu_cast", _swiglu_cast_cuda, "CUDA")
 _lib.impl("rmsnorm_amax", _rmsnorm_amax_cuda, "CUDA")
 _lib.impl("rmsnorm_cast", _rmsnorm_cast_cuda, "CUDA")
 _lib.impl("amax", _amax_cuda, "CUDA")
@@ -199,6 +228,16 @@ _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 # fake (meta) implementations: shapes and dtypes only, so torch.compile can trace
 # around the opaque ops
 # ---------------------------------------------------------------------------
+@torch.library.register_fake("f8b200::swiglu_amax")
+def _swiglu_amax_fake(a, b):
+    return a.new_empty((), dtype=torch.float32)
+
+
+@torch.library.register_fake("f8b200::swiglu_cast")
+def _swiglu_cast_fake(a, b, amax, fp8_kind):
+    return a.new_empty(a.shape, dtype=N.FP8_DTYPE[fp8_kind]), a.new_empty((), dtype=torch.float32)
+
+
 @torch.library.register_fake("f8b200::rmsnorm_amax")
 def _rmsnorm_amax_fake(x, weight, eps):
     cols = x.shape[-1]

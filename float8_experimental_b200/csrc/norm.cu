@@ -432,3 +432,207 @@ extern "C" int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, in
 #undef F8_LAUNCH_B
   return check_launch();
 }
+
+// ===========================================================================
+// SwiGLU gate fused into the dynamic fp8 cast of its output: y = RN_T(RN_T(silu(a)) * b),
+// silu(a) = a / (1 + exp(-a)) in fp32, which is `F.silu(self.w1(x)) * self.w3(x)` of
+// float8_experimental/benchmarks/profile_linear_float8.py:117-118, the producer of the input of
+// the w2 linear.  Unfused: silu 2 + 2, multiply 2 + 2 + 2, cast 2 + 2 + 1 = 17 bytes per element;
+// here pass A reads a and b for the amax of y (4), pass B reads them again and writes fp8 (4 + 1).
+// ===========================================================================
+namespace f8b200 {
+namespace {
+
+__device__ __forceinline__ float silu_f32(float a) { return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a))); }
+
+template <int HP>
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t a2, uint32_t b2) {
+  float a0, a1;
+  unpack_pair<HP>(a2, a0, a1);
+  return mul2<HP>(pack_round2<HP>(silu_f32(a0), silu_f32(a1)), b2);
+}
+
+template <int HP>
+__device__ __forceinline__ float swiglu_value(float a, float b) {
+  return round_hp<HP>(__fmul_rn(round_hp<HP>(silu_f32(a)), b));
+}
+
+constexpr int kGluThreads = 256;
+
+// 16-bit dtypes, 8 elements per thread and step; rows x cols with separate row pitches for a and b
+// (the two halves of one fused w1|w3 output are the usual case).
+template <int HP>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_amax_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda_bytes, int64_t ldb_bytes,
+                        int64_t rows, int64_t chunks_per_row, uint32_t* __restrict__ amax_bits) {
+  __shared__ uint32_t redu[kGluThreads / 32];
+  const int64_t total = rows * chunks_per_row;
+  uint32_t amax2 = 0;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+    const uint4 qa = __ldcs(reinterpret_cast<const uint4*>(a + r * lda_bytes) + c);
+    const uint4 qb = __ldcs(reinterpret_cast<const uint4*>(b + r * ldb_bytes) + c);
+    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.x, qb.x) & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.y, qb.y) & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.z, qb.z) & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.w, qb.w) & 0x7FFF7FFFu);
+  }
+  const uint32_t h = max(amax2 & 0xFFFFu, amax2 >> 16);
+  uint32_t amax = HP == F8B200_BF16 ? (h << 16) : __float_as_uint(__half2float(__ushort_as_half((unsigned short)h)));
+  amax = warp_max_u32(amax);
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  if (lane == 0) redu[wp] = amax;
+  __syncthreads();
+  if (wp == 0) {
+    amax = lane < (kGluThreads / 32) ? redu[lane] : 0u;
+    amax = warp_max_u32(amax);
+    if (lane == 0 && amax > *reinterpret_cast<volatile uint32_t*>(amax_bits)) atomicMax(amax_bits, amax);
+  }
+}
+
+template <int HP, int KIND>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_cast_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda_bytes, int64_t ldb_bytes,
+                        int64_t rows, int64_t chunks_per_row, const float* __restrict__ amax_in,
+                        float* __restrict__ scale_out, uint8_t* __restrict__ out, int64_t ld_out) {
+  const float scale = amax_to_scale_dev(__ldg(amax_in), fp8_max_of(KIND), HP, HP == F8B200_FP16);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) *scale_out = scale;
+  const uint32_t s2 = pack_round2<HP>(scale, scale);
+  const int64_t total = rows * chunks_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+    const uint4 qa = __ldcs(reinterpret_cast<const uint4*>(a + r * lda_bytes) + c);
+    const uint4 qb = __ldcs(reinterpret_cast<const uint4*>(b + r * ldb_bytes) + c);
+    const uint32_t lo = pair_to_fp8<HP, KIND>(swiglu_pair<HP>(qa.x, qb.x), s2) |
+                        (pair_to_fp8<HP, KIND>(swiglu_pair<HP>(qa.y, qb.y), s2) << 16);
+    const uint32_t hi = pair_to_fp8<HP, KIND>(swiglu_pair<HP>(qa.z, qb.z), s2) |
+                        (pair_to_fp8<HP, KIND>(swiglu_pair<HP>(qa.w, qb.w), s2) << 16);
+    reinterpret_cast<uint2*>(out + r * ld_out)[c] = make_uint2(lo, hi);
+  }
+}
+
+// Any dtype, shape and alignment: one element per thread and step.
+template <int HP>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_amax_generic_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda, int64_t ldb,
+                           int64_t rows, int64_t cols, uint32_t* __restrict__ amax_bits) {
+  __shared__ uint32_t redu[kGluThreads / 32];
+  const int64_t total = rows * cols;
+  uint32_t amax = 0;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / cols, c = i - r * cols;
+    amax = max(amax, abs_bits(swiglu_value<HP>(load_hp<HP>(a, r * lda + c), load_hp<HP>(b, r * ldb + c))));
+  }
+  amax = warp_max_u32(amax);
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  if (lane == 0) redu[wp] = amax;
+  __syncthreads();
+  if (wp == 0) {
+    amax = lane < (kGluThreads / 32) ? redu[lane] : 0u;
+    amax = warp_max_u32(amax);
+    if (lane == 0 && amax > *reinterpret_cast<volatile uint32_t*>(amax_bits)) atomicMax(amax_bits, amax);
+  }
+}
+
+template <int HP, int KIND>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_cast_generic_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda, int64_t ldb,
+                           int64_t rows, int64_t cols, const float* __restrict__ amax_in,
+                           float* __restrict__ scale_out, uint8_t* __restrict__ out, int64_t ld_out) {
+  const float scale = amax_to_scale_dev(__ldg(amax_in), fp8_max_of(KIND), HP, HP == F8B200_FP16);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) *scale_out = scale;
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float q = __fmul_rn(swiglu_value<HP>(load_hp<HP>(a, r * lda + c), load_hp<HP>(b, r * ldb + c)), scale);
+    out[r * ld_out + c] = (uint8_t)(cast4<HP, KIND>(q, 0.f, 0.f, 0.f, HP != F8B200_FP32) & 0xFFu);
+  }
+}
+
+int glu_grid(int64_t work_items) {
+  const int64_t need = (work_items + kGluThreads - 1) / kGluThreads;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (int)(need < cap ? (need < 1 ? 1 : need) : cap);
+}
+
+bool glu_vec_ok(int hp_dtype, int64_t cols, int64_t lda, int64_t ldb, const void* a, const void* b) {
+  return hp_size_of(hp_dtype) == 2 && cols % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 &&
+         reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0;
+}
+
+}  // namespace
+}  // namespace f8b200
+
+extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
+                                  int64_t ld_b, float* amax_out, void* stream) {
+  if (a == nullptr || b == nullptr || amax_out == nullptr) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2 || rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), st);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const char* ap = static_cast<const char*>(a);
+  const char* bp = static_cast<const char*>(b);
+  uint32_t* ab = reinterpret_cast<uint32_t*>(amax_out);
+  if (glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b)) {
+    const int64_t cpr = cols / 8;
+    const int grid = glu_grid(rows * cpr);
+    if (hp_dtype == F8B200_BF16)
+      swiglu_amax_fast_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab);
+    else
+      swiglu_amax_fast_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab);
+    return check_launch();
+  }
+  const int grid = glu_grid(rows * cols);
+  if (hp_dtype == F8B200_BF16)
+    swiglu_amax_generic_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+  else if (hp_dtype == F8B200_FP16)
+    swiglu_amax_generic_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+  else
+    swiglu_amax_generic_kernel<F8B200_FP32><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+  return check_launch();
+}
+
+extern "C" int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
+                                  int64_t ld_b, const float* amax, int fp8_kind, float* scale_out, void* out,
+                                  int64_t ld_out, void* stream) {
+  if (a == nullptr || b == nullptr || amax == nullptr || out == nullptr) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype < 0 || hp_dtype > 2 || fp8_kind < 0 || fp8_kind > 1) return F8B200_ERR_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols || ld_out < cols) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* ap = static_cast<const char*>(a);
+  const char* bp = static_cast<const char*>(b);
+  uint8_t* op = static_cast<uint8_t*>(out);
+  if (glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b) && ld_out % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0) {
+    const int64_t cpr = cols / 8;
+    const int grid = glu_grid(rows * cpr);
+#define F8_GLU_FAST(HP, KIND)                                                                                    \
+  swiglu_cast_fast_kernel<HP, KIND><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, amax, \
+                                                                   scale_out, op, ld_out)
+    if (hp_dtype == F8B200_BF16) {
+      if (fp8_kind == F8B200_E4M3) F8_GLU_FAST(F8B200_BF16, F8B200_E4M3); else F8_GLU_FAST(F8B200_BF16, F8B200_E5M2);
+    } else {
+      if (fp8_kind == F8B200_E4M3) F8_GLU_FAST(F8B200_FP16, F8B200_E4M3); else F8_GLU_FAST(F8B200_FP16, F8B200_E5M2);
+    }
+#undef F8_GLU_FAST
+    return check_launch();
+  }
+  const int grid = glu_grid(rows * cols);
+#define F8_GLU_GEN(HP, KIND)                                                                                  \
+  swiglu_cast_generic_kernel<HP, KIND><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, amax, \
+                                                                      scale_out, op, ld_out)
+#define F8_GLU_GEN_K(HP)                                              \
+  do {                                                                \
+    if (fp8_kind == F8B200_E4M3) F8_GLU_GEN(HP, F8B200_E4M3);         \
+    else F8_GLU_GEN(HP, F8B200_E5M2);                                 \
+  } while (0)
+  if (hp_dtype == F8B200_BF16) F8_GLU_GEN_K(F8B200_BF16);
+  else if (hp_dtype == F8B200_FP16) F8_GLU_GEN_K(F8B200_FP16);
+  else F8_GLU_GEN_K(F8B200_FP32);
+#undef F8_GLU_GEN_K
+#undef F8_GLU_GEN
+  return check_launch();
+}

@@ -1,4 +1,4 @@
-"""RMSNorm fused into the dynamic fp8 cast of its output.
+"""Producers fused into the dynamic fp8 cast of their output: RMSNorm and the SwiGLU gate.
 
 The reference models the start of a transformer block as RMSNorm -> Float8Linear
 (float8_experimental/benchmarks/profile_linear_float8.py:52-74,129-149) and leaves it to
@@ -12,6 +12,9 @@ reaches memory: 5 bytes of traffic per element instead of 9.
 the two agree on the last bit of 1/rms, see `tests/test_fused_norm_gpu.py`); a `Float8Linear`
 takes it as an already-cast input, as it does for tensor-parallel inputs
 (float8_experimental/float8_linear.py:240-262).
+
+`swiglu_to_float8_dynamic(a, b, ...)` does the same for the FFN gate `silu(a) * b` that feeds
+the w2 linear (profile_linear_float8.py:117-118): 9 bytes per element instead of 17.
 """
 from __future__ import annotations
 
@@ -22,7 +25,7 @@ from ._ops import ops
 from .float8_tensor import Float8Tensor, GemmInputRole, LinearMMConfig
 from .float8_utils import _kind, e4m3_dtype
 
-__all__ = ["rms_norm_to_float8_dynamic", "Float8RMSNorm"]
+__all__ = ["rms_norm_to_float8_dynamic", "Float8RMSNorm", "swiglu_to_float8_dynamic"]
 
 
 class _RMSNormToFloat8(torch.autograd.Function):
@@ -86,3 +89,40 @@ class Float8RMSNorm(torch.nn.Module):
 
     def reset_parameters(self):
         torch.nn.init.ones_(self.weight)
+
+
+class _SwiGLUToFloat8(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, float8_dtype, linear_mm_config, gemm_input_role, reduce_amax):
+        amax = ops.swiglu_amax(a, b)
+        if reduce_amax and dist.is_initialized():
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+        data, scale = ops.swiglu_cast(a, b, amax, _kind(float8_dtype))
+        ctx.save_for_backward(a, b)
+        return Float8Tensor(data, scale, a.dtype, linear_mm_config, gemm_input_role)
+
+    @staticmethod
+    def backward(ctx, g):
+        # y = silu(a) * b:  dy/db = silu(a),  dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))
+        a, b = ctx.saved_tensors
+        a32, g32 = a.float(), g.reshape(a.shape).float()
+        sig = torch.sigmoid(a32)
+        silu = a32 * sig
+        da = g32 * b.float() * (sig * (1 + a32 * (1 - sig)))
+        db = g32 * silu.to(a.dtype).float()
+        return da.to(a.dtype), db.to(b.dtype), None, None, None, None
+
+
+def swiglu_to_float8_dynamic(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    float8_dtype: torch.dtype = e4m3_dtype,
+    linear_mm_config: LinearMMConfig = None,
+    gemm_input_role: GemmInputRole = GemmInputRole.INPUT,
+    reduce_amax: bool = False,
+) -> Float8Tensor:
+    """fp8(silu(a) * b) with a dynamic per-tensor scale, without materialising the product.
+    `a` and `b` share shape and dtype; they may be column slices of one fused w1|w3 output."""
+    if a.numel() == 0:
+        raise RuntimeError("swiglu_to_float8_dynamic: empty input (amax of an empty tensor is undefined)")
+    return _SwiGLUToFloat8.apply(a, b, float8_dtype, linear_mm_config or LinearMMConfig(), gemm_input_role, reduce_amax)

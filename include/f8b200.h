@@ -248,6 +248,27 @@ int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols,
                         float* scale_out, void* out, int64_t ld_out, void* stream);
 
 /*
+ * SwiGLU gate fused into the dynamic fp8 cast of its output, like the RMSNorm pair above:
+ *
+ *   y = RN_T( float(RN_T(silu(a))) * b ),   silu(a) = a / (1 + exp(-a)) in fp32
+ *
+ * for a, b [rows, cols] of one dtype T with row pitches ld_a, ld_b (the two halves of a fused
+ * w1|w3 output are the usual case): `F.silu(self.w1(x)) * self.w3(x)` of
+ * float8_experimental/benchmarks/profile_linear_float8.py:117-118, the producer of the w2
+ * input.  9 bytes of traffic per element instead of 17.  exp is the device math library's
+ * expf, so results can differ from a CPU evaluation in the last fp32 bit of silu(a).
+ *
+ * f8b200_swiglu_amax  pass A: amax_out[0] = max |y| (fp32; zeroed by the call).
+ * f8b200_swiglu_cast  pass B: out = fp8(clamp(RN_T(y * scale))), scale derived from `amax` as
+ *                     in f8b200_cast(scale_src = 1); scale_out (optional) receives it.
+ */
+int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
+                       int64_t ld_a, int64_t ld_b, float* amax_out, void* stream);
+int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
+                       int64_t ld_a, int64_t ld_b, const float* amax, int fp8_kind,
+                       float* scale_out, void* out, int64_t ld_out, void* stream);
+
+/*
  * Reads and clears the device error word of the current device (synchronises the
  * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
  * last read; the result of that launch is undefined.  Test and debugging aid.

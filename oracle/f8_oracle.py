@@ -296,6 +296,24 @@ def rmsnorm_cast_dynamic(x: np.ndarray, dtype: str, weight: np.ndarray, eps: flo
     return bits, scale, amax, rstd
 
 
+def swiglu(a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+    """y = RN_T(float(RN_T(silu(a))) * b) with silu(a) = a / (1 + exp(-a)) in fp32:
+    `F.silu(self.w1(x)) * self.w3(x)` of
+    float8_experimental/benchmarks/profile_linear_float8.py:117-118.  exp is numpy's float32 exp,
+    which may differ from another math library's in the last bit.  Returns y widened to float32."""
+    a32, b32 = to_f32(a, dtype), to_f32(b, dtype)
+    with np.errstate(over="ignore", invalid="ignore"):
+        s = a32 / (np.float32(1.0) + np.exp(-a32, dtype=np.float32))
+    return round_f32_to(round_f32_to(s.astype(np.float32), dtype) * b32, dtype)
+
+
+def swiglu_cast_dynamic(a: np.ndarray, b: np.ndarray, dtype: str, fp8: str):
+    """The dynamic cast (float8_experimental/float8_scaling_utils.py:33-62) applied to the
+    SwiGLU gate output without materialising it.  Returns (bits, scale, amax)."""
+    y = swiglu(a, b, dtype)
+    return cast_dynamic(from_f32(y, dtype), dtype, fp8)
+
+
 # ---------------------------------------------------------------------------
 # delayed-scaling bookkeeping
 # ---------------------------------------------------------------------------

@@ -124,6 +124,21 @@ def _rmsnorm_cast(x, weight, rstd, amax, fp8_kind):
     return from_np(bits.reshape(tuple(x.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
 
 
+def _swiglu_amax(a, b):
+    name = _HP[a.dtype]
+    y = O.swiglu(to_np(a), to_np(b), name)
+    amax = np.float32(np.nan) if np.isnan(y).any() else np.float32(np.abs(y).max())
+    return torch.tensor(float(amax), dtype=torch.float32)
+
+
+def _swiglu_cast(a, b, amax, fp8_kind):
+    name = _HP[a.dtype]
+    y = O.swiglu(to_np(a), to_np(b), name)
+    scale = np.float32(O.amax_to_scale(np.float32(amax.item()), _F8[fp8_kind], name, name))
+    bits = O.cast_to_fp8(O.from_f32(y, name), name, scale, _F8[fp8_kind], name)
+    return from_np(bits.reshape(tuple(a.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
+
+
 def install() -> None:
     """Registers the CPU stand-ins once per process."""
     global _installed
@@ -138,6 +153,8 @@ def install() -> None:
     lib.impl("transpose_fp8", _transpose_fp8, "CPU")
     lib.impl("delayed_sync", _delayed_sync, "CPU")
     lib.impl("scaled_mm", _scaled_mm, "CPU")
+    lib.impl("swiglu_amax", _swiglu_amax, "CPU")
+    lib.impl("swiglu_cast", _swiglu_cast, "CPU")
     lib.impl("rmsnorm_amax", _rmsnorm_amax, "CPU")
     lib.impl("rmsnorm_cast", _rmsnorm_cast, "CPU")
     install._lib = lib  # keep the registrations alive

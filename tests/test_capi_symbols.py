@@ -47,3 +47,19 @@ def test_status_strings_and_argument_validation():
     assert lib.f8b200_gemm_fp8_ws(*args, ctypes.c_void_p(260), 256, None) == -2
     assert lib.f8b200_cast(ctypes.c_void_p(16), 0, 4, 4, 2, 0, ctypes.c_void_p(4), None, 0, 0, None, 0, None, 0,
                            None, 0, None) == -1
+
+
+def test_bindings_are_well_formed():
+    """Every ctypes binding hands `_check` exactly (status, entry-point name), and the name
+    is the entry point it called (a GPU is needed to reach these lines at run time)."""
+    import ast
+    import inspect
+
+    tree = ast.parse(inspect.getsource(_native))
+    calls = [n for n in ast.walk(tree) if isinstance(n, ast.Call) and getattr(n.func, "id", None) == "_check"]
+    assert len(calls) >= 14
+    for call in calls:
+        assert len(call.args) == 2 and not call.keywords, call.lineno
+        status, name = call.args
+        assert isinstance(name, ast.Constant) and name.value in _native.EXPORTS, call.lineno
+        assert isinstance(status, ast.Call) and status.func.attr == name.value, call.lineno

@@ -13,7 +13,11 @@ import float8_experimental_b200 as f8  # noqa: E402
 from float8_experimental_b200.float8_linear import Float8Linear  # noqa: E402
 from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic  # noqa: E402
 from float8_experimental_b200.float8_tensor import Float8Tensor, LinearMMConfig  # noqa: E402
-from float8_experimental_b200.fused_norm import Float8RMSNorm, rms_norm_to_float8_dynamic  # noqa: E402
+from float8_experimental_b200.fused_norm import (  # noqa: E402
+    Float8RMSNorm,
+    rms_norm_to_float8_dynamic,
+    swiglu_to_float8_dynamic,
+)
 from oracle import f8_oracle as O  # noqa: E402
 
 
@@ -70,3 +74,30 @@ def test_fused_norm_rejects_mismatched_weight_dtype_and_empty_input():
         rms_norm_to_float8_dynamic(x, torch.ones(64), 1e-6)
     with pytest.raises(RuntimeError):
         rms_norm_to_float8_dynamic(x[:0], torch.ones(64, dtype=torch.bfloat16), 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_oracle_fused_swiglu_equals_unfused_composition(dtype):
+    torch.manual_seed(9)
+    h = torch.randn(24, 2 * 264).mul(3).to(dtype)
+    a, b = h[:, :264], h[:, 264:]  # the two halves of one fused w1|w3 output
+    fused = swiglu_to_float8_dynamic(a, b)
+    unfused = hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, LinearMMConfig())
+    x, y = fused._data.view(torch.uint8), unfused._data.view(torch.uint8)
+    assert fused.shape == a.shape and fused.dtype == dtype
+    assert (x != y).float().mean().item() <= 2e-3 and (x.int() - y.int()).abs().max().item() <= 1
+    assert abs(fused._scale.item() / unfused._scale.item() - 1) <= 2 ** -7
+
+
+def test_fused_swiglu_backward_matches_autograd():
+    torch.manual_seed(4)
+    a = torch.randn(16, 128).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(16, 128).to(torch.bfloat16).requires_grad_(True)
+    lin = torch.nn.Linear(128, 64, bias=False, dtype=torch.bfloat16)
+    m = Float8Linear.from_float(lin, f8.Float8LinearConfig())
+    go = (torch.randn(16, 64) * 0.01).to(torch.bfloat16)
+    m(swiglu_to_float8_dynamic(a, b, linear_mm_config=m.linear_mm_config)).backward(go)
+    a2, b2 = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    m(torch.nn.functional.silu(a2) * b2).backward(go)
+    assert O.sqnr_db(a2.grad.float().numpy(), a.grad.float().numpy()) > 35
+    assert O.sqnr_db(b2.grad.float().numpy(), b.grad.float().numpy()) > 35

@@ -7,7 +7,7 @@ import torch
 from float8_experimental_b200._ops import ops
 from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic
 from float8_experimental_b200.float8_tensor import LinearMMConfig
-from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic
+from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic, swiglu_to_float8_dynamic
 from oracle import f8_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -80,3 +80,39 @@ def test_fused_norm_full_size_against_unfused_composition():
     # idempotence of the cast half: casting the dequantised result with the same scale returns the bytes
     again = hp_tensor_to_float8_dynamic(fused.to_original_precision(), torch.float8_e4m3fn, LinearMMConfig())
     assert again._scale.item() == fused._scale.item()
+
+
+def _close_fp8(a, b, frac):
+    a, b = a.view(torch.uint8), b.view(torch.uint8)
+    assert (a != b).float().mean().item() <= frac
+    assert (a.int() - b.int()).abs().max().item() <= 1
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(64, 4096), (33, 520), (5, 7), (3, 4, 264)])
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fused_swiglu_kernels_match_oracle(dtype, shape, fp8):
+    """exp comes from two math libraries (device expf, numpy), so a last-bit difference of
+    silu(a) may move an element across a rounding boundary: at most one fp8 step, on a
+    vanishing fraction of elements; amax and scale agree to a bf16 ulp."""
+    g = torch.Generator().manual_seed(shape[-1] + shape[0])
+    a = (torch.randn(shape, generator=g) * 3).to(dtype)
+    b = (torch.randn(shape, generator=g) * 2).to(dtype)
+    name, kind = _HP[dtype], (O.E4M3 if fp8 == torch.float8_e4m3fn else O.E5M2)
+    bits, scale, amax = O.swiglu_cast_dynamic(host_bits(a), host_bits(b), name, kind)
+    out = swiglu_to_float8_dynamic(a.cuda(), b.cuda(), fp8)
+    assert abs(out._scale.item() / float(scale) - 1) <= 2 ** -7
+    if out._scale.item() == float(scale):
+        _close_fp8(out._data.cpu(), torch.from_numpy(bits.reshape(shape)), 2e-3)
+
+
+def test_fused_swiglu_full_size_against_unfused_composition_on_gpu():
+    """The w2 input of the LLaMa-2-70B FFN: a, b = halves of the [16384, 57344] w1|w3 output.
+    Same math library on both sides, so the bytes agree."""
+    torch.manual_seed(12)
+    h = torch.randn(16384, 57344, device="cuda", dtype=torch.bfloat16) * 2
+    a, b = h[:, :28672], h[:, 28672:]
+    fused = swiglu_to_float8_dynamic(a, b)
+    ref = hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, LinearMMConfig())
+    assert fused._scale.item() == ref._scale.item()
+    _close_fp8(fused._data, ref._data, 1e-4)
