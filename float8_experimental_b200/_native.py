@@ -80,7 +80,7 @@ def load() -> ctypes.CDLL:
                                        i32, vp, i64, vp]
     lib.f8b200_rmsnorm_amax.argtypes = [vp, i32, i64, i64, i64, vp, ctypes.c_float, vp, vp, vp]
     lib.f8b200_rmsnorm_cast.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, vp, vp, i64, vp]
-    lib.f8b200_swiglu_amax.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, vp]
+    lib.f8b200_swiglu_amax.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
     lib.f8b200_swiglu_cast.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i32, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
@@ -339,12 +339,12 @@ def rmsnorm_cast(x: torch.Tensor, rows: int, cols: int, ld: int, weight: torch.T
 
 
 def swiglu_amax(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int,
-                amax_out: torch.Tensor) -> None:
-    _require_cuda(a, b, amax_out)
+                y_out: Optional[torch.Tensor], ld_y: int, amax_out: torch.Tensor) -> None:
+    _require_cuda(a, b, y_out, amax_out)
     with _Launch("glu_amax", a.device):
         _check(
             load().f8b200_swiglu_amax(a.data_ptr(), b.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b,
-                                      amax_out.data_ptr(), _stream(a)),
+                                      _ptr(y_out), ld_y, amax_out.data_ptr(), _stream(a)),
             "f8b200_swiglu_amax",
         )
 

@@ -16,7 +16,7 @@ Ops (namespace `f8b200`):
   scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum) -> out
   rmsnorm_amax(x, weight, eps) -> (rstd fp32 [rows], amax fp32 0-dim)      f8b200_rmsnorm_amax
   rmsnorm_cast(x, weight, rstd, amax, kind) -> (data, scale)               f8b200_rmsnorm_cast
-  swiglu_amax(a, b) -> amax fp32 0-dim                                     f8b200_swiglu_amax
+  swiglu_amax(a, b, write_y) -> (amax fp32 0-dim, y or empty)              f8b200_swiglu_amax
   swiglu_cast(a, b, amax, kind) -> (data, scale)                           f8b200_swiglu_cast
 """
 from __future__ import annotations
@@ -48,7 +48,7 @@ _lib.define(
 )
 _lib.define("rmsnorm_amax(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _lib.define("rmsnorm_cast(Tensor x, Tensor weight, Tensor rstd, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
-_lib.define("swiglu_amax(Tensor a, Tensor b) -> Tensor")
+_lib.define("swiglu_amax(Tensor a, Tensor b, bool write_y) -> (Tensor, Tensor)")
 _lib.define("swiglu_cast(Tensor a, Tensor b, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 
 
@@ -195,11 +195,12 @@ def _glu_operands(a, b):
     return am, bm, rows, cols, lda, ldb
 
 
-def _swiglu_amax_cuda(a, b):
+def _swiglu_amax_cuda(a, b, write_y: bool):
     am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
     amax = torch.empty((), dtype=torch.float32, device=a.device)
-    N.swiglu_amax(am, bm, rows, cols, lda, ldb, amax)
-    return amax
+    y = _empty_like_shape(a, a.dtype) if write_y else a.new_empty((0,))
+    N.swiglu_amax(am, bm, rows, cols, lda, ldb, y if write_y else None, cols, amax)
+    return amax, y
 
 
 def _swiglu_cast_cuda(a, b, amax, fp8_kind: int):
@@ -229,8 +230,8 @@ _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 # around the opaque ops
 # ---------------------------------------------------------------------------
 @torch.library.register_fake("f8b200::swiglu_amax")
-def _swiglu_amax_fake(a, b):
-    return a.new_empty((), dtype=torch.float32)
+def _swiglu_amax_fake(a, b, write_y):
+    return a.new_empty((), dtype=torch.float32), a.new_empty(a.shape if write_y else (0,))
 
 
 @torch.library.register_fake("f8b200::swiglu_cast")

@@ -437,8 +437,11 @@ extern "C" int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, in
 // SwiGLU gate fused into the dynamic fp8 cast of its output: y = RN_T(RN_T(silu(a)) * b),
 // silu(a) = a / (1 + exp(-a)) in fp32, which is `F.silu(self.w1(x)) * self.w3(x)` of
 // float8_experimental/benchmarks/profile_linear_float8.py:117-118, the producer of the input of
-// the w2 linear.  Unfused: silu 2 + 2, multiply 2 + 2 + 2, cast 2 + 2 + 1 = 17 bytes per element;
-// here pass A reads a and b for the amax of y (4), pass B reads them again and writes fp8 (4 + 1).
+// the w2 linear.  Unfused: silu 2 + 2, multiply 2 + 2 + 2, cast 2 + 2 + 1 = 17 bytes per element.
+// Here pass A reads a and b for the amax of y (4) and pass B either reads them again and writes fp8
+// (4 + 1; y is never written) or, when pass A was also asked to write y (4 + 2), is the plain cast of
+// y (2 + 1): 9 bytes per element both ways.  exp and an IEEE division per element make the gate
+// issue-bound rather than memory-bound, so evaluating it once (the second form) is the faster one.
 // ===========================================================================
 namespace f8b200 {
 namespace {
@@ -461,10 +464,11 @@ constexpr int kGluThreads = 256;
 
 // 16-bit dtypes, 8 elements per thread and step; rows x cols with separate row pitches for a and b
 // (the two halves of one fused w1|w3 output are the usual case).
-template <int HP>
+template <int HP, bool WRITE_Y>
 __global__ void __launch_bounds__(kGluThreads)
 swiglu_amax_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda_bytes, int64_t ldb_bytes,
-                        int64_t rows, int64_t chunks_per_row, uint32_t* __restrict__ amax_bits) {
+                        int64_t rows, int64_t chunks_per_row, uint32_t* __restrict__ amax_bits,
+                        char* __restrict__ y_out, int64_t ldy_bytes) {
   __shared__ uint32_t redu[kGluThreads / 32];
   const int64_t total = rows * chunks_per_row;
   uint32_t amax2 = 0;
@@ -472,10 +476,16 @@ swiglu_amax_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, 
     const int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
     const uint4 qa = __ldcs(reinterpret_cast<const uint4*>(a + r * lda_bytes) + c);
     const uint4 qb = __ldcs(reinterpret_cast<const uint4*>(b + r * ldb_bytes) + c);
-    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.x, qb.x) & 0x7FFF7FFFu);
-    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.y, qb.y) & 0x7FFF7FFFu);
-    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.z, qb.z) & 0x7FFF7FFFu);
-    amax2 = __vmaxu2(amax2, swiglu_pair<HP>(qa.w, qb.w) & 0x7FFF7FFFu);
+    uint4 y;
+    y.x = swiglu_pair<HP>(qa.x, qb.x);
+    y.y = swiglu_pair<HP>(qa.y, qb.y);
+    y.z = swiglu_pair<HP>(qa.z, qb.z);
+    y.w = swiglu_pair<HP>(qa.w, qb.w);
+    amax2 = __vmaxu2(amax2, y.x & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, y.y & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, y.z & 0x7FFF7FFFu);
+    amax2 = __vmaxu2(amax2, y.w & 0x7FFF7FFFu);
+    if constexpr (WRITE_Y) reinterpret_cast<uint4*>(y_out + r * ldy_bytes)[c] = y;
   }
   const uint32_t h = max(amax2 & 0xFFFFu, amax2 >> 16);
   uint32_t amax = HP == F8B200_BF16 ? (h << 16) : __float_as_uint(__half2float(__ushort_as_half((unsigned short)h)));
@@ -513,15 +523,29 @@ swiglu_cast_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, 
 
 // Any dtype, shape and alignment: one element per thread and step.
 template <int HP>
+__device__ __forceinline__ void store_hp(void* base, int64_t i, float v) {
+  if constexpr (HP == F8B200_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
+  } else if constexpr (HP == F8B200_FP16) {
+    reinterpret_cast<__half*>(base)[i] = __float2half_rn(v);
+  } else {
+    reinterpret_cast<float*>(base)[i] = v;
+  }
+}
+
+template <int HP>
 __global__ void __launch_bounds__(kGluThreads)
 swiglu_amax_generic_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda, int64_t ldb,
-                           int64_t rows, int64_t cols, uint32_t* __restrict__ amax_bits) {
+                           int64_t rows, int64_t cols, uint32_t* __restrict__ amax_bits, char* __restrict__ y_out,
+                           int64_t ldy) {
   __shared__ uint32_t redu[kGluThreads / 32];
   const int64_t total = rows * cols;
   uint32_t amax = 0;
   for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
     const int64_t r = i / cols, c = i - r * cols;
-    amax = max(amax, abs_bits(swiglu_value<HP>(load_hp<HP>(a, r * lda + c), load_hp<HP>(b, r * ldb + c))));
+    const float y = swiglu_value<HP>(load_hp<HP>(a, r * lda + c), load_hp<HP>(b, r * ldb + c));
+    amax = max(amax, abs_bits(y));
+    if (y_out != nullptr) store_hp<HP>(y_out, r * ldy + c, y);  // y is a value of T: the store is exact
   }
   amax = warp_max_u32(amax);
   const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
@@ -564,9 +588,10 @@ bool glu_vec_ok(int hp_dtype, int64_t cols, int64_t lda, int64_t ldb, const void
 }  // namespace f8b200
 
 extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
-                                  int64_t ld_b, float* amax_out, void* stream) {
+                                  int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out, void* stream) {
   if (a == nullptr || b == nullptr || amax_out == nullptr) return F8B200_ERR_BAD_ARG;
   if (hp_dtype < 0 || hp_dtype > 2 || rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols) return F8B200_ERR_BAD_ARG;
+  if (y_out != nullptr && ld_y < cols) return F8B200_ERR_BAD_ARG;
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -574,23 +599,29 @@ extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, in
   if (e != cudaSuccess) return record_cuda_error(e);
   const char* ap = static_cast<const char*>(a);
   const char* bp = static_cast<const char*>(b);
+  char* yp = static_cast<char*>(y_out);
   uint32_t* ab = reinterpret_cast<uint32_t*>(amax_out);
-  if (glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b)) {
+  const bool y_vec = y_out == nullptr || (ld_y % 8 == 0 && reinterpret_cast<uintptr_t>(y_out) % 16 == 0);
+  if (glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b) && y_vec) {
     const int64_t cpr = cols / 8;
     const int grid = glu_grid(rows * cpr);
-    if (hp_dtype == F8B200_BF16)
-      swiglu_amax_fast_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab);
-    else
-      swiglu_amax_fast_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab);
+#define F8_GLU_A(HP, WY) \
+  swiglu_amax_fast_kernel<HP, WY><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab, yp, ld_y * 2)
+    if (hp_dtype == F8B200_BF16) {
+      if (y_out != nullptr) F8_GLU_A(F8B200_BF16, true); else F8_GLU_A(F8B200_BF16, false);
+    } else {
+      if (y_out != nullptr) F8_GLU_A(F8B200_FP16, true); else F8_GLU_A(F8B200_FP16, false);
+    }
+#undef F8_GLU_A
     return check_launch();
   }
   const int grid = glu_grid(rows * cols);
   if (hp_dtype == F8B200_BF16)
-    swiglu_amax_generic_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+    swiglu_amax_generic_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab, yp, ld_y);
   else if (hp_dtype == F8B200_FP16)
-    swiglu_amax_generic_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+    swiglu_amax_generic_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab, yp, ld_y);
   else
-    swiglu_amax_generic_kernel<F8B200_FP32><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab);
+    swiglu_amax_generic_kernel<F8B200_FP32><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab, yp, ld_y);
   return check_launch();
 }
 

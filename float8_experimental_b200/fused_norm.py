@@ -93,11 +93,15 @@ class Float8RMSNorm(torch.nn.Module):
 
 class _SwiGLUToFloat8(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, b, float8_dtype, linear_mm_config, gemm_input_role, reduce_amax):
-        amax = ops.swiglu_amax(a, b)
+    def forward(ctx, a, b, float8_dtype, linear_mm_config, gemm_input_role, reduce_amax, recompute):
+        amax, y = ops.swiglu_amax(a, b, not recompute)
         if reduce_amax and dist.is_initialized():
             dist.all_reduce(amax, op=dist.ReduceOp.MAX)
-        data, scale = ops.swiglu_cast(a, b, amax, _kind(float8_dtype))
+        if recompute:
+            data, scale = ops.swiglu_cast(a, b, amax, _kind(float8_dtype))
+        else:
+            data, _, scale = ops.cast_from_amax(y, amax, _kind(float8_dtype), False)
+            del y  # a temporary: nothing keeps it for backward
         ctx.save_for_backward(a, b)
         return Float8Tensor(data, scale, a.dtype, linear_mm_config, gemm_input_role)
 
@@ -110,7 +114,7 @@ class _SwiGLUToFloat8(torch.autograd.Function):
         silu = a32 * sig
         da = g32 * b.float() * (sig * (1 + a32 * (1 - sig)))
         db = g32 * silu.to(a.dtype).float()
-        return da.to(a.dtype), db.to(b.dtype), None, None, None, None
+        return da.to(a.dtype), db.to(b.dtype), None, None, None, None, None
 
 
 def swiglu_to_float8_dynamic(
@@ -120,9 +124,16 @@ def swiglu_to_float8_dynamic(
     linear_mm_config: LinearMMConfig = None,
     gemm_input_role: GemmInputRole = GemmInputRole.INPUT,
     reduce_amax: bool = False,
+    recompute: bool = False,
 ) -> Float8Tensor:
-    """fp8(silu(a) * b) with a dynamic per-tensor scale, without materialising the product.
-    `a` and `b` share shape and dtype; they may be column slices of one fused w1|w3 output."""
+    """fp8(silu(a) * b) with a dynamic per-tensor scale in two launches and 9 bytes of traffic
+    per element (17 unfused).  `a` and `b` share shape and dtype; they may be column slices of one
+    fused w1|w3 output.  By default the first launch writes the gate output once (a temporary in
+    the input dtype, freed on return) while it takes the amax, and the second is the plain cast;
+    `recompute=True` never writes it and evaluates the gate in both launches instead (no
+    temporary, same bytes moved, more arithmetic: slower).  Both give the same bytes."""
     if a.numel() == 0:
         raise RuntimeError("swiglu_to_float8_dynamic: empty input (amax of an empty tensor is undefined)")
-    return _SwiGLUToFloat8.apply(a, b, float8_dtype, linear_mm_config or LinearMMConfig(), gemm_input_role, reduce_amax)
+    return _SwiGLUToFloat8.apply(
+        a, b, float8_dtype, linear_mm_config or LinearMMConfig(), gemm_input_role, reduce_amax, recompute
+    )

@@ -258,12 +258,17 @@ int f8b200_rmsnorm_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols,
  * input.  9 bytes of traffic per element instead of 17.  exp is the device math library's
  * expf, so results can differ from a CPU evaluation in the last fp32 bit of silu(a).
  *
- * f8b200_swiglu_amax  pass A: amax_out[0] = max |y| (fp32; zeroed by the call).
- * f8b200_swiglu_cast  pass B: out = fp8(clamp(RN_T(y * scale))), scale derived from `amax` as
- *                     in f8b200_cast(scale_src = 1); scale_out (optional) receives it.
+ * f8b200_swiglu_amax  pass A: amax_out[0] = max |y| (fp32; zeroed by the call).  With y_out !=
+ *                     NULL it also writes y (dtype T, row pitch ld_y) and pass B can then be
+ *                     f8b200_cast(y, scale_src = 1): same 9 bytes per element, and the gate,
+ *                     whose exp and division make it issue-bound, is evaluated once.
+ * f8b200_swiglu_cast  pass B from a and b again (y never written): out = fp8(clamp(RN_T(y *
+ *                     scale))), scale derived from `amax` as in f8b200_cast(scale_src = 1);
+ *                     scale_out (optional) receives it.
  */
 int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
-                       int64_t ld_a, int64_t ld_b, float* amax_out, void* stream);
+                       int64_t ld_a, int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out,
+                       void* stream);
 int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
                        int64_t ld_a, int64_t ld_b, const float* amax, int fp8_kind,
                        float* scale_out, void* out, int64_t ld_out, void* stream);

@@ -124,11 +124,12 @@ def _rmsnorm_cast(x, weight, rstd, amax, fp8_kind):
     return from_np(bits.reshape(tuple(x.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
 
 
-def _swiglu_amax(a, b):
+def _swiglu_amax(a, b, write_y):
     name = _HP[a.dtype]
     y = O.swiglu(to_np(a), to_np(b), name)
     amax = np.float32(np.nan) if np.isnan(y).any() else np.float32(np.abs(y).max())
-    return torch.tensor(float(amax), dtype=torch.float32)
+    y_t = from_np(O.from_f32(y, name).reshape(tuple(a.shape)), a.dtype) if write_y else a.new_empty((0,))
+    return torch.tensor(float(amax), dtype=torch.float32), y_t
 
 
 def _swiglu_cast(a, b, amax, fp8_kind):
