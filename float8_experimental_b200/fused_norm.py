@@ -13,8 +13,8 @@ the two agree on the last bit of 1/rms, see `tests/test_fused_norm_gpu.py`); a `
 takes it as an already-cast input, as it does for tensor-parallel inputs
 (float8_experimental/float8_linear.py:240-262).
 
-`swiglu_to_float8_dynamic(a, b, ...)` does the same for the FFN gate `silu(a) * b` that feeds
-the w2 linear (profile_linear_float8.py:117-118): 9 bytes per element instead of 17.
+`swiglu_to_float8_dynamic(a, b, ...)` fuses the FFN gate `silu(a) * b` that feeds the w2
+linear (profile_linear_float8.py:117-118) with the amax pass: 9 bytes per element instead of 17.
 """
 from __future__ import annotations
 
