@@ -256,6 +256,48 @@ def delayed_sync(amax_t: torch.Tensor, hist: torch.Tensor, n_e4m3: int, orig_dty
         )
 
 
+# ---------------------------------------------------------------------------
+# optional single-GPU library: the cluster-multicast GEMM (csrc/gemm_mc.cu).  Runs on several GPUs
+# ship without it; everything then goes through libf8b200.so.
+# ---------------------------------------------------------------------------
+_MC_LIB_PATH = os.path.join(os.path.dirname(_LIB_PATH), "libf8b200_mc.so")
+_mc_lib = None
+_mc_tried = False
+
+
+def load_mc():
+    """The multicast GEMM library, or None when it was not built / not shipped."""
+    global _mc_lib, _mc_tried
+    if not _mc_tried:
+        _mc_tried = True
+        if os.path.exists(_MC_LIB_PATH):
+            lib = ctypes.CDLL(_MC_LIB_PATH)
+            vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+            lib.f8b200_mc_gemm_fp8.argtypes = [vp, i32, i32, i64, vp, i32, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64,
+                                               i64, i32, i32, vp, i64, vp]
+            lib.f8b200_mc_gemm_fp8.restype = i32
+            lib.f8b200_mc_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+            lib.f8b200_mc_read_device_error.restype = i32
+            _mc_lib = lib
+    return _mc_lib
+
+
+def _mc_cluster(m: int, n: int, k: int):
+    """Cluster shape (tiles along M, along N) of the multicast GEMM for this product, or None
+    to use the kernels of libf8b200.so.  Only single-process runs use it: F8B200_GEMM_MC=0
+    switches it off, =21 / =22 force a shape for every product."""
+    mode = os.environ.get("F8B200_GEMM_MC", "0")
+    if mode == "0" or load_mc() is None:
+        return None
+    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+        return None
+    if mode == "21":
+        return (2, 1)
+    if mode == "22":
+        return (2, 2)
+    return None
+
+
 GEMM_WORKSPACE_BYTES = 256  # F8B200_GEMM_WORKSPACE_BYTES in include/f8b200.h
 _gemm_workspaces: dict = {}
 
@@ -280,7 +322,18 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
     workspace-free `f8b200_gemm_fp8` (K-major operands only)."""
     _require_cuda(a, b, scale_a, scale_b, bias, out)
     stream = _stream(a)
+    cluster = _mc_cluster(m, n, k)
     with _Launch("gemm", a.device):
+        if cluster is not None:
+            ws = _gemm_workspace(a.device, stream)
+            rc = _mc_lib.f8b200_mc_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), int(a_mn_major), lda, b.data_ptr(),
+                                            fp8_code(b.dtype), int(b_mn_major), ldb, scale_a.data_ptr(),
+                                            scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo,
+                                            m, n, k, cluster[0], cluster[1], ws.data_ptr(), ws.numel(), stream)
+            if rc != -6:  # F8B200_ERR_UNSUPPORTED: such clusters cannot be scheduled here
+                if rc != 0:
+                    raise F8B200Error(f"f8b200_mc_gemm_fp8: {load().f8b200_status_string(rc).decode()}")
+                return
         if os.environ.get("F8B200_GEMM_WS", "1") == "0" and not (a_mn_major or b_mn_major):
             _check(
                 load().f8b200_gemm_fp8(a.data_ptr(), fp8_code(a.dtype), lda, b.data_ptr(), fp8_code(b.dtype), ldb,
@@ -364,4 +417,9 @@ def swiglu_cast(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: in
 def read_device_error() -> int:
     v = ctypes.c_uint32(0)
     _check(load().f8b200_read_device_error(ctypes.byref(v)), "f8b200_read_device_error")
-    return int(v.value)
+    flags = int(v.value)
+    if _mc_lib is not None:  # the multicast library keeps an error word of its own
+        w = ctypes.c_uint32(0)
+        if _mc_lib.f8b200_mc_read_device_error(ctypes.byref(w)) == 0:
+            flags |= int(w.value)
+    return flags

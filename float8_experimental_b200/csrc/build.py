@@ -14,6 +14,10 @@ PKG = os.path.dirname(HERE)
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libf8b200.so")
 SOURCES = ["capi.cu", "cast.cu", "gemm.cu", "norm.cu"]
+# Single-GPU extra: the cluster-multicast GEMM lives in a library of its own, so that runs on
+# several GPUs can leave its source and binary out altogether (it includes gemm.cu).
+MC_LIB_PATH = os.path.join(LIB_DIR, "libf8b200_mc.so")
+MC_SOURCES = ["capi.cu", "gemm_mc.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "f8b200.h")]
 
 
@@ -35,8 +39,41 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
+def _compile(sources, out_path, verbose):
+    cmd = [
+        _nvcc(),
+        "-gencode", "arch=compute_100a,code=sm_100a",
+        "-O3", "-std=c++17", "-lineinfo",
+        "-Xcompiler", "-fPIC", "-shared",
+        "-o", out_path,
+    ]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += [os.path.join(HERE, s) for s in sources]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed building {os.path.basename(out_path)}")
+
+
+def build_mc(force: bool = False, verbose: bool = False):
+    """Compiles the single-GPU multicast GEMM library when its source is present; returns its
+    path, or None when the source was left out."""
+    src = os.path.join(HERE, "gemm_mc.cu")
+    if not os.path.exists(src):
+        return None
+    deps = [os.path.join(HERE, s) for s in MC_SOURCES + ["gemm.cu"] + HEADERS] + [os.path.abspath(__file__)]
+    if not force and os.path.exists(MC_LIB_PATH) and all(os.path.getmtime(d) <= os.path.getmtime(MC_LIB_PATH) for d in deps):
+        return MC_LIB_PATH
+    os.makedirs(LIB_DIR, exist_ok=True)
+    _compile(MC_SOURCES, MC_LIB_PATH, verbose)
+    return MC_LIB_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compiles the library if it is missing or older than its sources; returns its path."""
+    build_mc(force, verbose)
     if not force and not _stale():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
