@@ -284,9 +284,12 @@ def load_mc():
 
 def _mc_cluster(m: int, n: int, k: int):
     """Cluster shape (tiles along M, along N) of the multicast GEMM for this product, or None
-    to use the kernels of libf8b200.so.  Only single-process runs use it: F8B200_GEMM_MC=0
-    switches it off, =21 / =22 force a shape for every product."""
-    mode = os.environ.get("F8B200_GEMM_MC", "0")
+    to use the kernels of libf8b200.so.  Only single-process runs use it, and by default only
+    where it measured faster: K >= 16384 (the products that otherwise run on the wide kernel),
+    2 x 1 clusters (+1 to +4 % sustained; 2 x 2 clusters measured slower than 2 x 1).
+    F8B200_GEMM_MC=0 switches it off, =21 / =22 force a shape for every product; forcing a
+    kernel with F8B200_GEMM_MODE switches it off as well."""
+    mode = os.environ.get("F8B200_GEMM_MC", "auto")
     if mode == "0" or load_mc() is None:
         return None
     if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
@@ -295,7 +298,10 @@ def _mc_cluster(m: int, n: int, k: int):
         return (2, 1)
     if mode == "22":
         return (2, 2)
-    return None
+    forced = os.environ.get("F8B200_GEMM_MODE", "")
+    if forced[:1] in ("1", "2", "w"):
+        return None
+    return (2, 1) if k >= int(os.environ.get("F8B200_GEMM_WIDE_K", "16384")) else None
 
 
 GEMM_WORKSPACE_BYTES = 256  # F8B200_GEMM_WORKSPACE_BYTES in include/f8b200.h
