@@ -503,7 +503,11 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                 "ms_per_step": e2e_s * 1e3},
         "gpu_launches": launches,
         "roofline": {
-            "kernel": "gemm_fp8_pair_kernel (K < 16384; tcgen05.mma.cta_group::2) + gemm_fp8_wide_kernel (K >= 16384; cta_group::1, 256x256 per CTA), kind::f8f6f4", "bound": "tensor", "achieved": gemm_tflops,
+            "kernel": ("gemm_fp8_pair_kernel (K < 16384; tcgen05.mma.cta_group::2) + " +
+                       ("gemm_fp8_mc_kernel (K >= 16384; 2x1 clusters of 256x256 tiles, B multicast)"
+                        if _native._mc_cluster(16384, 8192, 16384) is not None else
+                        "gemm_fp8_wide_kernel (K >= 16384; cta_group::1, 256x256 per CTA)") + ", kind::f8f6f4"),
+            "bound": "tensor", "achieved": gemm_tflops,
             "peak": fp8_peak, "unit": "TFLOP/s", "frac": (gemm_tflops / fp8_peak) if gemm_tflops else None,
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (fp8 issues at twice the bf16 rate)",
             "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
