@@ -513,10 +513,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
             "launches": gemm_calls,
             # dram__bytes_read + dram__bytes_write per launch, mean of the three GEMMs of the wo layer (fwd and dgrad
-            # 16384x8192x8192 on the pair kernel, wgrad 8192x8192x16384 on the wide kernel), from the ncu captures
+            # 16384x8192x8192 on the pair kernel, wgrad 8192x8192x16384 on the multicast kernel; 0.881 GB read on the wide kernel), from the ncu captures
             # summarised in profiles/gemm_fp8_pair_kernel_wo_16384x8192x8192.md and
             # profiles/gemm_fp8_wide_kernel_wo_w2_w13.md
-            "traffic": (0.346e9 + 0.249e9 + 0.425e9 + 0.249e9 + 0.881e9 + 0.120e9) / 3,
+            "traffic": (0.346e9 + 0.249e9 + 0.425e9 + 0.249e9 + 0.820e9 + 0.120e9) / 3,
             "traffic_algorithmic": (2 * (201.3e6 + 268.4e6) + (268.4e6 + 134.2e6)) / 3,
         },
         "roofline_cast": {
