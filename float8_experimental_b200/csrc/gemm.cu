@@ -660,6 +660,77 @@ __device__ __forceinline__ void drain_accumulator_1box(const EpilogueArgs<OutT>&
   }
 }
 
+// 16-bit outputs: the warp's 4 KB of staging holds TWO boxes of 32 rows x 64 bytes (64-byte swizzle),
+// one per 32-column chunk, which alternate: the store of chunk c is in flight while chunk c+1 is
+// converted, and only the store issued two chunks ago has to have finished reading its box.  With a
+// single 128-byte box the warp stalled on every second chunk for its own store, and in these
+// kernels nothing hides the epilogue (the accumulator fills all of TMEM).
+template <typename OutT>
+__device__ __forceinline__ void drain_accumulator_halfbox(const EpilogueArgs<OutT>& e, uint32_t taddr, int row0,
+                                                          int col0, int ncol_total, uint32_t& boxes) {
+  static_assert(sizeof(OutT) == 2, "half boxes are for 16-bit outputs");
+  const int lane = threadIdx.x & 31;
+  if (row0 >= e.m) return;  // uniform over the warp
+#pragma unroll 1
+  for (int c = 0; c < ncol_total / 32; ++c) {
+    const int col = col0 + c * 32;
+    if (col >= e.n) break;
+    uint32_t r[32];
+    tc_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+    tc_wait_ld();
+    int ncols = e.n - col;
+    if (ncols > 32) ncols = 32;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * e.inv;
+    if (e.bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) v[i] += static_cast<float>(e.bias[col + i]);
+    }
+    uint8_t* box = e.staging + (boxes & 1u) * (EPI_BOX_BYTES / 2);
+    if (boxes >= 2u) {
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+    }
+    // row `lane` of the box is 64 bytes = four 16-byte chunks; chunk j lives at j ^ ((lane >> 1) & 3)
+    uint8_t* rowp = box + lane * 64;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        OutT lo = static_cast<OutT>(v[q * 8 + 2 * h]), hi = static_cast<OutT>(v[q * 8 + 2 * h + 1]);
+        w[h] = (uint32_t)(*reinterpret_cast<unsigned short*>(&lo)) |
+               ((uint32_t)(*reinterpret_cast<unsigned short*>(&hi)) << 16);
+      }
+      *reinterpret_cast<uint4*>(rowp + ((q ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (e.store_evict_first) tma_store_2d_hint(e.tma_out, box, col, row0, l2_policy(1));
+      else tma_store_2d(e.tma_out, box, col, row0);
+      bulk_commit();
+    }
+    ++boxes;
+  }
+}
+
+// Epilogue of the kernels whose accumulator fills TMEM: half boxes for 16-bit outputs when the TMA
+// store path is on (`use_tma` then means the output map was encoded with half boxes).
+template <typename OutT>
+__device__ __forceinline__ void drain_wide(const EpilogueArgs<OutT>& e, uint32_t taddr, int row0, int col0,
+                                           int ncol_total, uint32_t& boxes) {
+  if constexpr (sizeof(OutT) == 2) {
+    if (e.use_tma) {
+      drain_accumulator_halfbox<OutT>(e, taddr, row0, col0, ncol_total, boxes);
+      return;
+    }
+  }
+  drain_accumulator_1box<OutT>(e, taddr, row0, col0, ncol_total, boxes);
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(WTHREADS, 1)
 gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -809,7 +880,7 @@ gemm_fp8_wide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
-      drain_accumulator_1box<OutT>(ea, taddr, tc.m * WBM + half * 128 + quarter * 32, tc.n * WBN, WBN, boxes);
+      drain_wide<OutT>(ea, taddr, tc.m * WBM + half * 128 + quarter * 32, tc.n * WBN, WBN, boxes);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty);
@@ -1219,19 +1290,24 @@ static int encode_operand_map_mn(CUtensorMap* map, const void* base, int64_t row
 }
 
 // Output tensor map for the TMA-store epilogue: boxes of 32 rows x 128 bytes, 128B swizzle.
-static int encode_output_map(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int out_dtype) {
+// `half_boxes` (16-bit outputs only): boxes of 32 rows x 64 bytes with the 64-byte swizzle, the unit
+// the wide kernels' epilogue stages (two of them alternate per warp).
+static int encode_output_map(CUtensorMap* map, void* base, int64_t m, int64_t n, int64_t ldo, int out_dtype,
+                             bool half_boxes = false) {
   auto fn = get_encode_fn();
   if (fn == nullptr) return F8B200_ERR_DRIVER;
   const int esz = out_dtype == F8B200_FP32 ? 4 : 2;
+  half_boxes = half_boxes && esz == 2;
   const CUtensorMapDataType dt = out_dtype == F8B200_FP32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : out_dtype == F8B200_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const cuuint64_t gdim[2] = {(cuuint64_t)n, (cuuint64_t)m};
   const cuuint64_t gstride[1] = {(cuuint64_t)(ldo * esz)};
-  const cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+  const cuuint32_t box[2] = {(cuuint32_t)((half_boxes ? 64 : 128) / esz), 32u};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, dt, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        half_boxes ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
 }
 
@@ -1446,12 +1522,13 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
     const char* e = getenv("F8B200_GEMM_STORE");
     if (e != nullptr && e[0] == 'd') use_tma = 0;
   }
-  if (use_tma) {
-    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype);
-    if (rc != F8B200_OK) return rc;
-  } else {
-    memset(&mo, 0, sizeof(mo));
-  }
+  auto encode_output = [&](bool half_boxes) {
+    if (!use_tma) {
+      memset(&mo, 0, sizeof(mo));
+      return (int)F8B200_OK;
+    }
+    return gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype, half_boxes);
+  };
   const int layouts = (a_layout << gemm::LAYOUT_A_MN_BIT) | (b_layout << gemm::LAYOUT_B_MN_BIT);
   // operand maps: K-major boxes are [box_rows] x [128 bytes of K]; MN-major boxes are always
   // [128 k rows] x [128 bytes of M or N]
@@ -1464,6 +1541,7 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
   if (mode == 1) {
     // each CTA of a pair fetches 128-row boxes of both operands
     rc = encode_operands(128);
+    if (rc == F8B200_OK) rc = encode_output(false);
     if (rc != F8B200_OK) return rc;
     const uint32_t idesc2 = gemm::pair::make_idesc_pair(a_kind, b_kind, a_layout, b_layout);
     rc = dispatch_out_dtype(out_dtype, [&](auto* tag) {
@@ -1476,6 +1554,7 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
   }
   if (mode == 2) {
     rc = encode_operands(256);
+    if (rc == F8B200_OK) rc = encode_output(true);
     if (rc != F8B200_OK) return rc;
     const uint32_t idw = gemm::wide::make_idesc_wide(a_kind, b_kind, a_layout, b_layout);
     return dispatch_out_dtype(out_dtype, [&](auto* tag) {
@@ -1486,6 +1565,8 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
   }
   // one CTA per 128x256 tile (F8B200_GEMM_MODE=1cta): K-major operands, fixed tile stride
   if (a_layout != 0 || b_layout != 0) return F8B200_ERR_UNSUPPORTED;
+  rc = encode_output(false);
+  if (rc != F8B200_OK) return rc;
   rc = gemm::encode_operand_map(&ma, a, m, k, lda, gemm::BM);
   if (rc != F8B200_OK) return rc;
   rc = gemm::encode_operand_map(&mb, b, n, k, ldb, gemm::BN);

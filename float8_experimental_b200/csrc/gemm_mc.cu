@@ -270,7 +270,7 @@ gemm_fp8_mc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 256);
-      drain_accumulator_1box<OutT>(ea, taddr, tile_m * WBM + half * 128 + quarter * 32, tile_n * WBN, WBN, boxes);
+      drain_wide<OutT>(ea, taddr, tile_m * WBM + half * 128 + quarter * 32, tile_n * WBN, WBN, boxes);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty);
@@ -381,7 +381,7 @@ extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64
     if (e != nullptr && e[0] == 'd') use_tma = 0;
   }
   if (use_tma) {
-    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype);
+    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype, true);
     if (rc != F8B200_OK) return rc;
   } else {
     memset(&mo, 0, sizeof(mo));
