@@ -30,6 +30,7 @@ EXPORTS = (
     "f8b200_multi_amax",
     "f8b200_amax_to_scale",
     "f8b200_cast",
+    "f8b200_cast_scatter",
     "f8b200_transpose_u8",
     "f8b200_delayed_sync",
     "f8b200_gemm_fp8",
@@ -72,6 +73,8 @@ def load() -> ctypes.CDLL:
     lib.f8b200_multi_amax.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(i64), i32, i32, vp, vp]
     lib.f8b200_amax_to_scale.argtypes = [vp, i64, i32, i32, i32, vp, vp]
     lib.f8b200_cast.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, vp, i64, vp, i64, vp, i32, vp]
+    lib.f8b200_cast_scatter.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, ctypes.POINTER(vp), i32, i64,
+                                        vp]
     lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
     lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
@@ -417,6 +420,20 @@ def swiglu_cast(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: in
                                       amax.data_ptr(), fp8_code(out.dtype), _ptr(scale_out), out.data_ptr(), ld_out,
                                       _stream(a)),
             "f8b200_swiglu_cast",
+        )
+
+
+def cast_scatter(x: torch.Tensor, rows: int, cols: int, ld_x: int, amax: torch.Tensor, scale_out: torch.Tensor,
+                 fp8_kind: int, out_ptrs: Sequence[int], ld_out: int) -> None:
+    """Dynamic cast of `x` whose row-major bytes go to every address in `out_ptrs` (this
+    device's own buffer and peer-mapped buffers of other devices)."""
+    _require_cuda(x, amax, scale_out)
+    arr = (ctypes.c_void_p * len(out_ptrs))(*[ctypes.c_void_p(p) for p in out_ptrs])
+    with _Launch("cast", x.device):
+        _check(
+            load().f8b200_cast_scatter(x.data_ptr(), hp_code(x.dtype), rows, cols, ld_x, 1, amax.data_ptr(),
+                                       scale_out.data_ptr(), 0, fp8_kind, arr, len(out_ptrs), ld_out, _stream(x)),
+            "f8b200_cast_scatter",
         )
 
 

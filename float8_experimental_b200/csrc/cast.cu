@@ -145,6 +145,9 @@ struct CastParams {
   uint32_t* amax_out;
   int reverse;
   int64_t tiles_c, ntiles;
+  // further destinations of the row-major bytes (same row pitch): the gathered buffers of peer GPUs
+  uint8_t* out_more[F8B200_CAST_MAX_EXTRA];
+  int n_more;
 };
 
 template <int HP>
@@ -269,6 +272,13 @@ __global__ void __launch_bounds__(256, 3) cast_tile_kernel(const CastParams p) {
     for (int i = 0; i < 16; ++i) {
       const int64_t r = row0 + i;
       if (r < p.rows) *reinterpret_cast<uint32_t*>(p.out + r * p.ld_out + col) = rw[i];
+    }
+  }
+  for (int d = 0; d < p.n_more && col_ok; ++d) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t r = row0 + i;
+      if (r < p.rows) *reinterpret_cast<uint32_t*>(p.out_more[d] + r * p.ld_out + col) = rw[i];
     }
   }
   if (p.out_t != nullptr) {
@@ -463,6 +473,12 @@ __global__ void __launch_bounds__(256, 2) cast_tile8_kernel(const CastParams p) 
     for (int i = 0; i < 8; ++i)
       if (i < nrows) *reinterpret_cast<uint2*>(dst + i * p.ld_out) = make_uint2(lo[i], hi[i]);
   }
+  for (int d = 0; d < p.n_more; ++d) {  // the same bytes into every peer's gathered buffer
+    uint8_t* dst = p.out_more[d] + r0 * p.ld_out + c0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nrows) *reinterpret_cast<uint2*>(dst + i * p.ld_out) = make_uint2(lo[i], hi[i]);
+  }
   if (p.out_t != nullptr) {
     store_transposed_tile8(lo, hi, smem_t, p.out_t, p.ld_out_t, tile_row0, tile_col0, p.rows, p.cols);
   }
@@ -493,6 +509,7 @@ __global__ void __launch_bounds__(256) cast_generic_kernel(const CastParams p) {
     if (!p.product_fp32) pr = round_hp<HP>(pr);
     const uint8_t b = (uint8_t)(cvt_pair<KIND>(pr, 0.0f) & 0xFFu);
     if (p.out != nullptr) p.out[r * p.ld_out + c] = b;
+    for (int d = 0; d < p.n_more; ++d) p.out_more[d][r * p.ld_out + c] = b;
     if (p.out_t != nullptr) p.out_t[c * p.ld_out_t + r] = b;
   }
   if (p.amax_out != nullptr) block_atomic_max(acc.f32_bits(), p.amax_out, smem_max);
@@ -699,11 +716,15 @@ extern "C" int f8b200_amax_to_scale(const float* amax, int64_t n, int fp8_kind, 
   return check_launch();
 }
 
-extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
-                           const float* scale_in, float* scale_out, int product_fp32, int fp8_kind, void* out,
-                           int64_t ld_out, void* out_t, int64_t ld_out_t, float* amax_out, int reverse,
-                           void* stream) {
+static int cast_impl(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
+                     const float* scale_in, float* scale_out, int product_fp32, int fp8_kind, void* out, int64_t ld_out,
+                     void* out_t, int64_t ld_out_t, float* amax_out, int reverse, void* const* more_outs, int n_more,
+                     void* stream) {
   if (rows < 0 || cols < 0 || hp_dtype < 0 || hp_dtype > 2 || fp8_kind < 0 || fp8_kind > 1) return F8B200_ERR_BAD_ARG;
+  if (n_more < 0 || n_more > F8B200_CAST_MAX_EXTRA || (n_more > 0 && (more_outs == nullptr || ld_out < cols)))
+    return F8B200_ERR_BAD_ARG;
+  for (int d = 0; d < n_more; ++d)
+    if (more_outs[d] == nullptr) return F8B200_ERR_BAD_ARG;
   if (scale_src < 0 || scale_src > 1 || scale_in == nullptr) return F8B200_ERR_BAD_ARG;
   if (ld_x < cols || (out != nullptr && ld_out < cols) || (out_t != nullptr && ld_out_t < rows)) return F8B200_ERR_BAD_ARG;
   if (rows > 0 && cols > 0 && x == nullptr) return F8B200_ERR_BAD_ARG;
@@ -723,6 +744,15 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
   p.out = static_cast<uint8_t*>(out); p.ld_out = ld_out;
   p.out_t = static_cast<uint8_t*>(out_t); p.ld_out_t = ld_out_t;
   p.amax_out = reinterpret_cast<uint32_t*>(amax_out); p.reverse = reverse;
+  p.n_more = n_more;
+  bool more4 = ld_out % 4 == 0, more8 = ld_out % 8 == 0;
+  for (int d = 0; d < F8B200_CAST_MAX_EXTRA; ++d) {
+    p.out_more[d] = d < n_more ? static_cast<uint8_t*>(more_outs[d]) : nullptr;
+    if (d < n_more) {
+      more4 = more4 && aligned_to(more_outs[d], 4);
+      more8 = more8 && aligned_to(more_outs[d], 8);
+    }
+  }
   p.tiles_c = (cols + 127) / 128;
   p.ntiles = p.tiles_c * ((rows + 127) / 128);
   const bool empty = rows == 0 || cols == 0;
@@ -732,10 +762,10 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
   }
   const bool fast = cols % 4 == 0 && ld_x % 4 == 0 && aligned_to(x, 4 * es) &&
                     (out == nullptr || (ld_out % 4 == 0 && aligned_to(out, 4))) &&
-                    (out_t == nullptr || (ld_out_t % 16 == 0 && aligned_to(out_t, 16)));
+                    (out_t == nullptr || (ld_out_t % 16 == 0 && aligned_to(out_t, 16))) && (n_more == 0 || more4);
   const bool fast8 = cols % 8 == 0 && (ld_x * es) % 16 == 0 && aligned_to(x, 16) &&
                      (out == nullptr || (ld_out % 8 == 0 && aligned_to(out, 8))) &&
-                     (out_t == nullptr || (ld_out_t % 8 == 0 && aligned_to(out_t, 8)));
+                     (out_t == nullptr || (ld_out_t % 8 == 0 && aligned_to(out_t, 8))) && (n_more == 0 || more8);
   return dispatch_hp(hp_dtype, [&](auto hp) {
     constexpr int HP = decltype(hp)::value;
     if (empty) {
@@ -768,6 +798,22 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
     }
     return check_launch();
   });
+}
+
+extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
+                           const float* scale_in, float* scale_out, int product_fp32, int fp8_kind, void* out,
+                           int64_t ld_out, void* out_t, int64_t ld_out_t, float* amax_out, int reverse,
+                           void* stream) {
+  return cast_impl(x, hp_dtype, rows, cols, ld_x, scale_src, scale_in, scale_out, product_fp32, fp8_kind, out, ld_out,
+                   out_t, ld_out_t, amax_out, reverse, nullptr, 0, stream);
+}
+
+extern "C" int f8b200_cast_scatter(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
+                                   const float* scale_in, float* scale_out, int product_fp32, int fp8_kind,
+                                   void* const* outs, int n_outs, int64_t ld_out, void* stream) {
+  if (outs == nullptr || n_outs < 1 || n_outs > F8B200_CAST_MAX_EXTRA + 1) return F8B200_ERR_BAD_ARG;
+  return cast_impl(x, hp_dtype, rows, cols, ld_x, scale_src, scale_in, scale_out, product_fp32, fp8_kind, outs[0],
+                   ld_out, nullptr, 0, nullptr, 0, outs + 1, n_outs - 1, stream);
 }
 
 extern "C" int f8b200_transpose_u8(const void* in, int64_t rows, int64_t cols, int64_t ld_in, void* out,

@@ -112,6 +112,22 @@ int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t
                 float* amax_out, int reverse, void* stream);
 
 /*
+ * f8b200_cast whose row-major result goes to n_outs destinations at once (1 <= n_outs <=
+ * F8B200_CAST_MAX_EXTRA + 1, all with row pitch ld_out; `outs` is a HOST array of device
+ * pointers).  With the destinations being this rank's slot in the gathered buffer of every
+ * rank (peer-mapped memory, plain stores over NVLink), the cast IS the all-gather: it
+ * replaces the cast followed by the fp8 all-gather of
+ * float8_experimental/float8_tensor_parallel.py:49-60 (Float8ColwiseParallel input) and
+ * float8_experimental/fsdp_utils.py:168-207.  The caller orders the stores against the
+ * readers (one collective on the same stream after the call, another before the next use of
+ * the buffers).  No transposed copy, no amax output.
+ */
+#define F8B200_CAST_MAX_EXTRA 15
+int f8b200_cast_scatter(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                        int scale_src, const float* scale_in, float* scale_out, int product_fp32,
+                        int fp8_kind, void* const* outs, int n_outs, int64_t ld_out, void* stream);
+
+/*
  * out[c, r] = in[r, c] for an fp8 (byte) matrix [rows, cols].  Replaces the
  * `.contiguous()` / `.t().contiguous().t()` fix-ups in
  * float8_experimental/float8_ops.py:150-153 when no transposed copy was emitted by

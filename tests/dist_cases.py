@@ -289,6 +289,59 @@ def case_tensor_parallel(rank, world, port, sequence_parallel):
     dist.destroy_process_group()
 
 
+def case_cast_all_gather_over_peer_memory(rank, world, port):
+    """The cast that scatters its result into every rank's gathered buffer (peer stores) gives
+    the bytes and the scale of cast-then-NCCL-all-gather; repeated calls reuse the buffers.
+    GPU only: symmetric memory needs peer access."""
+    _init(rank, world, port)
+    from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic
+    from float8_experimental_b200.float8_tensor import LinearMMConfig
+    from float8_experimental_b200.fp8_all_gather import CastAllGather
+
+    gather = CastAllGather(max_numel_per_rank=8192 * 8192)
+    cfg = LinearMMConfig()
+    for it, (rows, cols) in enumerate([(8192, 8192), (1000, 520), (8192, 8192)]):
+        g = torch.Generator(device="cuda").manual_seed(100 * it + rank)
+        x = torch.randn(rows, cols, device="cuda", generator=g).mul_(1.0 + rank).to(torch.bfloat16)
+        got = gather(x)
+        # reference route: global-amax cast, then the NCCL all-gather of the bytes
+        ref_local = hp_tensor_to_float8_dynamic(x, torch.float8_e4m3fn, cfg, reduce_amax=True)
+        ref = torch.empty(world * rows, cols, dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(ref, ref_local._data.view(torch.uint8).contiguous())
+        assert got._scale.item() == ref_local._scale.item()
+        assert got._data.shape == (world * rows, cols)
+        assert torch.equal(got._data.view(torch.uint8), ref)
+    # timing of the two routes on the [8192, 8192] shard (events on this rank, after warm-up)
+    x = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    ref = torch.empty(world * 8192, 8192, dtype=torch.uint8, device="cuda")
+
+    def fused():
+        gather(x)
+
+    def unfused():
+        r = hp_tensor_to_float8_dynamic(x, torch.float8_e4m3fn, cfg, reduce_amax=True)
+        dist.all_gather_into_tensor(ref, r._data.view(torch.uint8))
+
+    out = {}
+    for name, fn in (("fused", fused), ("unfused", unfused)):
+        for _ in range(3):
+            fn()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        s0.record()
+        for _ in range(10):
+            fn()
+        s1.record()
+        torch.cuda.synchronize()
+        out[name] = s0.elapsed_time(s1) / 10
+    if rank == 0:
+        print(f"CAST_ALL_GATHER world={world} shard=8192x8192 bf16: fused {out['fused']:.3f} ms, "
+              f"cast + NCCL all-gather {out['unfused']:.3f} ms", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _all_gather_list(t, world):
     outs = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(outs, t.contiguous())

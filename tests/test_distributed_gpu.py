@@ -10,7 +10,7 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
-WORLD = 2
+WORLD = int(os.environ.get("F8_DIST_WORLD", "2"))  # ranks = GPUs used by every case
 
 
 def _free_port() -> int:
@@ -31,7 +31,7 @@ def _entry(rank, case, world, port, extra):
 
 def _run(case, *extra):
     if torch.cuda.device_count() < WORLD:
-        pytest.skip("needs two GPUs")
+        pytest.skip(f"needs {WORLD} GPUs")
     mp.spawn(_entry, args=(case, WORLD, _free_port(), extra), nprocs=WORLD, join=True)
 
 
@@ -51,3 +51,7 @@ def test_fsdp2_delayed_weight_scaling():
 @pytest.mark.parametrize("sequence_parallel", [False, True])
 def test_tensor_parallel_matches_unsharded(sequence_parallel):
     _run("case_tensor_parallel", sequence_parallel)
+
+
+def test_cast_all_gather_over_peer_memory():
+    _run("case_cast_all_gather_over_peer_memory")
