@@ -25,8 +25,6 @@ namespace mc {
 
 using namespace wide;
 
-constexpr int MAX_CLUSTER = 4;
-
 __device__ __forceinline__ void tma_load_2d_mcast(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
                                                   uint16_t cta_mask, uint64_t policy) {
   asm volatile(
