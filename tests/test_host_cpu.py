@@ -352,3 +352,24 @@ def test_package_has_no_cpu_path():
     )
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT)
     assert "RAISED" in out.stdout, out.stdout + out.stderr
+
+
+def test_gemm_operand_layout_selection():
+    """How `scaled_mm` hands an operand to the GEMM: as it lies when K or the rows are contiguous
+    and TMA can address it, else as a K-major copy."""
+    from float8_experimental_b200._ops import _gemm_operand
+
+    base = torch.zeros(64, 48, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    t, ld, mn = _gemm_operand(base)                      # [64, 48], K contiguous
+    assert t is base and ld == 48 and mn is False
+    t, ld, mn = _gemm_operand(base.t())                  # logical [48, 64] stored [64, 48]: rows contiguous
+    assert t.data_ptr() == base.data_ptr() and ld == 48 and mn is True
+    odd = torch.zeros(64, 40, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    t, ld, mn = _gemm_operand(odd.t())                   # pitch 40 is not a multiple of 16: copied
+    assert mn is False and t.is_contiguous() and t.shape == (40, 64) and ld == 64
+    sliced = base[:, 1:33]                               # K contiguous but the base address is odd
+    t, ld, mn = _gemm_operand(sliced)
+    assert mn is False and t.is_contiguous() and ld == 32
+    one_row = base[:1]
+    t, ld, mn = _gemm_operand(one_row)                   # a single row: any pitch that TMA accepts
+    assert mn is False and ld % 16 == 0 and ld >= 48
