@@ -137,18 +137,27 @@ def _delayed_sync_cuda(amax, hist, n_e4m3: int, orig_dtype: int, scale_out, hist
     N.delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out, hist_out)
 
 
+def _pitch16(n: int) -> int:
+    return -(-n // 16) * 16
+
+
 def _gemm_operand(x: torch.Tensor):
     """How the GEMM can read the logical [rows, K] operand `x` where it lies: (tensor, pitch,
     mn_major).  K contiguous = K-major; rows contiguous (a transposed view of a [K, rows]
     buffer) = MN-major, which the tensor cores read through an MN-major descriptor.  Anything
-    else, or a pitch / base address that TMA cannot take, is copied to a K-major buffer."""
+    else, or a pitch / base address that TMA cannot take, is copied into a K-major buffer
+    whose row pitch is rounded up to 16 bytes.  K itself may be any number: TMA zero-fills
+    beyond it, so no operand is ever zero-padded along K (the reference pads both operands
+    with a copy when K is not a multiple of 16, float8_experimental/float8_ops.py:143-148)."""
     rows, k = x.shape
     if x.stride(1) == 1 and (rows == 1 or (x.stride(0) >= k and x.stride(0) % 16 == 0)) and x.data_ptr() % 16 == 0:
-        return x, (x.stride(0) if rows > 1 else -(-k // 16) * 16), False
+        return x, (x.stride(0) if rows > 1 else _pitch16(k)), False
     if x.stride(0) == 1 and k > 1 and x.stride(1) >= rows and x.stride(1) % 16 == 0 and x.data_ptr() % 16 == 0:
         return x, x.stride(1), True
-    x = x.contiguous()
-    return x, x.stride(0), False
+    buf = torch.empty((rows, _pitch16(k)), dtype=torch.uint8, device=x.device)
+    view = buf[:, :k]
+    view.copy_(x.view(torch.uint8))
+    return view.view(x.dtype), buf.stride(0), False
 
 
 def _scaled_mm_cuda(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum: bool):

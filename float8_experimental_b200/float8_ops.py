@@ -16,7 +16,6 @@ from torch.utils._pytree import tree_map
 from ._ops import ops
 from .float8_python_api import addmm_float8_unwrapped
 from .float8_tensor import choose_scaled_mm_config, Float8Tensor
-from .float8_utils import pad_tensor_for_matmul
 
 aten = torch.ops.aten
 c10d_functional = torch.ops.c10d_functional
@@ -164,9 +163,9 @@ def _col_major_operand_as_nk(t: Float8Tensor) -> torch.Tensor:
 
 
 def preprocess_addmm(a: Float8Tensor, b: Float8Tensor):
-    """Operands in the layout the GEMM wants: A [M,K] row-major, B column-major
-    (returned as a [K,N] view of an [N,K] row-major buffer); optional zero padding of K
-    to a multiple of 16 (reference: float8_ops.py:131-155)."""
+    """Operands as the GEMM can read them: A [M,K] and B (returned as a [K,N] view of its [N,K]
+    form), each K-major or MN-major as it lies; the inner-dimension contract of the reference
+    (float8_ops.py:131-155) without its padding copies."""
     cfg = choose_scaled_mm_config(a._gemm_input_role, a._linear_mm_config, b._gemm_input_role, b._linear_mm_config)
     a_data = _row_major_operand(a)
     b_nk = _col_major_operand_as_nk(b)
@@ -174,15 +173,14 @@ def preprocess_addmm(a: Float8Tensor, b: Float8Tensor):
         assert a._data.size(1) == b._data.size(
             0
         ), f"Inner dims must match for mm, got {a._data.size(1)} and {b._data.size(0)}"
-    if a_data.shape[1] % 16 != 0:
-        if not cfg.pad_inner_dim:
-            raise RuntimeError(
-                f"float8 GEMM needs the inner dimension to be a multiple of 16, got {a_data.shape[1]}; "
-                "set Float8LinearConfig.pad_inner_dim=True"
-            )
-        dt = a_data.dtype, b_nk.dtype
-        a_data = pad_tensor_for_matmul(a_data.view(torch.uint8), dims=1).view(dt[0])
-        b_nk = pad_tensor_for_matmul(b_nk.view(torch.uint8), dims=1).view(dt[1])
+    if a_data.shape[1] % 16 != 0 and not cfg.pad_inner_dim:
+        # same contract as the reference, whose cuBLASLt path needs K % 16 == 0 unless it pads
+        raise RuntimeError(
+            f"float8 GEMM needs the inner dimension to be a multiple of 16, got {a_data.shape[1]}; "
+            "set Float8LinearConfig.pad_inner_dim=True"
+        )
+    # with pad_inner_dim nothing is padded here: the GEMM takes any K (TMA zero-fills the tail) and
+    # `scaled_mm` gives an operand whose row pitch TMA cannot take a pitch-aligned copy
     return a_data, a._scale, b_nk.t(), b._scale
 
 

@@ -370,6 +370,10 @@ def test_gemm_operand_layout_selection():
     sliced = base[:, 1:33]                               # K contiguous but the base address is odd
     t, ld, mn = _gemm_operand(sliced)
     assert mn is False and t.is_contiguous() and ld == 32
+    ragged = torch.arange(8 * 40, dtype=torch.uint8).view(8, 40).view(torch.float8_e4m3fn)
+    t, ld, mn = _gemm_operand(ragged)                    # K = 40: the copy gets a 48-byte row pitch, K stays 40
+    assert mn is False and ld == 48 and t.shape == (8, 40) and t.stride(0) == 48
+    assert torch.equal(t.view(torch.uint8), ragged.view(torch.uint8))
     one_row = base[:1]
     t, ld, mn = _gemm_operand(one_row)                   # a single row: any pitch that TMA accepts
     assert mn is False and ld % 16 == 0 and ld >= 48

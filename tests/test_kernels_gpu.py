@@ -310,6 +310,25 @@ def test_gemm_mn_major_operands(mnk, layouts, mode, monkeypatch):
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
 
 
+@pytest.mark.parametrize("mnk", [(256, 384, 100), (300, 72, 1000 + 8), (1024, 512, 16384 + 40)])
+def test_gemm_inner_dimension_need_not_be_a_multiple_of_16(mnk, gemm_mode):
+    """K is free as long as the row pitch is a multiple of 16 bytes: TMA zero-fills beyond K."""
+    m, n, k = mnk
+    pitch = -(-k // 16) * 16
+    g = torch.Generator(device="cuda").manual_seed(k)
+    a_buf = torch.randn(m, pitch, device="cuda", generator=g).to(torch.float8_e4m3fn)  # junk beyond K
+    b_buf = torch.randn(n, pitch, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    a, b = a_buf[:, :k], b_buf[:, :k]
+    one = torch.tensor(1.0, device="cuda")
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    N.gemm_fp8(a, pitch, b, pitch, one, one, None, out, n, m, n, k, False)
+    torch.cuda.synchronize()
+    assert N.read_device_error() == 0
+    ref = a.float() @ b.float().t()
+    check_gemm(out, ref)
+    assert (out - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item())
+
+
 def test_cast_full_size_properties():
     """Full-size activation (16384 x 8192 bf16): the oracle is too slow here, so check
     size-independent properties: amax equals max|x|; the transposed copy is the transpose;

@@ -242,3 +242,28 @@ def test_float8_linear_step_is_capturable_in_a_cuda_graph():
     want = [y2.detach(), x2.grad, m.weight.grad, m.bias.grad]
     for g, w in zip(got, want):
         assert torch.equal(g, w)
+
+
+@pytest.mark.parametrize("features", [(100, 72), (72, 100), (1000, 520)])
+def test_pad_inner_dim_without_padding_copies(features):
+    """in/out features that are not multiples of 16 (and a token count that is not either):
+    `pad_inner_dim=True` works and gives the result of the bf16 layer within fp8 tolerance;
+    without it the call is refused as in the reference."""
+    k, n = features
+    lin = nn.Linear(k, n, bias=False, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(50, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(50, n, device="cuda", dtype=torch.bfloat16)
+    m = Float8Linear.from_float(lin, f8.Float8LinearConfig(pad_inner_dim=True))
+    y = m(x)
+    y.backward(go)
+    x2 = x.detach().clone().requires_grad_(True)
+    y_ref = lin(x2)
+    y_ref.backward(go)
+    assert compute_error(y_ref.float(), y.detach().float()) > 18.0
+    assert compute_error(x2.grad.float(), x.grad.float()) > 17.0
+    assert compute_error(lin.weight.grad.float(), m.weight.grad.float()) > 17.0
+    if k % 16 != 0:
+        strict = Float8Linear.from_float(nn.Linear(k, n, bias=False, device="cuda", dtype=torch.bfloat16),
+                                         f8.Float8LinearConfig())
+        with pytest.raises(RuntimeError, match="multiple of 16"):
+            strict(x.detach())
