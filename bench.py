@@ -544,6 +544,65 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_gemm_sweep(args):
+    """Sustained per-shape comparison of GEMM variants in ONE process (box-to-box variation is
+    larger than the differences between variants): every GEMM of the step runs for ~0.6 s with
+    each variant in turn.  Variants: 2cta, 1cta, wide (kernels of libf8b200.so), mc21 / mc22 (the
+    single-GPU multicast library), auto (the default choice), cublaslt (torch._scaled_mm);
+    suffix -static = fixed tile stride, -direct = per-thread store epilogue."""
+    import torch
+
+    from float8_experimental_b200 import _native as N
+
+    dev = torch.device("cuda", 0)
+    variants = args.gemm_sweep.split(",")
+    shapes = [s for s in SHAPES if args.layers is None or s[0] in args.layers.split(",")]
+    one = torch.tensor(1.0, device=dev)
+    rows, totals = [], {v: 0.0 for v in variants}
+
+    def sustained(fn, seconds=0.6):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+        iters = max(3, int(seconds * 1e3 / e0.elapsed_time(e1)))
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    for name, k_in, n_out in shapes:
+        for tag, m, n, k, a_dt in ((".fwd", M_TOKENS, n_out, k_in, torch.float8_e4m3fn),
+                                   (".dgrad", M_TOKENS, k_in, n_out, torch.float8_e5m2),
+                                   (".wgrad", n_out, k_in, M_TOKENS, torch.float8_e5m2)):
+            a = torch.randn(m, k, device=dev).to(a_dt)
+            b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            row = {"gemm": name + tag, "m": m, "n": n, "k": k}
+            for v in variants:
+                if v == "cublaslt":
+                    fn = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
+                else:
+                    base = v.split("-")[0]
+                    os.environ["F8B200_GEMM_MC"] = base[2:] if base.startswith("mc") else "0"
+                    os.environ["F8B200_GEMM_MODE"] = "" if base in ("auto", "mc21", "mc22") else base
+                    os.environ["F8B200_GEMM_STORE"] = "direct" if v.endswith("-direct") else "tma"
+                    os.environ["F8B200_GEMM_WS"] = "0" if v.endswith("-static") else "1"
+                    if base == "auto":
+                        os.environ.pop("F8B200_GEMM_MC", None)
+                    fn = lambda: N.gemm_fp8(a, k, b, k, one, one, None, out, n, m, n, k, False)  # noqa: E731
+                ms = sustained(fn)
+                totals[v] += ms
+                row[v] = {"ms": round(ms, 4), "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+            del a, b, out
+    print(json.dumps({"gemm_sweep_totals_ms": {v: round(t, 3) for v, t in totals.items()},
+                      "device_error": N.read_device_error()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -558,12 +617,18 @@ def main():
                          "next layer's all-gather is prefetched under the current layer's GEMMs); 0 = each layer is "
                          "its own root (a root keeps its gathered weight: one all-gather per layer and step, nothing "
                          "overlaps).  Measured at N=8: 41.0 against 41.2 ms/step.")
+    ap.add_argument("--gemm-sweep", default=None,
+                    help="comma list of GEMM variants to compare per shape in one process (see run_gemm_sweep); "
+                         "prints one JSON line per GEMM and the totals, then exits")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-timed part only, short JSON; for profiler captures of a small case")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gemm_sweep:
+        run_gemm_sweep(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
