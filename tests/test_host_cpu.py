@@ -377,3 +377,26 @@ def test_gemm_operand_layout_selection():
     one_row = base[:1]
     t, ld, mn = _gemm_operand(one_row)                   # a single row: any pitch that TMA accepts
     assert mn is False and ld % 16 == 0 and ld >= 48
+
+
+def test_multicast_gemm_selection_rules(monkeypatch):
+    """The single-GPU multicast library is used only when present, only in single-process runs,
+    by default only for K >= 16384, and never when a kernel is forced."""
+    from float8_experimental_b200 import _native as N
+
+    monkeypatch.setattr(N, "load_mc", lambda: object())
+    monkeypatch.delenv("F8B200_GEMM_MC", raising=False)
+    monkeypatch.delenv("F8B200_GEMM_MODE", raising=False)
+    monkeypatch.delenv("F8B200_GEMM_WIDE_K", raising=False)
+    assert N._mc_cluster(8192, 8192, 16384) == (2, 1)
+    assert N._mc_cluster(16384, 8192, 8192) is None
+    monkeypatch.setenv("F8B200_GEMM_MODE", "wide")
+    assert N._mc_cluster(8192, 8192, 16384) is None
+    monkeypatch.delenv("F8B200_GEMM_MODE")
+    monkeypatch.setenv("F8B200_GEMM_MC", "22")
+    assert N._mc_cluster(16384, 8192, 8192) == (2, 2)
+    monkeypatch.setenv("F8B200_GEMM_MC", "0")
+    assert N._mc_cluster(8192, 8192, 16384) is None
+    monkeypatch.delenv("F8B200_GEMM_MC")
+    monkeypatch.setattr(N, "load_mc", lambda: None)  # library not shipped (runs on several GPUs)
+    assert N._mc_cluster(8192, 8192, 16384) is None
