@@ -547,8 +547,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 def run_gemm_sweep(args):
     """Sustained per-shape comparison of GEMM variants in ONE process (box-to-box variation is
     larger than the differences between variants): every GEMM of the step runs for ~0.6 s with
-    each variant in turn.  Variants: 2cta, 1cta, wide (kernels of libf8b200.so), mc21 / mc22 (the
-    single-GPU multicast library), auto (the default choice), cublaslt (torch._scaled_mm);
+    each variant in turn.  Variants: 2cta, 1cta, wide (kernels of libf8b200.so), mc21 / mc22 / mc41
+    (the single-GPU multicast library: wide tiles in 2x1 / 2x2 clusters, two CTA pairs), auto (the default choice), cublaslt (torch._scaled_mm);
     suffix -static = fixed tile stride, -direct = per-thread store epilogue."""
     import torch
 
@@ -587,7 +587,7 @@ def run_gemm_sweep(args):
                 else:
                     base = v.split("-")[0]
                     os.environ["F8B200_GEMM_MC"] = base[2:] if base.startswith("mc") else "0"
-                    os.environ["F8B200_GEMM_MODE"] = "" if base in ("auto", "mc21", "mc22") else base
+                    os.environ["F8B200_GEMM_MODE"] = "" if base in ("auto", "mc21", "mc22", "mc41") else base
                     os.environ["F8B200_GEMM_STORE"] = "direct" if v.endswith("-direct") else "tma"
                     os.environ["F8B200_GEMM_WS"] = "0" if v.endswith("-static") else "1"
                     if base == "auto":

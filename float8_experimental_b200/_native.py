@@ -301,6 +301,8 @@ def _mc_cluster(m: int, n: int, k: int):
         return (2, 1)
     if mode == "22":
         return (2, 2)
+    if mode == "41":  # two CTA pairs sharing B; K-major operands only (others fall back)
+        return (4, 1)
     forced = os.environ.get("F8B200_GEMM_MODE", "")
     if forced[:1] in ("1", "2", "w"):
         return None
@@ -339,7 +341,7 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
                                             fp8_code(b.dtype), int(b_mn_major), ldb, scale_a.data_ptr(),
                                             scale_b.data_ptr(), _ptr(bias), hp_code(out.dtype), out.data_ptr(), ldo,
                                             m, n, k, cluster[0], cluster[1], ws.data_ptr(), ws.numel(), stream)
-            if rc != -6:  # F8B200_ERR_UNSUPPORTED: such clusters cannot be scheduled here
+            if rc != -6:  # F8B200_ERR_UNSUPPORTED: such clusters cannot be scheduled here / layout not covered
                 if rc != 0:
                     raise F8B200Error(f"f8b200_mc_gemm_fp8: {load().f8b200_status_string(rc).decode()}")
                 return

@@ -340,6 +340,335 @@ static int launch_mc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
                                               sched));
 }
 
+// ===========================================================================
+// CTA pairs with multicast: a cluster of FOUR CTAs = two cta_group::2 pairs that work on two
+// 256x256 tiles with the same N range (adjacent in M).  Both pairs need the same 256 rows of B,
+// 128 per CTA as in the pair kernel; the CTAs with the same position in their pairs split those
+// 128 rows and multicast their 64-row box to each other, so a CTA pulls 16 + 8 KB per k-block
+// through L2 instead of 32 KB and the epilogue stays hidden behind the next tile's MMAs (two
+// accumulators in TMEM), which the wide multicast kernel above cannot offer.
+//
+// Every CTA has its own full[s] (its own A box + the two B boxes multicast into it).  The pair's
+// MMAs are issued by its leader, which cannot wait on its partner's barrier; the partner's
+// otherwise idle MMA warp relays: it waits for its local full[s] and arrives (release.cluster)
+// on peer_full[s] in the leader.  empty[s] counts two arrivals, one tcgen05.commit from each
+// pair's leader, multicast to all four CTAs: a B box may only be overwritten once both pairs have
+// consumed the stage.
+// ===========================================================================
+namespace pairmc {
+
+using namespace pair;
+
+struct __align__(8) PairMcBarriers {
+  uint64_t full[PSTAGES];
+  uint64_t peer_full[PSTAGES];  // used in the pair leaders
+  uint64_t empty[PSTAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  TileRing ring;
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+constexpr int PMC_SMEM_BYTES = PSTAGES * PSTAGE_BYTES + EPI_STAGING_BYTES + 1024 + (int)sizeof(PairMcBarriers);
+constexpr int PMC_CLUSTER = 4;
+
+template <bool CLUSTER_ACQUIRE = false>
+__device__ __forceinline__ bool pmc_wait(uint64_t* bar, uint32_t parity, PairMcBarriers* bars, uint32_t who,
+                                         uint32_t backoff_ns = 0) {
+  auto probe = [&]() { return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  if (probe()) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
+    if (probe()) return true;
+    if (backoff_ns != 0u) __nanosleep(backoff_ns);
+    if ((it & 63u) == 63u) {
+      if (bars->abort_flag != 0u) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
+    }
+  }
+  for (int r = 0; r < PMC_CLUSTER; ++r)
+    st_cluster_u32(mapa_u32(smem_u32(const_cast<uint32_t*>(&bars->abort_flag)), (uint32_t)r), 1u);
+  atomicOr(&g_device_error, who | 0x800u);
+  return false;
+}
+
+__device__ __forceinline__ int32_t pmc_ring_read(PairMcBarriers* bars, uint32_t j, uint32_t who, uint32_t backoff_ns) {
+  const uint32_t slot = j & (RING - 1);
+  if (!pmc_wait<true>(&bars->ring.full[slot], (j >> 4) & 1u, bars, who, backoff_ns)) return -2;
+  return *reinterpret_cast<volatile int32_t*>(&bars->ring.tile[slot]);
+}
+
+__device__ __forceinline__ void tc_commit_pair_mask(uint64_t* bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+// K-major operands only.
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_pairmc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                       const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
+                       const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
+                       int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store, int raster,
+                       uint32_t* sched) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = tiles + PSTAGES * PSTAGE_BYTES;
+  PairMcBarriers* bars = reinterpret_cast<PairMcBarriers*>(staging + EPI_STAGING_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0..3
+  const uint32_t pr = rank >> 1, r = rank & 1u;  // pair in the cluster, position in the pair
+  const bool leader = r == 0;
+  const uint32_t my_leader = rank & ~1u;
+  const uint16_t pair_mask = (uint16_t)(3u << (2 * pr));
+  const uint16_t b_mask = (uint16_t)((1u << r) | (1u << (r + 2)));  // same position in both pairs
+  const int stiles_m = (m + 2 * PBM - 1) / (2 * PBM), tiles_n = (n + PBN - 1) / PBN;
+  const int64_t num_tiles = (int64_t)stiles_m * tiles_n;  // blocks of two tiles
+  const int num_kb = (k + BK - 1) / BK;
+  const int64_t cluster_id = blockIdx.x / PMC_CLUSTER, num_clusters = gridDim.x / PMC_CLUSTER;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->peer_full[s], 1);
+      mbar_init(&bars->empty[s], 2);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 8);
+    }
+    for (int q = 0; q < RING; ++q) mbar_init(&bars->ring.full[q], 1);
+    bars->abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (every CTA) ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      const uint64_t pol = l2_policy(0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const int claim_kb = num_kb > 4 ? num_kb - 4 : 0;
+      uint32_t entry = 0;
+      int64_t t = cluster_id;
+      while (ok && t < num_tiles) {
+        const TileCoord tc = tile_coord(t, stiles_m, tiles_n, raster);
+        const int row_a = (tc.m * 2 + (int)pr) * PBM + (int)r * 128;      // my 128 rows of my pair's A tile
+        const int row_b = tc.n * PBN + (int)r * 128 + (int)pr * 64;       // my 64 of the 128 B rows CTAs r need
+        int64_t next = t + num_clusters;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (sched != nullptr && rank == 0 && kb == claim_kb) next = num_clusters + (int64_t)atomicAdd(sched, 1u);
+          if (!pmc_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * PSTAGE_BYTES;
+          mbar_expect_tx(&bars->full[stage], PSTAGE_BYTES);
+          tma_load_2d_hint(sa, &tma_a, kb * BK, row_a, &bars->full[stage], pol);
+          mc::tma_load_2d_mcast(sa + PA_BYTES + pr * 64 * BK, &tma_b, kb * BK, row_b, &bars->full[stage], b_mask, pol);
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (sched != nullptr) {
+          if (rank == 0) {
+            const uint32_t slot = entry & (RING - 1);
+            const int32_t v = next < num_tiles ? (int32_t)next : -1;
+            bars->ring.tile[slot] = v;
+            mbar_arrive(&bars->ring.full[slot]);
+#pragma unroll
+            for (int q = 1; q < PMC_CLUSTER; ++q) {
+              st_cluster_u32(mapa_u32(smem_u32(&bars->ring.tile[slot]), (uint32_t)q), (uint32_t)v);
+              mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->ring.full[slot]), (uint32_t)q));
+            }
+          } else {
+            const int32_t v = pmc_ring_read(bars, entry, 64u, 32u);
+            if (v == -2) { ok = false; break; }
+            next = v < 0 ? num_tiles : (int64_t)v;
+          }
+          ++entry;
+        }
+        t = next;
+      }
+      for (int s = 0; ok && s < PSTAGES; ++s) {
+        if (!pmc_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
+        if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (pair leaders) ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      int64_t t = cluster_id;
+      for (; ok && t < num_tiles; ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!pmc_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, bars, 2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * PBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pmc_wait(&bars->full[stage], phase, bars, 4u)) { ok = false; break; }
+          if (!pmc_wait<true>(&bars->peer_full[stage], phase, bars, 4u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * PSTAGE_BYTES);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + PA_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            tc_mma_f8_pair(tmem_d, da + (uint64_t)(kk * (UMMA_K >> 4)), db + (uint64_t)(kk * (UMMA_K >> 4)), idesc,
+                           (kb | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair_mask(&bars->empty[stage], (uint16_t)0xF);
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair_mask(&bars->tmem_full[acc], pair_mask);
+        if (sched != nullptr) {
+          const int32_t v = pmc_ring_read(bars, (uint32_t)local, 16u, 0u);
+          if (v == -2) { ok = false; break; }
+          t = v < 0 ? num_tiles : (int64_t)v;
+        } else {
+          t += num_clusters;
+        }
+      }
+    } else if (lane == 0) {
+      // ---------------- relay (pair partners): my stage has landed -> tell my leader ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      int64_t t = cluster_id;
+      for (; ok && t < num_tiles; ++local) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pmc_wait(&bars->full[stage], phase, bars, 128u)) { ok = false; break; }
+          mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->peer_full[stage]), my_leader));
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (sched != nullptr) {
+          const int32_t v = pmc_ring_read(bars, (uint32_t)local, 128u, 0u);
+          if (v == -2) { ok = false; break; }
+          t = v < 0 ? num_tiles : (int64_t)v;
+        } else {
+          t += num_clusters;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of every CTA) ----------------
+    const int quarter = warp & 3;
+    float inv = 0.f;
+    {
+      const float sa = __ldg(scale_a), sb = __ldg(scale_b);
+      inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
+    }
+    const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
+                                staging + (warp - 2) * 2 * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
+    uint32_t boxes = 0;
+    bool ok = true;
+    int64_t local = 0;
+    int64_t t = cluster_id;
+    for (; ok && t < num_tiles; ++local) {
+      const TileCoord tc = tile_coord(t, stiles_m, tiles_n, raster);
+      const int acc = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      int got = 1;
+      if (lane == 0) got = pmc_wait(&bars->tmem_full[acc], acc_phase, bars, 8u, 256u) ? 1 : 0;
+      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PBN);
+      drain_accumulator<OutT>(ea, taddr, (tc.m * 2 + (int)pr) * PBM + (int)r * 128 + quarter * 32, tc.n * PBN, PBN, boxes);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), my_leader));
+      if (sched != nullptr) {
+        int v = 0;
+        if (lane == 0) v = pmc_ring_read(bars, (uint32_t)local, 32u, 64u);
+        v = __shfl_sync(0xFFFFFFFFu, v, 0);
+        if (v == -2) { ok = false; break; }
+        t = v < 0 ? num_tiles : (int64_t)v;
+      } else {
+        t += num_clusters;
+      }
+    }
+    if (use_tma_store && lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+template <typename OutT>
+static int launch_pairmc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
+                         const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
+                         uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  static int max_clusters = 0;
+  auto kernel = gemm_fp8_pairmc_kernel<OutT>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PMC_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = PMC_SMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PMC_SMEM_BYTES);
+    if (attr_err == cudaSuccess) {
+      cfg.gridDim = dim3(PMC_CLUSTER * (sm_count() / PMC_CLUSTER));
+      attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+    }
+  });
+  if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
+  if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
+  const int64_t tiles = (int64_t)((m + 2 * PBM - 1) / (2 * PBM)) * ((n + PBN - 1) / PBN);
+  int clusters = max_clusters;
+  if (tiles < clusters) clusters = (int)tiles;
+  cfg.gridDim = dim3(PMC_CLUSTER * clusters);
+  sched = usable_sched(sched, tiles, clusters);
+  if (sched != nullptr) {
+    const cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(uint32_t), st);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  const OutT* bias_t = static_cast<const OutT*>(bias);
+  OutT* out_t = static_cast<OutT*>(out);
+  return record_cuda_error(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc,
+                                              vec_ok, use_tma, choose_raster(m, n, k, 2 * PBM, PBN), sched));
+}
+
+}  // namespace pairmc
 }  // namespace mc
 }  // namespace gemm
 }  // namespace f8b200
@@ -354,7 +683,9 @@ extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64
   if (m < 0 || n < 0 || k < 0) return F8B200_ERR_BAD_ARG;
   if (a_kind < 0 || a_kind > 1 || b_kind < 0 || b_kind > 1 || out_dtype < 0 || out_dtype > 2) return F8B200_ERR_BAD_ARG;
   if (a_layout < 0 || a_layout > 1 || b_layout < 0 || b_layout > 1) return F8B200_ERR_BAD_ARG;
-  if (!((cluster_m == 2 && cluster_n == 1) || (cluster_m == 2 && cluster_n == 2))) return F8B200_ERR_BAD_ARG;
+  const bool pairs = cluster_m == 4 && cluster_n == 1;  // two CTA pairs sharing B (K-major operands only)
+  if (!((cluster_m == 2 && cluster_n == 1) || (cluster_m == 2 && cluster_n == 2) || pairs)) return F8B200_ERR_BAD_ARG;
+  if (pairs && (a_layout != 0 || b_layout != 0)) return F8B200_ERR_UNSUPPORTED;
   if (m == 0 || n == 0) return F8B200_OK;
   if (a == nullptr || b == nullptr || out == nullptr || scale_a == nullptr || scale_b == nullptr) return F8B200_ERR_BAD_ARG;
   if (k == 0) return F8B200_ERR_UNSUPPORTED;
@@ -379,10 +710,24 @@ extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64
     if (e != nullptr && e[0] == 'd') use_tma = 0;
   }
   if (use_tma) {
-    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype, true);
+    rc = gemm::encode_output_map(&mo, out, m, n, ldo, out_dtype, !pairs);
     if (rc != F8B200_OK) return rc;
   } else {
     memset(&mo, 0, sizeof(mo));
+  }
+  if (pairs) {
+    // A: 128-row boxes (one per CTA); B: 64-row boxes (each CTA fetches a quarter of the tile's rows)
+    rc = gemm::encode_operand_map(&ma, a, m, k, lda, 128);
+    if (rc != F8B200_OK) return rc;
+    rc = gemm::encode_operand_map(&mb, b, n, k, ldb, 64);
+    if (rc != F8B200_OK) return rc;
+    const uint32_t idp = gemm::pair::make_idesc_pair(a_kind, b_kind);
+    uint32_t* sched_p = static_cast<uint32_t*>(workspace);
+    return dispatch_out_dtype(out_dtype, [&](auto* tag) {
+      using OutT = std::remove_pointer_t<decltype(tag)>;
+      return gemm::mc::pairmc::launch_pairmc<OutT>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n,
+                                                   (int)k, idp, vec_ok, sched_p, st);
+    });
   }
   // K-major boxes hold the rows one CTA fetches per k-block: 256 / cluster_n of A, 256 / cluster_m of B
   rc = a_layout ? gemm::encode_operand_map_mn(&ma, a, m, k, lda)

@@ -23,7 +23,7 @@ def _gemm(a, b, sa, sb, m, n, k, out_dtype, bias, a_mn, b_mn):
     return out
 
 
-@pytest.mark.parametrize("cluster", ["21", "22"])
+@pytest.mark.parametrize("cluster", ["21", "22", "41"])
 @pytest.mark.parametrize("mnk", [(512, 512, 256), (4096, 2048, 1024), (300, 520, 272), (8192, 4096 + 48, 512 + 16),
                                  (1280, 768, 128), (256, 256, 64), (4096, 8192, 16384 + 128)])
 @pytest.mark.parametrize("layouts", [(False, False), (False, True), (True, True)])
@@ -46,7 +46,7 @@ def test_multicast_gemm_matches_plain_kernels(cluster, mnk, layouts, monkeypatch
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
-@pytest.mark.parametrize("cluster", ["21", "22"])
+@pytest.mark.parametrize("cluster", ["21", "22", "41"])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
 def test_multicast_gemm_bias_and_output_types(cluster, out_dtype, monkeypatch):
     m, n, k = 768, 640, 512
