@@ -348,20 +348,20 @@ static int launch_mc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
 // through L2 instead of 32 KB and the epilogue stays hidden behind the next tile's MMAs (two
 // accumulators in TMEM), which the wide multicast kernel above cannot offer.
 //
-// Every CTA has its own full[s] (its own A box + the two B boxes multicast into it).  The pair's
-// MMAs are issued by its leader, which cannot wait on its partner's barrier; the partner's
-// otherwise idle MMA warp relays: it waits for its local full[s] and arrives (release.cluster)
-// on peer_full[s] in the leader.  empty[s] counts two arrivals, one tcgen05.commit from each
-// pair's leader, multicast to all four CTAs: a B box may only be overwritten once both pairs have
-// consumed the stage.
+// full[s] lives in each pair's leader and expects the 64 KB both CTAs of the pair receive per stage,
+// as in the pair kernel.  The loads are the cta_group::2 forms, whose mbarrier operand may name the
+// partner CTA: the address of the local full[s] with the pair bit (bit 24 of a shared-window
+// address) cleared designates the even CTA of the pair, and for a multicast load it does so in
+// every destination's pair, so a B box multicast to the same position of the other pair completes
+// on that pair's leader.  empty[s] counts two arrivals, one tcgen05.commit from each pair's leader,
+// multicast to all four CTAs: a B box may only be overwritten once both pairs have consumed the stage.
 // ===========================================================================
 namespace pairmc {
 
 using namespace pair;
 
 struct __align__(8) PairMcBarriers {
-  uint64_t full[PSTAGES];
-  uint64_t peer_full[PSTAGES];  // used in the pair leaders
+  uint64_t full[PSTAGES];  // used in the pair leaders
   uint64_t empty[PSTAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
@@ -369,6 +369,26 @@ struct __align__(8) PairMcBarriers {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
+
+constexpr uint32_t PAIR_BIT_MASK = 0xFEFFFFFFu;  // clears the bit that tells the two CTAs of a pair apart
+
+// cta_group::2 loads: `leader_bar` is the local barrier address with the pair bit cleared.
+__device__ __forceinline__ void tma_load_2d_pair_local(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                       uint32_t leader_bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_mcast(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                       uint32_t leader_bar, uint16_t cta_mask, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5, %6;" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar), "h"(cta_mask), "l"(policy)
+      : "memory");
+}
 
 constexpr int PMC_SMEM_BYTES = PSTAGES * PSTAGE_BYTES + EPI_STAGING_BYTES + 1024 + (int)sizeof(PairMcBarriers);
 constexpr int PMC_CLUSTER = 4;
@@ -435,7 +455,6 @@ gemm_fp8_pairmc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < PSTAGES; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->peer_full[s], 1);
       mbar_init(&bars->empty[s], 2);
     }
     for (int a = 0; a < 2; ++a) {
@@ -479,9 +498,10 @@ gemm_fp8_pairmc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           if (sched != nullptr && rank == 0 && kb == claim_kb) next = num_clusters + (int64_t)atomicAdd(sched, 1u);
           if (!pmc_wait(&bars->empty[stage], phase ^ 1u, bars, 1u, 64u)) { ok = false; break; }
           uint8_t* sa = tiles + stage * PSTAGE_BYTES;
-          mbar_expect_tx(&bars->full[stage], PSTAGE_BYTES);
-          tma_load_2d_hint(sa, &tma_a, kb * BK, row_a, &bars->full[stage], pol);
-          mc::tma_load_2d_mcast(sa + PA_BYTES + pr * 64 * BK, &tma_b, kb * BK, row_b, &bars->full[stage], b_mask, pol);
+          if (leader) mbar_expect_tx(&bars->full[stage], 2 * PSTAGE_BYTES);
+          const uint32_t leader_bar = smem_u32(&bars->full[stage]) & PAIR_BIT_MASK;
+          tma_load_2d_pair_local(sa, &tma_a, kb * BK, row_a, leader_bar, pol);
+          tma_load_2d_pair_mcast(sa + PA_BYTES + pr * 64 * BK, &tma_b, kb * BK, row_b, leader_bar, b_mask, pol);
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -530,7 +550,6 @@ gemm_fp8_pairmc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * PBN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!pmc_wait(&bars->full[stage], phase, bars, 4u)) { ok = false; break; }
-          if (!pmc_wait<true>(&bars->peer_full[stage], phase, bars, 4u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * PSTAGE_BYTES);
           const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + PA_BYTES);
@@ -546,28 +565,6 @@ gemm_fp8_pairmc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         tc_commit_pair_mask(&bars->tmem_full[acc], pair_mask);
         if (sched != nullptr) {
           const int32_t v = pmc_ring_read(bars, (uint32_t)local, 16u, 0u);
-          if (v == -2) { ok = false; break; }
-          t = v < 0 ? num_tiles : (int64_t)v;
-        } else {
-          t += num_clusters;
-        }
-      }
-    } else if (lane == 0) {
-      // ---------------- relay (pair partners): my stage has landed -> tell my leader ----------------
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int64_t local = 0;
-      int64_t t = cluster_id;
-      for (; ok && t < num_tiles; ++local) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!pmc_wait(&bars->full[stage], phase, bars, 128u)) { ok = false; break; }
-          mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->peer_full[stage]), my_leader));
-          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
-        }
-        if (!ok) break;
-        if (sched != nullptr) {
-          const int32_t v = pmc_ring_read(bars, (uint32_t)local, 128u, 0u);
           if (v == -2) { ok = false; break; }
           t = v < 0 ? num_tiles : (int64_t)v;
         } else {
