@@ -1,16 +1,22 @@
 // Scaled fp8 GEMM for sm_100a:  out[M,N] = (A[M,K] . B[N,K]^T) / (sa * sb) (+ bias).
 //
-// Both operands are K-major fp8 bytes.  One persistent CTA per SM walks 128x256
-// output tiles.  Warp roles:
-//   warp 0      TMA producer: cp.async.bulk.tensor 128-byte-swizzled boxes of A (128x128 B)
-//               and B (256x128 B) into a 4-stage shared-memory ring, mbarrier complete_tx.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f8f6f4 (M128 N256 K32)
-//               from shared-memory descriptors into one of two 256-column fp32
-//               accumulators in tensor memory; tcgen05.commit releases ring slots and
-//               publishes finished accumulators.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, multiply by 1/(sa*sb), add bias,
-//               convert to the output dtype and store; runs under the next tile's
-//               main loop because the accumulator is double buffered.
+// Three persistent, warp-specialised kernels share the device code of this file:
+//   pair kernel   (namespace pair, default for K < 16384) two CTAs per 256x256 tile,
+//                 tcgen05.mma.cta_group::2, accumulators double buffered in tensor memory;
+//   wide kernel   (namespace wide, default for K >= 16384) one CTA per 256x256 tile, two
+//                 M128 N256 MMAs per k-step, the accumulator fills tensor memory;
+//   one-CTA kernel (below) one CTA per 128x256 tile; kept as the simplest reference of the scheme.
+// Each operand is fp8 bytes, K-major (storage [rows, K]) or MN-major (storage [K, rows]).
+// Tiles are walked in L2-friendly bands, with a fixed stride per CTA or claimed from a counter
+// (dynamic tile scheduling, see TileRing).  Warp roles, in every kernel:
+//   warp 0      TMA producer: cp.async.bulk.tensor 128-byte-swizzled boxes of A and B into a
+//               shared-memory ring, mbarrier complete_tx.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f8f6f4 (K = 32 per instruction)
+//               from shared-memory descriptors into fp32 accumulators in tensor memory;
+//               tcgen05.commit releases ring slots and publishes finished accumulators.
+//   warps 2..   epilogue: tcgen05.ld the accumulator, multiply by 1/(sa*sb), add bias,
+//               convert to the output dtype and store through swizzled staging boxes and
+//               TMA stores (or per-thread stores when the output is not 16-byte aligned).
 // Every mbarrier wait is bounded by a cycle budget; on expiry the kernel raises a flag
 // in a device error word, all roles leave their loops, tensor memory is released and
 // the kernel returns.
