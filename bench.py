@@ -204,11 +204,53 @@ def measure_delayed(torch, f8, _native, dev, x):
     torch.cuda.synchronize()
     cast_ms = s0.elapsed_time(s1) / 20
     return {"sync_rows": 960, "sync_kernel_us": ev[0] / max(ev[1], 1) * 1e3, "sync_launches_per_call": 1,
-            "sync_wall_us_per_call": wall_us,
+            "sync_wall_us_per_call": wall_us, "step": measure_delayed_step(torch, f8, dev),
             "delayed_cast_ms_16384x8192": cast_ms,
             "delayed_cast_gbs": (4.0 if TRANSPOSED_COPIES else 3.0) * x.numel() / (cast_ms * 1e-3) / 1e9,
             "delayed_cast_bytes": ("4 B per element: 2 read + 1 fp8 + 1 transposed fp8, amax from the same read"
                                    if TRANSPOSED_COPIES else "3 B per element: 2 read + 1 fp8, amax from the same read")}
+
+
+def measure_delayed_step(torch, f8, dev, steps: int = 10):
+    """The step of the timed region with delayed scaling for all three tensors (the reference's
+    third configuration): the same four linears, fwd+bwd, plus one
+    sync_float8_amax_and_scale_history over them per step.  Casts are one launch each (the amax
+    comes from the cast's own read), so the dynamic step's twelve amax launches disappear."""
+    from float8_experimental_b200.float8_linear import Float8Linear
+
+    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    cfg = f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d)
+    gen = torch.Generator(device=dev).manual_seed(77)
+    layers, xs, gos = [], [], []
+    for _, k, n in SHAPES:
+        lin = torch.nn.Linear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            lin.weight.normal_(0.0, 0.02, generator=gen)
+        layers.append(Float8Linear.from_float(lin, cfg))
+        xs.append(torch.randn(M_TOKENS, k, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True))
+        gos.append(torch.randn(M_TOKENS, n, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3))
+    model = torch.nn.ModuleList(layers)
+
+    def step():
+        for layer, x, go in zip(layers, xs, gos):
+            x.grad = None
+            layer.weight.grad = None
+            layer(x).backward(go)
+        f8.sync_float8_amax_and_scale_history(model, layers)
+
+    for _ in range(3):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    flops = sum(layer_flops(k, n) for _, k, n in SHAPES)
+    return {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps,
+            "workload": "the four linears with delayed scaling x3, fwd+bwd, one sync per step"}
 
 
 def measure_fused_norm(torch, dev, x):
