@@ -21,7 +21,7 @@ Ops (namespace `f8b200`):
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 

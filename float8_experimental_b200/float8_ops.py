@@ -13,7 +13,6 @@ from typing import Any, Dict, Optional
 import torch
 from torch.utils._pytree import tree_map
 
-from ._ops import ops
 from .float8_python_api import addmm_float8_unwrapped
 from .float8_tensor import choose_scaled_mm_config, Float8Tensor
 

@@ -20,7 +20,6 @@ import torch.distributed as dist
 import torch.distributed._functional_collectives as funcol
 from torch.distributed._tensor import DTensor
 
-from . import _native as N
 from ._ops import ops
 from .float8_utils import _kind, e4m3_dtype
 

@@ -1,7 +1,6 @@
 """Host logic of the fused RMSNorm -> fp8 cast (autograd wiring, composition with
 Float8Linear), on the CPU stand-ins; and the oracle's restatement of the fused arithmetic
 against the unfused composition the reference's benchmark model performs."""
-import numpy as np
 import pytest
 import torch
 

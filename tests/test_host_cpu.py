@@ -300,27 +300,44 @@ def test_mm_config_mismatch_message():
         torch.mm(a, b.t())
 
 
-def test_backward_gemms_use_preemitted_layouts(monkeypatch):
-    calls = []
-    real = FLOAT8_OPS_TABLE  # noqa: F841
-    import float8_experimental_b200.float8_ops as fo
+def test_gemms_read_the_cast_outputs_where_they_lie(monkeypatch):
+    """Forward, dgrad and wgrad hand the GEMM views of the three cast results: no transposed
+    or contiguous copy of an fp8 tensor is made on the way."""
+    import float8_experimental_b200.float8_python_api as api
+    import float8_experimental_b200.float8_tensor as ft
 
-    orig = fo.ops.transpose_fp8
+    cast_ptrs, operand_ptrs = set(), []
 
     class Spy:
-        def __getattr__(self, name):
-            if name == "transpose_fp8":
-                def wrapped(*a, **k):
-                    calls.append(1)
-                    return orig(*a, **k)
-                return wrapped
-            return getattr(torch.ops.f8b200, name)
+        def __init__(self, record):
+            self.record = record
 
-    monkeypatch.setattr(fo, "ops", Spy())
+        def __getattr__(self, name):
+            fn = getattr(torch.ops.f8b200, name)
+
+            def wrapped(*a, **k):
+                out = fn(*a, **k)
+                self.record(name, a, out)
+                return out
+
+            return wrapped
+
+    def on_cast(name, args, out):
+        if name == "cast_from_amax":
+            cast_ptrs.add(out[0].data_ptr())
+
+    def on_mm(name, args, out):
+        if name == "scaled_mm":
+            operand_ptrs.extend([args[0].data_ptr(), args[1].data_ptr()])
+
+    monkeypatch.setattr(ft, "ops", Spy(on_cast))
+    monkeypatch.setattr(api, "ops", Spy(on_mm))
     m = make_linear(torch.randn(48, 32, dtype=torch.bfloat16), f8.Float8LinearConfig())
     x = torch.randn(2, 8, 32, dtype=torch.bfloat16, requires_grad=True)
     m(x).sum().backward()
-    assert calls == [] and x.grad.shape == x.shape and m.weight.grad.shape == (48, 32)
+    assert len(cast_ptrs) == 3 and len(operand_ptrs) == 6
+    assert set(operand_ptrs) == cast_ptrs
+    assert x.grad.shape == x.shape and m.weight.grad.shape == (48, 32)
 
 
 def test_autocast_output_dtype():
