@@ -290,7 +290,34 @@ def measure_fused_norm(torch, dev, x):
     glu_ms = timed(lambda: swiglu_to_float8_dynamic(a, b))
     glu_recompute_ms = timed(lambda: swiglu_to_float8_dynamic(a, b, recompute=True))
     glu_unfused_ms = timed(lambda: hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, cfg))
-    return {"shape": list(x.shape), "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
+    # backward of the two producers (CUDA kernels) against eager autograd of the same formulas
+    from float8_experimental_b200._ops import ops
+
+    rstd, _ = ops.rmsnorm_amax(x, w, 1e-6)
+    gy = torch.randn_like(x)
+    norm_bwd_ms = timed(lambda: ops.rmsnorm_bwd(x, gy, w, rstd))
+
+    def eager_norm_bwd():
+        xr = x.detach().requires_grad_(True)
+        wr = w.detach().requires_grad_(True)
+        xf = xr.float()
+        ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(xr) * wr).backward(gy)
+
+    norm_bwd_eager_ms = timed(eager_norm_bwd)
+    gg = torch.randn(a.shape, device=dev, dtype=x.dtype)
+    glu_bwd_ms = timed(lambda: ops.swiglu_bwd(a, b, gg))
+
+    def eager_glu_bwd():
+        ar, br = a.detach().requires_grad_(True), b.detach().requires_grad_(True)
+        (torch.nn.functional.silu(ar) * br).backward(gg)
+
+    glu_bwd_eager_ms = timed(eager_glu_bwd)
+    backward = {"rmsnorm_bwd_ms": norm_bwd_ms, "rmsnorm_bwd_gbs": 6.0 * x.numel() / (norm_bwd_ms * 1e-3) / 1e9,
+                "rmsnorm_eager_fwd_bwd_ms": norm_bwd_eager_ms,
+                "swiglu_bwd_ms": glu_bwd_ms, "swiglu_bwd_gbs": 10.0 * a.numel() / (glu_bwd_ms * 1e-3) / 1e9,
+                "swiglu_eager_fwd_bwd_ms": glu_bwd_eager_ms}
+    return {"shape": list(x.shape), "backward": backward,
+            "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
             "fused_bytes": "5 B per element: 2 read (1/rms + amax pass) + 2 read + 1 fp8 written (cast pass)",
             "unfused_eager_norm_then_cast_ms": unfused_ms,
             "swiglu": {"shape": list(a.shape), "fused_ms": glu_ms, "fused_gbs": 9.0 * a.numel() / (glu_ms * 1e-3) / 1e9,

@@ -40,6 +40,9 @@ EXPORTS = (
     "f8b200_rmsnorm_cast",
     "f8b200_swiglu_amax",
     "f8b200_swiglu_cast",
+    "f8b200_rmsnorm_bwd_workspace_bytes",
+    "f8b200_rmsnorm_bwd",
+    "f8b200_swiglu_bwd",
     "f8b200_read_device_error",
 )
 
@@ -85,10 +88,14 @@ def load() -> ctypes.CDLL:
     lib.f8b200_rmsnorm_cast.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.f8b200_swiglu_amax.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
     lib.f8b200_swiglu_cast.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i32, vp, vp, i64, vp]
+    lib.f8b200_rmsnorm_bwd_workspace_bytes.argtypes = [i64]
+    lib.f8b200_rmsnorm_bwd_workspace_bytes.restype = i64
+    lib.f8b200_rmsnorm_bwd.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, vp, vp, i64, vp, vp, i64, vp]
+    lib.f8b200_swiglu_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if fn.restype is not ctypes.c_char_p:
+        if fn.restype is not ctypes.c_char_p and fn.restype is not i64:
             fn.restype = i32
     _lib = lib
     return lib
@@ -436,6 +443,31 @@ def cast_scatter(x: torch.Tensor, rows: int, cols: int, ld_x: int, amax: torch.T
             load().f8b200_cast_scatter(x.data_ptr(), hp_code(x.dtype), rows, cols, ld_x, 1, amax.data_ptr(),
                                        scale_out.data_ptr(), 0, fp8_kind, arr, len(out_ptrs), ld_out, _stream(x)),
             "f8b200_cast_scatter",
+        )
+
+
+def rmsnorm_bwd(x: torch.Tensor, g: torch.Tensor, rows: int, cols: int, ld_x: int, ld_g: int, weight: torch.Tensor,
+                rstd: torch.Tensor, dx: torch.Tensor, dweight: torch.Tensor) -> None:
+    _require_cuda(x, g, weight, rstd, dx, dweight)
+    nbytes = int(load().f8b200_rmsnorm_bwd_workspace_bytes(cols))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    with _Launch("norm_bwd", x.device, 2):
+        _check(
+            load().f8b200_rmsnorm_bwd(x.data_ptr(), g.data_ptr(), hp_code(x.dtype), rows, cols, ld_x, ld_g,
+                                      weight.data_ptr(), rstd.data_ptr(), dx.data_ptr(), cols, dweight.data_ptr(),
+                                      ws.data_ptr(), nbytes, _stream(x)),
+            "f8b200_rmsnorm_bwd",
+        )
+
+
+def swiglu_bwd(a: torch.Tensor, b: torch.Tensor, g: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int,
+               ld_g: int, da: torch.Tensor, db: torch.Tensor) -> None:
+    _require_cuda(a, b, g, da, db)
+    with _Launch("glu_bwd", a.device):
+        _check(
+            load().f8b200_swiglu_bwd(a.data_ptr(), b.data_ptr(), g.data_ptr(), hp_code(a.dtype), rows, cols, ld_a,
+                                     ld_b, ld_g, da.data_ptr(), db.data_ptr(), cols, _stream(a)),
+            "f8b200_swiglu_bwd",
         )
 
 

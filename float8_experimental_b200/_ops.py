@@ -49,6 +49,8 @@ _lib.define(
 _lib.define("rmsnorm_amax(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _lib.define("rmsnorm_cast(Tensor x, Tensor weight, Tensor rstd, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 _lib.define("swiglu_amax(Tensor a, Tensor b, bool write_y) -> (Tensor, Tensor)")
+_lib.define("rmsnorm_bwd(Tensor x, Tensor grad_y, Tensor weight, Tensor rstd) -> (Tensor, Tensor)")
+_lib.define("swiglu_bwd(Tensor a, Tensor b, Tensor grad_y) -> (Tensor, Tensor)")
 _lib.define("swiglu_cast(Tensor a, Tensor b, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 
 
@@ -220,6 +222,33 @@ def _swiglu_cast_cuda(a, b, amax, fp8_kind: int):
     return data, scale
 
 
+def fused_bwd_supported(x: torch.Tensor, max_cols: int = 0) -> bool:
+    """Whether the backward kernels of the fused producers cover this tensor (16-bit dtype, last
+    dimension a multiple of 8 and, for RMSNorm, at most 8192)."""
+    cols = x.shape[-1]
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and cols % 8 == 0 and (max_cols == 0 or cols <= max_cols)
+
+
+def _rmsnorm_bwd_cuda(x, grad_y, weight, rstd):
+    xm, rows, cols, ld = _as_matrix(x.contiguous())
+    gm, _, _, ldg = _as_matrix(grad_y.contiguous())
+    dx = torch.empty_like(xm)
+    dw = torch.empty_like(weight)
+    N.rmsnorm_bwd(xm, gm, rows, cols, ld, ldg, weight.contiguous(), rstd, dx, dw)
+    return dx.view(x.shape), dw
+
+
+def _swiglu_bwd_cuda(a, b, grad_y):
+    am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
+    gm, _, _, ldg = _as_matrix(grad_y.contiguous())
+    da = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    db = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    N.swiglu_bwd(am, bm, gm, rows, cols, lda, ldb, ldg, da, db)
+    return da, db
+
+
+_lib.impl("rmsnorm_bwd", _rmsnorm_bwd_cuda, "CUDA")
+_lib.impl("swiglu_bwd", _swiglu_bwd_cuda, "CUDA")
 _lib.impl("swiglu_amax", _swiglu_amax_cuda, "CUDA")
 _lib.impl("swiglu_cast", _swiglu_cast_cuda, "CUDA")
 _lib.impl("rmsnorm_amax", _rmsnorm_amax_cuda, "CUDA")
@@ -238,6 +267,16 @@ _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 # fake (meta) implementations: shapes and dtypes only, so torch.compile can trace
 # around the opaque ops
 # ---------------------------------------------------------------------------
+@torch.library.register_fake("f8b200::rmsnorm_bwd")
+def _rmsnorm_bwd_fake(x, grad_y, weight, rstd):
+    return torch.empty_like(x), torch.empty_like(weight)
+
+
+@torch.library.register_fake("f8b200::swiglu_bwd")
+def _swiglu_bwd_fake(a, b, grad_y):
+    return torch.empty_like(a), torch.empty_like(a)
+
+
 @torch.library.register_fake("f8b200::swiglu_amax")
 def _swiglu_amax_fake(a, b, write_y):
     return a.new_empty((), dtype=torch.float32), a.new_empty(a.shape if write_y else (0,))

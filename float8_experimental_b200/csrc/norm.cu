@@ -667,3 +667,225 @@ extern "C" int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, in
 #undef F8_GLU_GEN
   return check_launch();
 }
+
+// ===========================================================================
+// Backward of the two fused producers (the casts are transparent to autograd, so these are the
+// plain RMSNorm and SwiGLU backward formulas), one pass over the saved inputs each.
+//
+// RMSNorm:  n = x * rstd,  dn = RN_T(g * w),  c = mean(dn * n) over the row,
+//           dx = RN_T(rstd * (dn - n * c)),   dw[col] = sum over rows of g * RN_T(n)
+//           (the gradient of `output * weight` and of `_norm` in
+//           float8_experimental/benchmarks/profile_linear_float8.py:69-74).  Reads x and g, writes
+//           dx: 6 bytes per element; dw is accumulated per CTA in registers and written as
+//           per-CTA partial sums that a second small kernel adds up.
+// SwiGLU:   s = a * sig(a),  ds = RN_T(g * b),  da = RN_T(ds * sig * (1 + a * (1 - sig))),
+//           db = RN_T(g * RN_T(s)).  Reads a, b, g, writes da, db: 10 bytes per element.
+// ===========================================================================
+namespace f8b200 {
+namespace {
+
+template <int HP, int CH>
+__global__ void __launch_bounds__(kNormThreads, 2)
+rmsnorm_bwd_kernel(const char* __restrict__ x, int64_t ldx_bytes, const char* __restrict__ g, int64_t ldg_bytes,
+                   int64_t rows, int64_t cols, const char* __restrict__ weight, const float* __restrict__ rstd_in,
+                   char* __restrict__ dx, int64_t lddx_bytes, float* __restrict__ dw_partial) {
+  __shared__ float red[kNormThreads / 32];
+  const int chunks = (int)(cols / 8);
+  uint4 wq[CH];
+  float dw[CH][8];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    wq[i] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(weight) + c) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.0f;
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* xrow = reinterpret_cast<const uint4*>(x + r * ldx_bytes);
+    const uint4* grow = reinterpret_cast<const uint4*>(g + r * ldg_bytes);
+    const float rstd = __ldg(rstd_in + r);
+    // the row of x and of g stays packed in registers; n and dn are recomputed in the second sweep
+    uint4 qx[CH], qg[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      qx[i] = c < chunks ? __ldcs(xrow + c) : make_uint4(0u, 0u, 0u, 0u);
+      qg[i] = c < chunks ? __ldcs(grow + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      float xv[8], gv[8], wv[8];
+      widen8<HP>(qx[i], xv);
+      widen8<HP>(qg[i], gv);
+      widen8<HP>(wq[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = xv[j] * rstd;
+        dot = fmaf(round_hp<HP>(gv[j] * wv[j]), n, dot);
+        dw[i][j] = fmaf(gv[j], round_hp<HP>(n), dw[i][j]);
+      }
+    }
+    const float cmean = block_sum_fixed(dot, red) / (float)cols;
+    uint4* orow = reinterpret_cast<uint4*>(dx + r * lddx_bytes);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      if (c < chunks) {
+        float xv[8], gv[8], wv[8], o[8];
+        widen8<HP>(qx[i], xv);
+        widen8<HP>(qg[i], gv);
+        widen8<HP>(wq[i], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (round_hp<HP>(gv[j] * wv[j]) - xv[j] * rstd * cmean);
+        orow[c] = make_uint4(pack_round2<HP>(o[0], o[1]), pack_round2<HP>(o[2], o[3]), pack_round2<HP>(o[4], o[5]),
+                             pack_round2<HP>(o[6], o[7]));
+      }
+    }
+  }
+  float* mine = dw_partial + (int64_t)blockIdx.x * cols;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < chunks) {
+      reinterpret_cast<float4*>(mine + (int64_t)c * 8)[0] = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
+      reinterpret_cast<float4*>(mine + (int64_t)c * 8)[1] = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+    }
+  }
+}
+
+// dw[col] = sum of the per-CTA partial sums, rounded to T.  One CTA per 32 columns; its eight
+// warps take every eighth partial row, shared memory adds the eight sums.
+template <int HP>
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int parts, int64_t cols, char* __restrict__ dw_out) {
+  __shared__ float acc[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+  float s = 0.0f;
+  if (c < cols)
+    for (int p = ty; p < parts; p += 8) s += partial[(int64_t)p * cols + c];
+  acc[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += acc[k][tx];
+    store_hp<HP>(dw_out, c, t);
+  }
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_bwd_kernel(const char* __restrict__ a, const char* __restrict__ b, const char* __restrict__ g, int64_t lda_bytes,
+                  int64_t ldb_bytes, int64_t ldg_bytes, int64_t rows, int64_t chunks_per_row, char* __restrict__ da,
+                  char* __restrict__ db, int64_t ldo_bytes) {
+  const int64_t total = rows * chunks_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+    float av[8], bv[8], gv[8], dav[8], dbv[8];
+    widen8<HP>(__ldcs(reinterpret_cast<const uint4*>(a + r * lda_bytes) + c), av);
+    widen8<HP>(__ldcs(reinterpret_cast<const uint4*>(b + r * ldb_bytes) + c), bv);
+    widen8<HP>(__ldcs(reinterpret_cast<const uint4*>(g + r * ldg_bytes) + c), gv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-av[j])));
+      const float ds = round_hp<HP>(gv[j] * bv[j]);
+      dav[j] = ds * (sig * (1.0f + av[j] * (1.0f - sig)));
+      dbv[j] = gv[j] * round_hp<HP>(silu_f32(av[j]));
+    }
+    uint4 oa, ob;
+    oa.x = pack_round2<HP>(dav[0], dav[1]); oa.y = pack_round2<HP>(dav[2], dav[3]);
+    oa.z = pack_round2<HP>(dav[4], dav[5]); oa.w = pack_round2<HP>(dav[6], dav[7]);
+    ob.x = pack_round2<HP>(dbv[0], dbv[1]); ob.y = pack_round2<HP>(dbv[2], dbv[3]);
+    ob.z = pack_round2<HP>(dbv[4], dbv[5]); ob.w = pack_round2<HP>(dbv[6], dbv[7]);
+    reinterpret_cast<uint4*>(da + r * ldo_bytes)[c] = oa;
+    reinterpret_cast<uint4*>(db + r * ldo_bytes)[c] = ob;
+  }
+}
+
+}  // namespace
+}  // namespace f8b200
+
+// 16-bit dtypes, cols a multiple of 8 and at most 8192, 16-byte aligned rows: anything else returns
+// F8B200_ERR_UNSUPPORTED and the caller uses framework ops.  `workspace` holds the per-CTA partial
+// sums of dw: f8b200_rmsnorm_bwd_workspace_bytes(cols) bytes of device memory, fp32.
+static int norm_bwd_grid(int64_t rows) {
+  const int64_t cap = (int64_t)sm_count() * 2;  // two CTAs of the backward kernel fit an SM
+  return (int)(rows < cap ? rows : cap);
+}
+
+extern "C" int64_t f8b200_rmsnorm_bwd_workspace_bytes(int64_t cols) {
+  return (int64_t)sm_count() * 2 * cols * (int64_t)sizeof(float);
+}
+
+extern "C" int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtype, int64_t rows, int64_t cols,
+                                  int64_t ld_x, int64_t ld_g, const void* weight, const float* rstd, void* dx,
+                                  int64_t ld_dx, void* dweight, void* workspace, int64_t workspace_bytes,
+                                  void* stream) {
+  if (x == nullptr || grad_y == nullptr || weight == nullptr || rstd == nullptr || dx == nullptr ||
+      dweight == nullptr || workspace == nullptr)
+    return F8B200_ERR_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ld_x < cols || ld_g < cols || ld_dx < cols) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype != F8B200_BF16 && hp_dtype != F8B200_FP16) return F8B200_ERR_UNSUPPORTED;
+  auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (cols % 8 != 0 || cols > 8192 || ld_x % 8 != 0 || ld_g % 8 != 0 || ld_dx % 8 != 0 || !al16(x) || !al16(grad_y) ||
+      !al16(weight) || !al16(dx) || !al16(workspace))
+    return F8B200_ERR_UNSUPPORTED;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  const int grid = norm_bwd_grid(rows);
+  if (workspace_bytes < (int64_t)grid * cols * (int64_t)sizeof(float)) return F8B200_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* xp = static_cast<const char*>(x);
+  const char* gp = static_cast<const char*>(grad_y);
+  const char* wp = static_cast<const char*>(weight);
+  char* dxp = static_cast<char*>(dx);
+  float* part = static_cast<float*>(workspace);
+#define F8_RMS_BWD(HP, CH)                                                                                        \
+  rmsnorm_bwd_kernel<HP, CH><<<grid, kNormThreads, 0, st>>>(xp, ld_x * 2, gp, ld_g * 2, rows, cols, wp, rstd, dxp, \
+                                                            ld_dx * 2, part)
+#define F8_RMS_BWD_CH(HP)                    \
+  do {                                       \
+    if (cols <= 2048) F8_RMS_BWD(HP, 1);     \
+    else if (cols <= 4096) F8_RMS_BWD(HP, 2); \
+    else F8_RMS_BWD(HP, 4);                  \
+  } while (0)
+  if (hp_dtype == F8B200_BF16) F8_RMS_BWD_CH(F8B200_BF16); else F8_RMS_BWD_CH(F8B200_FP16);
+#undef F8_RMS_BWD_CH
+#undef F8_RMS_BWD
+  rc = check_launch();
+  if (rc != F8B200_OK) return rc;
+  const unsigned blocks = (unsigned)((cols + 31) / 32);
+  if (hp_dtype == F8B200_BF16)
+    rmsnorm_dw_reduce_kernel<F8B200_BF16><<<blocks, 256, 0, st>>>(part, grid, cols, static_cast<char*>(dweight));
+  else
+    rmsnorm_dw_reduce_kernel<F8B200_FP16><<<blocks, 256, 0, st>>>(part, grid, cols, static_cast<char*>(dweight));
+  return check_launch();
+}
+
+extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
+                                 int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
+                                 int64_t ld_out, void* stream) {
+  if (a == nullptr || b == nullptr || grad_y == nullptr || da == nullptr || db == nullptr) return F8B200_ERR_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols || ld_g < cols || ld_out < cols) return F8B200_ERR_BAD_ARG;
+  if (hp_dtype != F8B200_BF16 && hp_dtype != F8B200_FP16) return F8B200_ERR_UNSUPPORTED;
+  auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (cols % 8 != 0 || ld_a % 8 != 0 || ld_b % 8 != 0 || ld_g % 8 != 0 || ld_out % 8 != 0 || !al16(a) || !al16(b) ||
+      !al16(grad_y) || !al16(da) || !al16(db))
+    return F8B200_ERR_UNSUPPORTED;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t cpr = cols / 8;
+  const int grid = glu_grid(rows * cpr);
+  if (hp_dtype == F8B200_BF16)
+    swiglu_bwd_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(
+        static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a * 2, ld_b * 2,
+        ld_g * 2, rows, cpr, static_cast<char*>(da), static_cast<char*>(db), ld_out * 2);
+  else
+    swiglu_bwd_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(
+        static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a * 2, ld_b * 2,
+        ld_g * 2, rows, cpr, static_cast<char*>(da), static_cast<char*>(db), ld_out * 2);
+  return check_launch();
+}

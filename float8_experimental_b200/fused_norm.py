@@ -21,7 +21,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from ._ops import ops
+from ._ops import fused_bwd_supported, ops
 from .float8_tensor import Float8Tensor, GemmInputRole, LinearMMConfig
 from .float8_utils import _kind, e4m3_dtype
 
@@ -45,6 +45,9 @@ class _RMSNormToFloat8(torch.autograd.Function):
         # the cast is transparent to autograd (float8_experimental/float8_tensor.py:193-195); what is
         # left is the RMSNorm backward, in fp32 from the saved x and 1/rms
         x, weight, rstd = ctx.saved_tensors
+        if fused_bwd_supported(x, 8192) and g.dtype == x.dtype:
+            dx, dw = ops.rmsnorm_bwd(x, g, weight, rstd)
+            return dx, dw, None, None, None, None, None
         cols = x.shape[-1]
         g32 = g.reshape(-1, cols).float()
         n = x.reshape(-1, cols).float() * rstd[:, None]
@@ -109,6 +112,9 @@ class _SwiGLUToFloat8(torch.autograd.Function):
     def backward(ctx, g):
         # y = silu(a) * b:  dy/db = silu(a),  dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))
         a, b = ctx.saved_tensors
+        if fused_bwd_supported(a) and g.dtype == a.dtype:
+            da, db = ops.swiglu_bwd(a, b, g)
+            return da, db, None, None, None, None, None
         a32, g32 = a.float(), g.reshape(a.shape).float()
         sig = torch.sigmoid(a32)
         silu = a32 * sig

@@ -290,6 +290,32 @@ int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows,
                        float* scale_out, void* out, int64_t ld_out, void* stream);
 
 /*
+ * Backward of the two fused producers (the casts are transparent to autograd:
+ * float8_experimental/float8_tensor.py:193-195), one pass over the saved inputs each; the
+ * formulas are the gradients of float8_experimental/benchmarks/profile_linear_float8.py:69-74
+ * and :117-118 as eager autograd evaluates them for 16-bit tensors.
+ *
+ * f8b200_rmsnorm_bwd  dx = RN_T(rstd * (dn - n * mean(dn * n))) with n = x * rstd, dn = RN_T(g * w);
+ *                     dweight[col] = RN_T(sum over rows of g * RN_T(n)).  Reads x and grad_y, writes
+ *                     dx (6 bytes per element).  `workspace`: at least
+ *                     f8b200_rmsnorm_bwd_workspace_bytes(cols) bytes of device memory for per-CTA
+ *                     partial sums (contents need no initialisation).
+ * f8b200_swiglu_bwd   da = RN_T(RN_T(g * b) * sig(a) * (1 + a * (1 - sig(a)))), db = RN_T(g * RN_T(silu(a))).
+ *                     Reads a, b, grad_y, writes da, db with row pitch ld_out (10 bytes per element).
+ *
+ * Both cover 16-bit dtypes, cols a multiple of 8 (RMSNorm: at most 8192) and 16-byte aligned rows;
+ * anything else returns F8B200_ERR_UNSUPPORTED and the caller falls back to framework ops.
+ */
+int64_t f8b200_rmsnorm_bwd_workspace_bytes(int64_t cols);
+int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtype, int64_t rows, int64_t cols,
+                       int64_t ld_x, int64_t ld_g, const void* weight, const float* rstd, void* dx,
+                       int64_t ld_dx, void* dweight, void* workspace, int64_t workspace_bytes,
+                       void* stream);
+int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
+                      int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
+                      int64_t ld_out, void* stream);
+
+/*
  * Reads and clears the device error word of the current device (synchronises the
  * device).  *flags_out != 0 means a bounded wait inside a kernel gave up since the
  * last read; the result of that launch is undefined.  Test and debugging aid.
