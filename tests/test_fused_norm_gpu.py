@@ -161,3 +161,47 @@ def test_fused_swiglu_backward_kernel_matches_eager_autograd(dtype, shape):
         assert got.dtype == dtype
         assert _sqnr(ref, got) > (50 if dtype == torch.bfloat16 else 65)
     assert (b.grad != b2.grad).float().mean().item() <= 1e-3
+
+
+def test_ffn_fragment_with_fused_producers_matches_unfused_float8_model():
+    """RMSNorm -> w1|w3 -> SwiGLU -> w2 (the FFN of the reference's benchmark model,
+    float8_experimental/benchmarks/profile_linear_float8.py:52-149) with both producers fused
+    into the casts of the linears that follow them, forward and backward, against the same
+    float8 linears fed by eager RMSNorm and silu * mul."""
+    import copy
+
+    import torch.nn as nn
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.float8_linear import Float8Linear
+
+    torch.manual_seed(3)
+    dim, hidden, tokens = 1024, 2816, 512
+    w13 = Float8Linear.from_float(nn.Linear(dim, 2 * hidden, bias=False, device="cuda", dtype=torch.bfloat16),
+                                  f8.Float8LinearConfig())
+    w2 = Float8Linear.from_float(nn.Linear(hidden, dim, bias=False, device="cuda", dtype=torch.bfloat16),
+                                 f8.Float8LinearConfig())
+    norm_w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    x = torch.randn(tokens, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(tokens, dim, device="cuda", dtype=torch.bfloat16) * 1e-2
+
+    def fused(xi, nw, l13, l2):
+        h = l13(rms_norm_to_float8_dynamic(xi, nw, 1e-6, linear_mm_config=l13.linear_mm_config))
+        return xi + l2(swiglu_to_float8_dynamic(h[:, :hidden], h[:, hidden:], linear_mm_config=l2.linear_mm_config))
+
+    def unfused(xi, nw, l13, l2):
+        h = l13(reference_rmsnorm(xi, nw, 1e-6))
+        return xi + l2(torch.nn.functional.silu(h[:, :hidden]) * h[:, hidden:])
+
+    y = fused(x, norm_w, w13, w2)
+    y.backward(go)
+    got = [y.detach(), x.grad, norm_w.grad, w13.weight.grad, w2.weight.grad]
+    x2, nw2 = x.detach().clone().requires_grad_(True), norm_w.detach().clone().requires_grad_(True)
+    l13b, l2b = copy.deepcopy(w13), copy.deepcopy(w2)
+    l13b.weight.grad = None
+    l2b.weight.grad = None
+    y2 = unfused(x2, nw2, l13b, l2b)
+    y2.backward(go)
+    want = [y2.detach(), x2.grad, nw2.grad, l13b.weight.grad, l2b.weight.grad]
+    for name, a, b in zip(("y", "dx", "dnorm_w", "dw13", "dw2"), got, want):
+        assert _sqnr(b, a) > 40, name
