@@ -327,6 +327,52 @@ def measure_fused_norm(torch, dev, x):
                        "unfused_eager_silu_mul_then_cast_ms": glu_unfused_ms}}
 
 
+def measure_ffn_fragment(torch, f8, dev):
+    """RMSNorm -> w1|w3 -> SwiGLU -> w2 with a residual, forward + backward, at the LLaMa-2-70B FFN
+    size (16384 tokens, 8192 -> 2 x 28672 -> 8192; the fragment of the reference's benchmark model):
+    the two producers fused into the casts of the float8 linears that follow them, against the
+    same float8 linears fed by eager RMSNorm and silu * mul."""
+    from float8_experimental_b200.float8_linear import Float8Linear
+    from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic, swiglu_to_float8_dynamic
+
+    dim, hidden = 8192, 28672
+    gen = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda i, o: Float8Linear.from_float(  # noqa: E731
+        torch.nn.Linear(i, o, bias=False, device=dev, dtype=torch.bfloat16), f8.Float8LinearConfig())
+    w13, w2 = mk(dim, 2 * hidden), mk(hidden, dim)
+    nw = torch.ones(dim, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    x = torch.randn(M_TOKENS, dim, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True)
+    go = torch.randn(M_TOKENS, dim, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3)
+
+    def fused():
+        h = w13(rms_norm_to_float8_dynamic(x, nw, 1e-6, linear_mm_config=w13.linear_mm_config))
+        y = x + w2(swiglu_to_float8_dynamic(h[:, :hidden], h[:, hidden:], linear_mm_config=w2.linear_mm_config))
+        y.backward(go)
+
+    def unfused():
+        xf = x.float()
+        n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(x) * nw
+        h = w13(n)
+        y = x + w2(torch.nn.functional.silu(h[:, :hidden]) * h[:, hidden:])
+        y.backward(go)
+
+    out = {"shape": {"tokens": M_TOKENS, "dim": dim, "hidden": hidden}}
+    for name, fn in (("fused_ms", fused), ("unfused_ms", unfused)):
+        for _ in range(2):
+            x.grad = nw.grad = w13.weight.grad = w2.weight.grad = None
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            x.grad = nw.grad = w13.weight.grad = w2.weight.grad = None
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / 5
+    return out
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -495,6 +541,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     fused_norm = None
     if rank == 0 and world == 1 and shapes[0][1] == 8192:
         fused_norm = measure_fused_norm(torch, dev, xs[0].detach())
+        if args.layers is None:
+            fused_norm["ffn_fragment"] = measure_ffn_fragment(torch, f8, dev)
 
     # ---- library kernel to beat, outside every timed region -----------------
     cublaslt = None
