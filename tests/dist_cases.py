@@ -205,9 +205,9 @@ class _FFN(nn.Module):
 
 
 class _Toy(nn.Module):
-    def __init__(self):
+    def __init__(self, dim=16, hidden=32):
         super().__init__()
-        self.ffn = _FFN()
+        self.ffn = _FFN(dim, hidden)
 
     def forward(self, x):
         return self.ffn(x)
@@ -286,6 +286,65 @@ def case_tensor_parallel(rank, world, port, sequence_parallel):
     w1g = tp.ffn.w1.weight.grad
     w1g = w1g.full_tensor() if isinstance(w1g, DTensor) else w1g
     torch.testing.assert_close(w1g, ref.ffn.w1.weight.grad, **tol)
+    dist.destroy_process_group()
+
+
+def case_tensor_parallel_ffn_timing(rank, world, port):
+    """Sequence-parallel float8 FFN at the size of the reference's tensor-parallel configuration
+    (8192 -> 2 x 28672 -> 8192, 2 x 8192 tokens sequence-sharded): forward + backward time per
+    step, printed by rank 0.  GPU only."""
+    _init(rank, world, port)
+    from torch.distributed._tensor import Replicate, Shard
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor.parallel import parallelize_module
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.float8_tensor_parallel import (
+        Float8ColwiseParallel,
+        Float8RowwiseParallel,
+        PrepareFloat8ModuleInput,
+    )
+
+    dim, hidden, batch, seq = 8192, 28672, 2, 8192
+    mesh = init_device_mesh(DEVICE, (world,))
+    torch.manual_seed(5)
+    model = _Toy(dim, hidden).to(torch.bfloat16)
+    f8.convert_to_float8_training(model, config=f8.Float8LinearConfig())
+    plan = {
+        "ffn": PrepareFloat8ModuleInput(input_layouts=Shard(1), desired_input_layouts=Replicate()),
+        "ffn.w1": Float8ColwiseParallel(),
+        "ffn.w2": Float8RowwiseParallel(output_layouts=Shard(1)),
+        "ffn.w3": Float8ColwiseParallel(),
+    }
+    model = parallelize_module(model, mesh, plan)
+    x = torch.randn(batch, seq // world, dim, dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(batch, seq // world, dim, dtype=torch.bfloat16) * 1e-3
+
+    def step():
+        x.grad = None
+        for p in model.parameters():
+            p.grad = None
+        y = model(x)
+        y = y.to_local() if hasattr(y, "to_local") else y
+        y.backward(go)
+
+    for _ in range(3):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(5):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / 5], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        flops = 3 * 6.0 * batch * seq * dim * hidden
+        print(f"TP_FFN_TIMING world={world} tokens={batch * seq} ffn {dim}->2x{hidden}->{dim}: "
+              f"{ms.item():.2f} ms/step, {flops / ms.item() / 1e9:.0f} TFLOP/s over {world} GPUs", flush=True)
+    dist.barrier()
     dist.destroy_process_group()
 
 

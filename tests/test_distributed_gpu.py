@@ -55,3 +55,8 @@ def test_tensor_parallel_matches_unsharded(sequence_parallel):
 
 def test_cast_all_gather_over_peer_memory():
     _run("case_cast_all_gather_over_peer_memory")
+
+
+def test_tensor_parallel_ffn_timing_at_full_size():
+    """Not a parity case: runs the sequence-parallel FFN at full size and prints its step time."""
+    _run("case_tensor_parallel_ffn_timing")
