@@ -44,6 +44,7 @@ EXPORTS = (
     "f8b200_rmsnorm_bwd",
     "f8b200_swiglu_bwd",
     "f8b200_read_device_error",
+    "f8b200_check_device_error",
 )
 
 
@@ -93,6 +94,7 @@ def load() -> ctypes.CDLL:
     lib.f8b200_rmsnorm_bwd.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, vp, vp, i64, vp, vp, i64, vp]
     lib.f8b200_swiglu_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+    lib.f8b200_check_device_error.argtypes = []
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is not ctypes.c_char_p and fn.restype is not i64:
@@ -292,17 +294,35 @@ def load_mc():
     return _mc_lib
 
 
+def _single_gpu_job() -> bool:
+    """True only when this process can be sure it belongs to a job that uses ONE GPU: exactly one
+    CUDA device is visible, no launcher announced more than one rank (WORLD_SIZE /
+    LOCAL_WORLD_SIZE, which are set before `init_process_group` runs), and no process group with
+    more than one rank exists.  The multicast GEMM may run in such jobs only: its TMA loads must
+    never be handed memory of another GPU."""
+    if torch.cuda.device_count() != 1:
+        return False
+    for var in ("WORLD_SIZE", "LOCAL_WORLD_SIZE"):
+        try:
+            if int(os.environ.get(var, "1")) > 1:
+                return False
+        except ValueError:
+            return False
+    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+        return False
+    return True
+
+
 def _mc_cluster(m: int, n: int, k: int):
     """Cluster shape (tiles along M, along N) of the multicast GEMM for this product, or None
-    to use the kernels of libf8b200.so.  Only single-process runs use it, and by default only
-    where it measured faster: K >= 16384 (the products that otherwise run on the wide kernel),
-    2 x 1 clusters (+1 to +4 % sustained; 2 x 2 clusters measured slower than 2 x 1).
+    to use the kernels of libf8b200.so.  Only jobs on a single GPU use it (`_single_gpu_job`; the
+    C entry point checks on its side that every pointer is the current device's own memory), and
+    by default only where it measured faster: K >= 16384 (the products that otherwise run on the
+    wide kernel), 2 x 1 clusters (+1 to +4 % sustained; 2 x 2 clusters measured slower than 2 x 1).
     F8B200_GEMM_MC=0 switches it off, =21 / =22 force a shape for every product; forcing a
     kernel with F8B200_GEMM_MODE switches it off as well."""
     mode = os.environ.get("F8B200_GEMM_MC", "auto")
-    if mode == "0" or load_mc() is None:
-        return None
-    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+    if mode == "0" or not _single_gpu_job() or load_mc() is None:
         return None
     if mode == "21":
         return (2, 1)
@@ -311,7 +331,7 @@ def _mc_cluster(m: int, n: int, k: int):
     if mode == "41":  # two CTA pairs sharing B; K-major operands only (others fall back)
         return (4, 1)
     forced = os.environ.get("F8B200_GEMM_MODE", "")
-    if forced[:1] in ("1", "2", "w"):
+    if forced[:1] in ("1", "2", "w", "p"):
         return None
     return (2, 1) if k >= int(os.environ.get("F8B200_GEMM_WIDE_K", "16384")) else None
 
@@ -469,6 +489,22 @@ def swiglu_bwd(a: torch.Tensor, b: torch.Tensor, g: torch.Tensor, rows: int, col
                                      ld_b, ld_g, da.data_ptr(), db.data_ptr(), cols, _stream(a)),
             "f8b200_swiglu_bwd",
         )
+
+
+def check_device_error() -> None:
+    """Raises F8B200Error (F8B200_ERR_TIMEOUT) when a bounded wait inside a GEMM kernel gave up
+    since the last poll: the outputs of those launches are undefined.  Synchronises the device, so
+    call it where the program synchronises anyway (the end of a step, a benchmark's timed region).
+    With F8B200_POLL_ERRORS=1 in the environment `sync_float8_amax_and_scale_history` and
+    `precompute_float8_dynamic_scale_for_fsdp` poll it once per call."""
+    flags = read_device_error()
+    if flags != 0:
+        raise F8B200Error(f"device error word {flags:#x}: " + load().f8b200_status_string(-7).decode())
+
+
+def poll_errors_if_enabled() -> None:
+    if os.environ.get("F8B200_POLL_ERRORS", "0") == "1" and torch.cuda.is_available():
+        check_device_error()
 
 
 def read_device_error() -> int:

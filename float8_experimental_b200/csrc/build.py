@@ -39,12 +39,12 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def _compile(sources, out_path, verbose):
+def _compile(sources, out_path, verbose, extra=()):
     cmd = [
         _nvcc(),
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-O3", "-std=c++17", "-lineinfo",
-        "-Xcompiler", "-fPIC", "-shared",
+        "-Xcompiler", "-fPIC", "-shared", *extra,
         "-o", out_path,
     ]
     if verbose:
@@ -67,7 +67,9 @@ def build_mc(force: bool = False, verbose: bool = False):
     if not force and os.path.exists(MC_LIB_PATH) and all(os.path.getmtime(d) <= os.path.getmtime(MC_LIB_PATH) for d in deps):
         return MC_LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
-    _compile(MC_SOURCES, MC_LIB_PATH, verbose)
+    # hidden visibility: only the f8b200_mc_* entry points leave this library, so the copy of gemm.cu
+    # it includes cannot interpose the symbols of libf8b200.so
+    _compile(MC_SOURCES, MC_LIB_PATH, verbose, extra=("-Xcompiler", "-fvisibility=hidden"))
     return MC_LIB_PATH
 
 
@@ -77,21 +79,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [
-        _nvcc(),
-        "-gencode", "arch=compute_100a,code=sm_100a",
-        "-O3", "-std=c++17", "-lineinfo",
-        "-Xcompiler", "-fPIC", "-shared",
-        "-o", LIB_PATH,
-    ]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(HERE, s) for s in SOURCES]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libf8b200.so")
+    _compile(SOURCES, LIB_PATH, verbose)
     return LIB_PATH
 
 

@@ -19,8 +19,8 @@ struct DeviceInfo {
   int major = -1;
   int sms = 0;
 };
-constexpr int kMaxDevices = 64;
 DeviceInfo g_info[kMaxDevices];
+std::mutex g_per_device_mutex;
 std::mutex g_info_mutex;
 
 const DeviceInfo* current_info() {
@@ -38,6 +38,14 @@ const DeviceInfo* current_info() {
   return &d;
 }
 }  // namespace
+
+int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+void per_device_lock() { g_per_device_mutex.lock(); }
+void per_device_unlock() { g_per_device_mutex.unlock(); }
 
 int sm_count() {
   const DeviceInfo* d = current_info();

@@ -19,6 +19,38 @@ constexpr float kEps = 1e-12f;  // float8_experimental/float8_utils.py:19
 // Remembers the last CUDA error text for f8b200_last_cuda_error().
 int record_cuda_error(cudaError_t e);
 int sm_count();  // SM count of the current device
+
+// One-time set-up that has to run once on EVERY device of the process (function attributes such as
+// the dynamic shared-memory opt-in are per device).  run() calls `fn` the first time the current
+// device asks and remembers only a success: a failed attempt is tried again by the next call.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  unsigned char done[kMaxDevices] = {};
+  int value[kMaxDevices] = {};  // a number the set-up computed for the device (e.g. an occupancy)
+  template <typename Fn>
+  cudaError_t run(Fn&& fn, int* value_out = nullptr);
+};
+int current_device_slot();                 // index of the current device, -1 when unknown / beyond kMaxDevices
+void per_device_lock();
+void per_device_unlock();
+template <typename Fn>
+cudaError_t PerDeviceOnce::run(Fn&& fn, int* value_out) {
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  per_device_lock();
+  cudaError_t e = cudaSuccess;
+  if (!done[dev]) {
+    int v = 0;
+    e = fn(&v);
+    if (e == cudaSuccess) {
+      value[dev] = v;
+      done[dev] = 1;
+    }
+  }
+  if (value_out != nullptr) *value_out = value[dev];
+  per_device_unlock();
+  return e;
+}
 inline int check_launch() { return record_cuda_error(cudaGetLastError()); }
 
 __host__ __device__ inline float fp8_max_of(int kind) { return kind == F8B200_E4M3 ? kE4M3Max : kE5M2Max; }

@@ -1020,8 +1020,8 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind, i
 }
 
 // Bounded wait that also raises the partner's abort flag when it gives up.
-template <bool CLUSTER_ACQUIRE = false>
-__device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBarriers* bars, uint32_t peer_rank,
+template <bool CLUSTER_ACQUIRE = false, typename Bars = PairBarriers>
+__device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, Bars* bars, uint32_t peer_rank,
                                           uint32_t who, uint32_t backoff_ns = 0) {
   auto probe = [&]() { return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity); };
   if (probe()) return true;
@@ -1041,7 +1041,8 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBa
 }
 
 // Entry `j` of this CTA's tile ring (the (j+1)-th tile of the pair): -1 = no more tiles, -2 = gave up.
-__device__ __forceinline__ int32_t pair_ring_read(PairBarriers* bars, uint32_t j, uint32_t peer_rank, uint32_t who,
+template <typename Bars>
+__device__ __forceinline__ int32_t pair_ring_read(Bars* bars, uint32_t j, uint32_t peer_rank, uint32_t who,
                                                   uint32_t backoff_ns) {
   const uint32_t slot = j & (RING - 1);
   if (!pair_wait<true>(&bars->ring.full[slot], (j >> 4) & 1u, bars, peer_rank, who, backoff_ns)) return -2;
@@ -1249,6 +1250,280 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 
 }  // namespace pair
 
+
+// ===========================================================================
+// Two-CTA variant with a 256x256 accumulator per CTA: a cluster of two CTAs works on one 512x256
+// output tile.  CTA r stages rows [256r, 256r+256) of the A tile and rows [128r, 128r+128) of the B
+// tile, and every k-step issues TWO tcgen05.mma.cta_group::2 (M256 N256 K32): MMA h multiplies
+// the h-th 128-row block of both CTAs' A stages with the pair's B and accumulates into tensor-memory
+// columns [256h, 256h+256) of both CTAs.  Per k-block a CTA pulls 48 KB through L2 for 256x256 of
+// output where the kernels above pull 64 KB (32 KB for 128x256), i.e. 25 % fewer operand bytes
+// per flop, and 4 stages of 48 KB buffer as many k-steps of tensor work as 6 stages did there.
+// The price: the accumulators fill all 512 tensor-memory columns, so they cannot be double buffered.
+// The epilogue is instead overlapped by halves: all eight epilogue warps drain columns 0..255 first
+// and release them (tmem_empty[0]), then columns 256..511 (tmem_empty[1]); the MMA thread starts the
+// next tile's h = 0 MMAs for the first k-blocks (as many as there are stages) as soon as the first
+// half is free, catches up with h = 1 on the same stages when the second half is free, and only then
+// releases those stages.  Accumulation order per output element is unchanged (k ascending), so the
+// result is bit-identical to the other kernels.
+//   full[s]        lives in the leader; both CTAs' TMA loads complete_tx on it (96 KB per stage)
+//   empty[s]       one per CTA; released by a multicast tcgen05.commit from the leader
+//   tmem_full      one per CTA; same multicast commit when a tile's MMAs are done
+//   tmem_empty[h]  live in the leader; 16 arrivals each (8 epilogue warps of each CTA)
+// No TMA load here uses cluster multicast.
+// ===========================================================================
+namespace pairwide {
+
+using namespace pair;
+
+constexpr int QBM = 512;  // rows of the pair tile (256 per CTA)
+constexpr int QBN = 256;  // columns of the pair tile (each CTA stages 128 of B's rows)
+constexpr int QSTAGES = 4;
+constexpr int QA_BYTES = 256 * BK;  // rows 0..127 then 128..255 of this CTA's half of the A tile
+constexpr int QB_BYTES = 128 * BK;
+constexpr int QSTAGE_BYTES = QA_BYTES + QB_BYTES;
+constexpr int QTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int SPLIT_DRAIN_BIT = 26;  // bit of the packed `raster` word: overlap the epilogue by halves
+
+struct __align__(8) QBarriers {
+  uint64_t full[QSTAGES];
+  uint64_t empty[QSTAGES];
+  uint64_t tmem_full;
+  uint64_t tmem_empty[2];
+  TileRing ring;  // written in both CTAs by the leader's producer thread
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+constexpr int QSMEM_BYTES = QSTAGES * QSTAGE_BYTES + 8 * EPI_BOX_BYTES + 1024 + (int)sizeof(QBarriers);
+
+template <typename OutT>
+__global__ void __launch_bounds__(QTHREADS, 1)
+gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
+                         const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
+                         int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store,
+                         int raster, uint32_t* sched) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = tiles + QSTAGES * QSTAGE_BYTES;
+  QBarriers* bars = reinterpret_cast<QBarriers*>(staging + 8 * EPI_BOX_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t peer = rank ^ 1u;
+  const bool leader = rank == 0;
+  const int tiles_m = (m + QBM - 1) / QBM, tiles_n = (n + QBN - 1) / QBN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+  const int num_kb = (k + BK - 1) / BK;
+  const int64_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
+  const bool split_drain = (raster >> SPLIT_DRAIN_BIT) & 1;
+  const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < QSTAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->tmem_full, 1);
+    mbar_init(&bars->tmem_empty[0], 16);
+    mbar_init(&bars->tmem_empty[1], 16);
+    for (int r = 0; r < RING; ++r) mbar_init(&bars->ring.full[r], 1);
+    bars->abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
+      const uint64_t pol = l2_policy(0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const int claim_kb = num_kb > 4 ? num_kb - 4 : 0;
+      uint32_t entry = 0;  // ring entries published (leader) or read (partner) so far
+      int64_t t = cluster_id;
+      while (ok && t < num_tiles) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
+        const int row_a = tc.m * QBM + (int)rank * 256;
+        const int row_b = tc.n * QBN + (int)rank * 128;
+        int64_t next = t + num_clusters;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (sched != nullptr && leader && kb == claim_kb) next = num_clusters + (int64_t)atomicAdd(sched, 1u);
+          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * QSTAGE_BYTES;
+          if (leader) mbar_expect_tx(&bars->full[stage], 2 * QSTAGE_BYTES);
+          const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
+          if (!a_mn) {  // one box of 256 rows x 128 bytes of K
+            tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader, pol);
+          } else {  // two boxes of [128 k rows] x [128 M positions]
+            tma_load_2d_pair(sa, &tma_a, row_a, kb * BK, full_in_leader, pol);
+            tma_load_2d_pair(sa + 128 * BK, &tma_a, row_a + 128, kb * BK, full_in_leader, pol);
+          }
+          tma_load_2d_pair(sa + QA_BYTES, &tma_b, b_mn ? row_b : kb * BK, b_mn ? kb * BK : row_b, full_in_leader, pol);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (sched != nullptr) {
+          if (leader) {
+            const uint32_t slot = entry & (RING - 1);
+            const int32_t v = next < num_tiles ? (int32_t)next : -1;
+            bars->ring.tile[slot] = v;
+            mbar_arrive(&bars->ring.full[slot]);
+            st_cluster_u32(mapa_u32(smem_u32(&bars->ring.tile[slot]), 1u), (uint32_t)v);
+            mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->ring.full[slot]), 1u));
+          } else {
+            const int32_t v = pair_ring_read(bars, entry, peer, 64u, 32u);
+            if (v == -2) { ok = false; break; }
+            next = v < 0 ? num_tiles : (int64_t)v;
+          }
+          ++entry;
+        }
+        t = next;
+      }
+      // tail: every release the leader multicast to this CTA's empty barriers has landed
+      for (int s = 0; ok && s < QSTAGES; ++s) {
+        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
+        if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t local = 0;
+      int64_t t = cluster_id;
+      // the four K = 32 MMAs of one k-block into accumulator half h
+      auto issue_half = [&](int st, int kb, int h) {
+        const uint32_t a_addr = smem_u32(tiles + st * QSTAGE_BYTES);
+        const uint32_t ah = a_addr + (uint32_t)h * 128u * BK;
+        const uint64_t da = a_mn ? make_smem_desc_mn(ah, 128 * BK) : make_smem_desc(ah);
+        const uint64_t db = b_mn ? make_smem_desc_mn(a_addr + QA_BYTES, QB_BYTES) : make_smem_desc(a_addr + QA_BYTES);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(h * 256);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          tc_mma_f8_pair(tmem_d, da + (uint64_t)kk * step_a, db + (uint64_t)kk * step_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+      };
+      for (; ok && t < num_tiles; ++local) {
+        const uint32_t free_parity = (uint32_t)(local & 1) ^ 1u;
+        if (!pair_wait(&bars->tmem_empty[0], free_parity, bars, peer, 2u)) { ok = false; break; }
+        tc_fence_after();
+        // head of the tile on accumulator half 0 alone, while the epilogue still drains half 1
+        const int head = split_drain ? (num_kb < QSTAGES ? num_kb : QSTAGES) : 0;
+        {
+          int st = stage;
+          uint32_t ph = phase;
+          for (int kb = 0; kb < head; ++kb) {
+            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u)) { ok = false; break; }
+            tc_fence_after();
+            issue_half(st, kb, 0);
+            if (++st == QSTAGES) { st = 0; ph ^= 1u; }
+          }
+        }
+        if (!ok) break;
+        if (!pair_wait(&bars->tmem_empty[1], free_parity, bars, peer, 2u)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < head; ++kb) {  // these stages are known to be full
+          issue_half(stage, kb, 1);
+          tc_commit_pair(&bars->empty[stage]);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        for (int kb = head; kb < num_kb; ++kb) {
+          if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u)) { ok = false; break; }
+          tc_fence_after();
+          issue_half(stage, kb, 0);
+          issue_half(stage, kb, 1);
+          tc_commit_pair(&bars->empty[stage]);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(&bars->tmem_full);
+        if (sched != nullptr) {
+          const int32_t v = pair_ring_read(bars, (uint32_t)local, peer, 16u, 0u);
+          if (v == -2) { ok = false; break; }
+          t = v < 0 ? num_tiles : (int64_t)v;
+        } else {
+          t += num_clusters;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
+    // Warp w drains lanes [32q, 32q+32), q = w & 3, and the column block p = (w - 2) >> 2 (128 of the
+    // 256 columns) of accumulator half 0 (rows 0..127 of this CTA), then of half 1 (rows 128..255).
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    float inv = 0.f;
+    {
+      const float sa = __ldg(scale_a), sb = __ldg(scale_b);
+      inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
+    }
+    const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
+                                staging + (warp - 2) * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
+    uint32_t boxes = 0;
+    bool ok = true;
+    int64_t local = 0;
+    int64_t t = cluster_id;
+    for (; ok && t < num_tiles; ++local) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
+      int got = 1;
+      if (lane == 0) got = pair_wait(&bars->tmem_full, (uint32_t)(local & 1), bars, peer, 8u, 256u) ? 1 : 0;
+      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 256 + part * 128);
+        wide::drain_wide<OutT>(ea, taddr, tc.m * QBM + (int)rank * 256 + h * 128 + quarter * 32, tc.n * QBN + part * 128,
+                               128, boxes);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[h]), 0u));
+      }
+      if (sched != nullptr) {
+        int v = 0;
+        if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, 64u);
+        v = __shfl_sync(0xFFFFFFFFu, v, 0);
+        if (v == -2) { ok = false; break; }
+        t = v < 0 ? num_tiles : (int64_t)v;
+      } else {
+        t += num_clusters;
+      }
+    }
+    if (use_tma_store && lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers or TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace pairwide
+
 // ---- host side --------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -1378,10 +1653,9 @@ template <typename OutT>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma, const float* sa,
                   const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k, uint32_t idesc,
                   int vec_ok, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_fp8_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  static PerDeviceOnce setup;  // the shared-memory opt-in is a per-device attribute
+  const cudaError_t attr_err = setup.run([](int*) {
+    return cudaFuncSetAttribute(gemm_fp8_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   });
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   const int64_t tiles = (int64_t)((m + BM - 1) / BM) * ((n + BN - 1) / BN);
@@ -1397,9 +1671,8 @@ template <typename OutT>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
                        uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int max_clusters = 0;
+  static PerDeviceOnce setup;  // shared-memory opt-in and cluster occupancy, once per device
+  int max_clusters = 0;
   auto kernel = pair::gemm_fp8_pair_kernel<OutT>;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -1412,13 +1685,16 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::PSMEM_BYTES);
-    if (attr_err == cudaSuccess) {
-      cfg.gridDim = dim3(2 * (sm_count() / 2));
-      attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-    }
-  });
+  const cudaError_t attr_err = setup.run(
+      [&](int* clusters_out) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::PSMEM_BYTES);
+        if (e == cudaSuccess) {
+          cfg.gridDim = dim3(2 * (sm_count() / 2));
+          e = cudaOccupancyMaxActiveClusters(clusters_out, kernel, &cfg);
+        }
+        return e;
+      },
+      &max_clusters);
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
   const int64_t tiles = (int64_t)((m + pair::PBM - 1) / pair::PBM) * ((n + pair::PBN - 1) / pair::PBN);
@@ -1442,11 +1718,10 @@ template <typename OutT>
 static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
                        uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(wide::gemm_fp8_wide_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    wide::WSMEM_BYTES);
+  static PerDeviceOnce setup;
+  const cudaError_t attr_err = setup.run([](int*) {
+    return cudaFuncSetAttribute(wide::gemm_fp8_wide_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                wide::WSMEM_BYTES);
   });
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   const int64_t tiles = (int64_t)((m + wide::WBM - 1) / wide::WBM) * ((n + wide::WBN - 1) / wide::WBN);
@@ -1463,6 +1738,57 @@ static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   return check_launch();
 }
 
+template <typename OutT>
+static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
+                           const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n,
+                           int k, uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
+  static PerDeviceOnce setup;  // shared-memory opt-in and cluster occupancy, once per device
+  int max_clusters = 0;
+  auto kernel = pairwide::gemm_fp8_pairwide_kernel<OutT>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(pairwide::QTHREADS);
+  cfg.dynamicSmemBytes = pairwide::QSMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t attr_err = setup.run(
+      [&](int* clusters_out) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pairwide::QSMEM_BYTES);
+        if (e == cudaSuccess) {
+          cfg.gridDim = dim3(2 * (sm_count() / 2));
+          e = cudaOccupancyMaxActiveClusters(clusters_out, kernel, &cfg);
+        }
+        return e;
+      },
+      &max_clusters);
+  if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
+  if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
+  const int64_t tiles = (int64_t)((m + pairwide::QBM - 1) / pairwide::QBM) * ((n + pairwide::QBN - 1) / pairwide::QBN);
+  int clusters = max_clusters;
+  if (persistent_ctas() / 2 < clusters) clusters = persistent_ctas() / 2;
+  if (tiles < clusters) clusters = (int)tiles;
+  cfg.gridDim = dim3(2 * clusters);
+  const OutT* bias_t = static_cast<const OutT*>(bias);
+  OutT* out_t = static_cast<OutT*>(out);
+  sched = usable_sched(sched, tiles, clusters);
+  if (sched != nullptr) {
+    const cudaError_t e = cudaMemsetAsync(sched, 0, sizeof(uint32_t), st);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  // F8B200_GEMM_SPLIT_DRAIN=0 makes the MMA thread wait for the whole accumulator (read at every call)
+  int split = 1 << pairwide::SPLIT_DRAIN_BIT;
+  if (const char* e = getenv("F8B200_GEMM_SPLIT_DRAIN"))
+    if (e[0] == '0') split = 0;
+  return record_cuda_error(
+      cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
+                         choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched));
+}
+
 // Kernel choice: 0 = one CTA per 128x256 tile, 1 = CTA pairs (256x256, cta_group::2), 2 = one CTA per 256x256 tile.
 // The pair kernel hides its epilogue behind the next tile's MMAs (two accumulators in tensor memory) but its MMAs
 // read half of B from the peer's shared memory; the wide kernel reads only its own shared memory but drains its
@@ -1476,6 +1802,7 @@ static int gemm_mode(int64_t k) {
   if (e != nullptr && e[0] == '1') return 0;
   if (e != nullptr && e[0] == '2') return 1;
   if (e != nullptr && e[0] == 'w') return 2;
+  if (e != nullptr && e[0] == 'p') return 3;
   int64_t wide_k = 16384;
   const char* t = getenv("F8B200_GEMM_WIDE_K");
   if (t != nullptr && t[0] != 0) wide_k = atoll(t);
@@ -1496,15 +1823,19 @@ static int dispatch_out_dtype(int out_dtype, Fn&& fn) {
   }
 }
 
-// a_layout / b_layout: F8B200_K_MAJOR = storage [rows, K] with K contiguous (ld >= K);
-// F8B200_MN_MAJOR = storage [K, rows] with rows contiguous (ld >= rows).
-static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind, int b_layout,
-                         int64_t ldb, const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
-                         void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* sched, void* stream) {
+// Argument checks shared by the entry points.  *empty is set when there is nothing to compute
+// (m == 0 or n == 0): the caller returns F8B200_OK without launching.
+static int gemm_fp8_validate(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
+                             int b_layout, int64_t ldb, const float* scale_a, const float* scale_b, const void* bias,
+                             int out_dtype, const void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, bool* empty) {
+  *empty = false;
   if (m < 0 || n < 0 || k < 0) return F8B200_ERR_BAD_ARG;
   if (a_kind < 0 || a_kind > 1 || b_kind < 0 || b_kind > 1 || out_dtype < 0 || out_dtype > 2) return F8B200_ERR_BAD_ARG;
   if (a_layout < 0 || a_layout > 1 || b_layout < 0 || b_layout > 1) return F8B200_ERR_BAD_ARG;
-  if (m == 0 || n == 0) return F8B200_OK;
+  if (m == 0 || n == 0) {
+    *empty = true;
+    return F8B200_OK;
+  }
   if (a == nullptr || b == nullptr || out == nullptr || scale_a == nullptr || scale_b == nullptr) return F8B200_ERR_BAD_ARG;
   if (k == 0) return F8B200_ERR_UNSUPPORTED;
   if (lda < (a_layout ? m : k) || ldb < (b_layout ? n : k) || ldo < n) return F8B200_ERR_BAD_ARG;
@@ -1515,8 +1846,19 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
   const int osz = out_dtype == F8B200_FP32 ? 4 : 2;
   if (reinterpret_cast<uintptr_t>(out) % osz != 0 || (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % osz != 0))
     return F8B200_ERR_ALIGNMENT;
-  int rc = f8b200_device_check();
-  if (rc != F8B200_OK) return rc;
+  return f8b200_device_check();
+}
+
+// a_layout / b_layout: F8B200_K_MAJOR = storage [rows, K] with K contiguous (ld >= K);
+// F8B200_MN_MAJOR = storage [K, rows] with rows contiguous (ld >= rows).
+static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind, int b_layout,
+                         int64_t ldb, const float* scale_a, const float* scale_b, const void* bias, int out_dtype,
+                         void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, uint32_t* sched, void* stream) {
+  bool empty = false;
+  int rc = gemm_fp8_validate(a, a_kind, a_layout, lda, b, b_kind, b_layout, ldb, scale_a, scale_b, bias, out_dtype, out,
+                             ldo, m, n, k, &empty);
+  if (rc != F8B200_OK || empty) return rc;
+  const int osz = out_dtype == F8B200_FP32 ? 4 : 2;
 
   const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1538,12 +1880,27 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
   const int layouts = (a_layout << gemm::LAYOUT_A_MN_BIT) | (b_layout << gemm::LAYOUT_B_MN_BIT);
   // operand maps: K-major boxes are [box_rows] x [128 bytes of K]; MN-major boxes are always
   // [128 k rows] x [128 bytes of M or N]
-  auto encode_operands = [&](int box_rows) {
+  auto encode_operands = [&](int box_rows, int box_rows_b = 0) {
     int r = a_layout ? gemm::encode_operand_map_mn(&ma, a, m, k, lda) : gemm::encode_operand_map(&ma, a, m, k, lda, box_rows);
     if (r != F8B200_OK) return r;
-    return b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb) : gemm::encode_operand_map(&mb, b, n, k, ldb, box_rows);
+    return b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb)
+                    : gemm::encode_operand_map(&mb, b, n, k, ldb, box_rows_b > 0 ? box_rows_b : box_rows);
   };
   int mode = gemm::gemm_mode(k);
+  if (mode == 3) {
+    // CTA pairs on 512x256 tiles: each CTA fetches a 256-row box of A and a 128-row box of B
+    rc = encode_operands(256, 128);
+    if (rc == F8B200_OK) rc = encode_output(true);
+    if (rc != F8B200_OK) return rc;
+    const uint32_t idq = gemm::pair::make_idesc_pair(a_kind, b_kind, a_layout, b_layout);
+    rc = dispatch_out_dtype(out_dtype, [&](auto* tag) {
+      using OutT = std::remove_pointer_t<decltype(tag)>;
+      return gemm::launch_pairwide<OutT>(ma, mb, mo, use_tma, scale_a, scale_b, bias, out, ldo, (int)m, (int)n, (int)k,
+                                         idq, vec_ok, layouts, sched, st);
+    });
+    if (rc != F8B200_ERR_UNSUPPORTED) return rc;
+    mode = 2;  // no room for a two-CTA cluster on this device
+  }
   if (mode == 1) {
     // each CTA of a pair fetches 128-row boxes of both operands
     rc = encode_operands(128);
@@ -1610,13 +1967,10 @@ extern "C" int f8b200_gemm_fp8_ws(const void* a, int a_kind, int a_layout, int64
 // file-scope device array, one 256-byte slot per stream that has called it on this device.
 namespace {
 constexpr int kStaticSlots = F8B200_STATIC_SCRATCH_BYTES / F8B200_GEMM_WORKSPACE_BYTES;
-constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_static_scratch[F8B200_STATIC_SCRATCH_BYTES];
 
 struct StaticScratch {
-  std::once_flag once;
-  cudaError_t err = cudaSuccess;
-  unsigned char* base = nullptr;  // address of g_static_scratch on this device
+  unsigned char* base = nullptr;  // address of g_static_scratch on this device; null until a lookup succeeds
   std::mutex mu;
   cudaStream_t owner[kStaticSlots];
   int used = 0;
@@ -1629,25 +1983,28 @@ extern "C" int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t
                                               const void* bias, int out_dtype, void* out, int64_t ldo, int64_t m,
                                               int64_t n, int64_t k, int use_fast_accum, void* stream) {
   (void)use_fast_accum;
-  int rc = f8b200_device_check();
-  if (rc != F8B200_OK) return rc;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return record_cuda_error(e);
-  if (dev < 0 || dev >= kMaxDevices) return F8B200_ERR_UNSUPPORTED;
+  // the argument checks come first: a refused or empty call neither looks the array up nor takes a slot
+  bool empty = false;
+  int rc = gemm_fp8_validate(a, a_kind, F8B200_K_MAJOR, lda, b, b_kind, F8B200_K_MAJOR, ldb, scale_a, scale_b, bias,
+                             out_dtype, out, ldo, m, n, k, &empty);
+  if (rc != F8B200_OK || empty) return rc;
+  const int dev = current_device_slot();
+  if (dev < 0) return F8B200_ERR_UNSUPPORTED;
   StaticScratch& sc = g_static[dev];
-  // set-up, once per device: the symbol's address (this is the call that must not fall inside a
-  // stream capture)
-  std::call_once(sc.once, [&sc] {
-    void* p = nullptr;
-    sc.err = cudaGetSymbolAddress(&p, g_static_scratch);
-    sc.base = static_cast<unsigned char*>(p);
-  });
-  if (sc.err != cudaSuccess) return record_cuda_error(sc.err);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int slot = -1;
+  unsigned char* base = nullptr;
   {
     std::lock_guard<std::mutex> lock(sc.mu);
+    // set-up, once per device: the symbol's address (the call that must not fall inside a stream
+    // capture).  Only a successful lookup is kept; after a failure the next call tries again.
+    if (sc.base == nullptr) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return record_cuda_error(e);
+      sc.base = static_cast<unsigned char*>(p);
+    }
+    base = sc.base;
     for (int i = 0; i < sc.used; ++i)
       if (sc.owner[i] == st) slot = i;
     if (slot < 0) {
@@ -1659,8 +2016,8 @@ extern "C" int f8b200_gemm_fp8_static_scratch(const void* a, int a_kind, int64_t
     }
   }
   return gemm_fp8_impl(a, a_kind, F8B200_K_MAJOR, lda, b, b_kind, F8B200_K_MAJOR, ldb, scale_a, scale_b, bias, out_dtype,
-                       out, ldo, m, n, k,
-                       reinterpret_cast<uint32_t*>(sc.base + (size_t)slot * F8B200_GEMM_WORKSPACE_BYTES), stream);
+                       out, ldo, m, n, k, reinterpret_cast<uint32_t*>(base + (size_t)slot * F8B200_GEMM_WORKSPACE_BYTES),
+                       stream);
 }
 
 extern "C" int f8b200_read_device_error(uint32_t* flags_out) {
@@ -1674,4 +2031,11 @@ extern "C" int f8b200_read_device_error(uint32_t* flags_out) {
   rc = record_cuda_error(cudaMemcpyToSymbol(g_device_error, &zero, sizeof(zero)));
   *flags_out = v;
   return rc;
+}
+
+extern "C" int f8b200_check_device_error(void) {
+  uint32_t flags = 0;
+  const int rc = f8b200_read_device_error(&flags);
+  if (rc != F8B200_OK) return rc;
+  return flags != 0 ? F8B200_ERR_TIMEOUT : F8B200_OK;
 }

@@ -3,6 +3,14 @@
 // is used only when that library is present: runs on two or more GPUs leave both out and fall
 // back to the kernels of gemm.cu, which this file includes for the shared device code.
 //
+// ONLY jobs that use ONE GPU may call into this library.  A multicast load must never be given a
+// tensor map that covers another GPU's memory, so the entry point refuses (F8B200_ERR_UNSUPPORTED,
+// nothing launched) any operand or output that is not plain device memory OWNED BY THE CURRENT
+// DEVICE: a peer pointer, an IPC or symmetric-memory mapping, managed or host memory.  The library
+// is built with hidden visibility and exports only its two f8b200_mc_* symbols: the copies of
+// gemm.cu's functions, error word and static scratch array it carries are private to it and never
+// interpose the ones of libf8b200.so.
+//
 // A cluster of CM x CN CTAs computes a (CM*256) x (CN*256) block of the output, one 256x256 tile
 // per CTA (two M128 N256 K32 MMAs per k-step, accumulators in all 512 TMEM columns, as in the
 // wide kernel).  The CN CTAs of one block row need the same 256 rows of A: each fetches 256/CN of
@@ -300,9 +308,8 @@ static int launch_mc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
                      const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k, uint32_t idesc,
                      int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
   constexpr int CS = CM * CN;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int max_clusters = 0;
+  static PerDeviceOnce setup;
+  int max_clusters = 0;
   auto kernel = gemm_fp8_mc_kernel<OutT, CM, CN>;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -315,13 +322,16 @@ static int launch_mc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WSMEM_BYTES);
-    if (attr_err == cudaSuccess) {
-      cfg.gridDim = dim3(CS * (sm_count() / CS));
-      attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-    }
-  });
+  const cudaError_t attr_err = setup.run(
+      [&](int* clusters_out) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WSMEM_BYTES);
+        if (e == cudaSuccess) {
+          cfg.gridDim = dim3(CS * (sm_count() / CS));
+          e = cudaOccupancyMaxActiveClusters(clusters_out, kernel, &cfg);
+        }
+        return e;
+      },
+      &max_clusters);
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
   const int64_t tiles = (int64_t)((m + CM * WBM - 1) / (CM * WBM)) * ((n + CN * WBN - 1) / (CN * WBN));
@@ -626,9 +636,8 @@ template <typename OutT>
 static int launch_pairmc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                          const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
                          uint32_t idesc, int vec_ok, uint32_t* sched, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int max_clusters = 0;
+  static PerDeviceOnce setup;
+  int max_clusters = 0;
   auto kernel = gemm_fp8_pairmc_kernel<OutT>;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -641,13 +650,16 @@ static int launch_pairmc(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PMC_SMEM_BYTES);
-    if (attr_err == cudaSuccess) {
-      cfg.gridDim = dim3(PMC_CLUSTER * (sm_count() / PMC_CLUSTER));
-      attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-    }
-  });
+  const cudaError_t attr_err = setup.run(
+      [&](int* clusters_out) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PMC_SMEM_BYTES);
+        if (e == cudaSuccess) {
+          cfg.gridDim = dim3(PMC_CLUSTER * (sm_count() / PMC_CLUSTER));
+          e = cudaOccupancyMaxActiveClusters(clusters_out, kernel, &cfg);
+        }
+        return e;
+      },
+      &max_clusters);
   if (attr_err != cudaSuccess) return record_cuda_error(attr_err);
   if (max_clusters < 1) return F8B200_ERR_UNSUPPORTED;
   const int64_t tiles = (int64_t)((m + 2 * PBM - 1) / (2 * PBM)) * ((n + PBN - 1) / PBN);
@@ -670,9 +682,24 @@ static int launch_pairmc(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
 }  // namespace gemm
 }  // namespace f8b200
 
+#define F8B200_MC_EXPORT extern "C" __attribute__((visibility("default")))
+
+// True when `p` is ordinary device memory allocated on the current device.
+static bool owned_by_current_device(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  return attr.type == cudaMemoryTypeDevice && attr.device == dev;
+}
+
 // Same contract as f8b200_gemm_fp8_ws plus the cluster shape (cluster_m x cluster_n tiles: 2x1 or
-// 2x2).  F8B200_ERR_UNSUPPORTED when such clusters cannot be scheduled on the device.
-extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
+// 2x2).  F8B200_ERR_UNSUPPORTED when such clusters cannot be scheduled on the device, or when an
+// operand / the output is not this device's own memory (see the head of this file).
+F8B200_MC_EXPORT int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
                                   int b_layout, int64_t ldb, const float* scale_a, const float* scale_b,
                                   const void* bias, int out_dtype, void* out, int64_t ldo, int64_t m, int64_t n,
                                   int64_t k, int cluster_m, int cluster_n, void* workspace, int64_t workspace_bytes,
@@ -698,6 +725,9 @@ extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64
     return F8B200_ERR_ALIGNMENT;
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
+  // the tensor maps given to multicast loads may cover this GPU's own memory only
+  if (!owned_by_current_device(a) || !owned_by_current_device(b) || !owned_by_current_device(out))
+    return F8B200_ERR_UNSUPPORTED;
   const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * osz) % 16 == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap ma, mb, mo;
@@ -747,4 +777,4 @@ extern "C" int f8b200_mc_gemm_fp8(const void* a, int a_kind, int a_layout, int64
 }
 
 // The device error word of THIS library's kernels (a bounded wait that gave up).
-extern "C" int f8b200_mc_read_device_error(uint32_t* flags_out) { return f8b200_read_device_error(flags_out); }
+F8B200_MC_EXPORT int f8b200_mc_read_device_error(uint32_t* flags_out) { return f8b200_read_device_error(flags_out); }

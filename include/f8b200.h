@@ -322,6 +322,16 @@ int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_d
  */
 int f8b200_read_device_error(uint32_t* flags_out);
 
+/*
+ * The same read as a status: F8B200_OK when no bounded wait gave up since the last read,
+ * F8B200_ERR_TIMEOUT otherwise (the word is cleared either way; synchronises the device).  A
+ * launch returns F8B200_OK as soon as the kernel is queued, so a wait that runs out later can only
+ * show up here: C callers poll this at a point where they synchronise anyway (end of a step) and
+ * treat F8B200_ERR_TIMEOUT as "the outputs of the GEMMs since the last poll are undefined".  No
+ * counterpart in the reference (cuBLASLt reports nothing of the kind).
+ */
+int f8b200_check_device_error(void);
+
 #ifdef __cplusplus
 }
 #endif

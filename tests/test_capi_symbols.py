@@ -10,8 +10,8 @@ from float8_experimental_b200.csrc import build as builder
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "f8b200.h")).read()
+def declared_symbols(header="f8b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(f8b200_\w+)\s*\(", text)))
 
@@ -25,6 +25,32 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert sorted(_native.EXPORTS) == names
+
+
+def test_multicast_library_exports_exactly_its_header():
+    """libf8b200_mc.so (single-GPU jobs only) exports the two entry points of f8b200_mc.h and
+    nothing else: the copy of gemm.cu it carries stays private (hidden visibility), so it cannot
+    interpose libf8b200.so's symbols.  Its entry point refuses pointers before any CUDA work."""
+    import subprocess
+
+    path = builder.build_mc()
+    if path is None:
+        import pytest
+
+        pytest.skip("gemm_mc.cu is not part of this checkout")
+    names = declared_symbols("f8b200_mc.h")
+    assert names == ["f8b200_mc_gemm_fp8", "f8b200_mc_read_device_error"]
+    out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+    exported = sorted(line.split()[-1] for line in out.splitlines() if " T " in line)
+    assert exported == names, exported
+    lib = ctypes.CDLL(path)
+    vp = ctypes.c_void_p
+    lib.f8b200_mc_gemm_fp8.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, vp, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_int64, vp, vp, vp, ctypes.c_int, vp, ctypes.c_int64, ctypes.c_int64,
+                                       ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp, ctypes.c_int64, vp]
+    # unknown cluster shape: refused before anything touches CUDA
+    assert lib.f8b200_mc_gemm_fp8(vp(16), 0, 0, 16, vp(16), 0, 0, 16, vp(4), vp(4), None, 0, vp(16), 16, 4, 4, 16, 3, 1,
+                                  None, 0, None) == -1
 
 
 def test_status_strings_and_argument_validation():
@@ -45,6 +71,12 @@ def test_status_strings_and_argument_validation():
     assert lib.f8b200_gemm_fp8_ws(*args, None, 256, None) == -1
     assert lib.f8b200_gemm_fp8_ws(*args, ctypes.c_void_p(256), 8, None) == -1
     assert lib.f8b200_gemm_fp8_ws(*args, ctypes.c_void_p(260), 256, None) == -2
+    # the static-scratch entry validates before it looks anything up or takes a slot
+    assert lib.f8b200_gemm_fp8_static_scratch(ctypes.c_void_p(16), 0, 8, ctypes.c_void_p(16), 0, 16, ctypes.c_void_p(4),
+                                              ctypes.c_void_p(4), None, 0, ctypes.c_void_p(16), 16, 4, 4, 16, 0,
+                                              None) == -1
+    assert lib.f8b200_gemm_fp8_static_scratch(None, 0, 16, None, 0, 16, None, None, None, 0, None, 16, 0, 4, 16, 0,
+                                              None) == 0  # m == 0: nothing to do
     assert lib.f8b200_cast(ctypes.c_void_p(16), 0, 4, 4, 2, 0, ctypes.c_void_p(4), None, 0, 0, None, 0, None, 0,
                            None, 0, None) == -1
 

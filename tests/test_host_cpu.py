@@ -402,6 +402,7 @@ def test_multicast_gemm_selection_rules(monkeypatch):
     from float8_experimental_b200 import _native as N
 
     monkeypatch.setattr(N, "load_mc", lambda: object())
+    monkeypatch.setattr(N, "_single_gpu_job", lambda: True)
     monkeypatch.delenv("F8B200_GEMM_MC", raising=False)
     monkeypatch.delenv("F8B200_GEMM_MODE", raising=False)
     monkeypatch.delenv("F8B200_GEMM_WIDE_K", raising=False)
@@ -417,3 +418,37 @@ def test_multicast_gemm_selection_rules(monkeypatch):
     monkeypatch.delenv("F8B200_GEMM_MC")
     monkeypatch.setattr(N, "load_mc", lambda: None)  # library not shipped (runs on several GPUs)
     assert N._mc_cluster(8192, 8192, 16384) is None
+    # ... and never in a job that may use a second GPU, whatever was shipped or forced
+    monkeypatch.setattr(N, "load_mc", lambda: object())
+    monkeypatch.setattr(N, "_single_gpu_job", lambda: False)
+    monkeypatch.setenv("F8B200_GEMM_MC", "21")
+    assert N._mc_cluster(8192, 8192, 16384) is None
+
+
+def test_single_gpu_job_rules(monkeypatch):
+    """The multicast GEMM is for jobs on one GPU: more than one visible device, a launcher that
+    announced several ranks (before any process group exists) or an initialised group of several
+    ranks all switch it off."""
+    import torch
+
+    from float8_experimental_b200 import _native as N
+
+    for var in ("WORLD_SIZE", "LOCAL_WORLD_SIZE"):
+        monkeypatch.delenv(var, raising=False)
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 1)
+    assert N._single_gpu_job()
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 2)
+    assert not N._single_gpu_job()
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 0)
+    assert not N._single_gpu_job()
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 1)
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    assert not N._single_gpu_job()
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert not N._single_gpu_job()
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "1")
+    assert N._single_gpu_job()
+    monkeypatch.setattr(torch.distributed, "is_initialized", lambda: True)
+    monkeypatch.setattr(torch.distributed, "get_world_size", lambda *a, **k: 2)
+    assert not N._single_gpu_job()

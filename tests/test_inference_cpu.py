@@ -32,26 +32,53 @@ class FFN(nn.Module):
         return self.w2(torch.relu(self.w1(x)))
 
 
+class FeedForward(nn.Module):
+    """The model of the reference's inference tests (test/test_inference_flows.py:35-49: w1, w3,
+    w2 without bias around a SiLU gate, default nn.Linear init) at a quarter of its width."""
+
+    def __init__(self, dim=256, hidden=896):
+        super().__init__()
+        self.w1 = nn.Linear(dim, hidden, bias=False)
+        self.w3 = nn.Linear(dim, hidden, bias=False)
+        self.w2 = nn.Linear(hidden, dim, bias=False)
+
+    def forward(self, x):
+        return self.w2(nn.functional.silu(self.w1(x)) * self.w3(x))
+
+
 def configs():
+    # the static scale of the reference's test (test/test_inference_flows.py:105-110)
     return [
         QuantConfig(ActivationCasting.WEIGHT_ONLY),
         QuantConfig(ActivationCasting.DYNAMIC),
-        QuantConfig(ActivationCasting.STATIC, static_quantization_scale=torch.tensor([40.0])),
+        QuantConfig(ActivationCasting.STATIC, static_quantization_scale=torch.tensor([1.0])),
     ]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
 @pytest.mark.parametrize("cfg", configs(), ids=["weight_only", "dynamic", "static"])
-def test_modes_track_the_high_precision_model(cfg):
+def test_modes_track_the_high_precision_model(cfg, dtype):
+    """SQNR against the high-precision model above 20 dB, the reference's own bar
+    (test/test_inference_flows.py:51-58), for the three activation-casting modes."""
     torch.manual_seed(0)
-    ref = FFN()
+    ref = FeedForward().to(dtype)
     q = quantize_to_float8(copy.deepcopy(ref), cfg)
     assert isinstance(q.w1, Float8InferenceLinear) and isinstance(q.w1.weight, Float8Tensor)
     assert not q.w1.weight.requires_grad
-    x = torch.randn(4, 16, 64)
+    x = torch.randn(4, 64, 256, dtype=dtype)
     with torch.no_grad():
         y_ref, y = ref(x), q(x)
     assert y.shape == y_ref.shape and y.dtype == y_ref.dtype
-    assert compute_error(y_ref, y) > 15.0  # two stacked e4m3 quantisations on a toy FFN
+    assert compute_error(y_ref, y) > 20.0
+
+
+def test_bias_is_carried_through_the_quantised_linear():
+    torch.manual_seed(0)
+    ref = FFN()
+    q = quantize_to_float8(copy.deepcopy(ref), QuantConfig(ActivationCasting.DYNAMIC))
+    x = torch.randn(4, 16, 64)
+    with torch.no_grad():
+        assert compute_error(ref.w1(x), q.w1(x)) > 20.0
 
 
 def test_static_config_needs_a_scale_and_double_quantize_is_rejected():

@@ -191,11 +191,11 @@ def test_transpose_u8():
 
 
 # ---------------------------------------------------------------------------
-@pytest.fixture(params=["2cta", "1cta", "wide", "2cta-direct", "1cta-direct", "wide-direct"])
+@pytest.fixture(params=["2cta", "1cta", "wide", "pw", "2cta-direct", "1cta-direct", "wide-direct", "pw-direct"])
 def gemm_mode(request, monkeypatch):
-    """The three GEMM kernels (CTA pairs with cta_group::2, the default; one CTA per 128x256
-    tile; one CTA per 256x256 tile), each with the TMA-store epilogue and with the per-thread
-    store epilogue."""
+    """The four GEMM kernels (CTA pairs on 256x256 tiles; one CTA per 128x256 tile; one CTA per
+    256x256 tile; CTA pairs on 512x256 tiles), each with the TMA-store epilogue and with the
+    per-thread store epilogue."""
     mode, _, store = request.param.partition("-")
     monkeypatch.setenv("F8B200_GEMM_MODE", mode)
     monkeypatch.setenv("F8B200_GEMM_STORE", store or "tma")
@@ -284,9 +284,30 @@ def test_gemm_dynamic_schedule_matches_fixed_stride(mnk, gemm_mode, monkeypatch)
     check_gemm(fixed[rows].float(), a[rows].float() @ b.float().t())
 
 
+@pytest.mark.parametrize("mnk", [(2048, 1024, 384), (4096 + 40, 2048 + 24, 1024 + 16), (1024, 512, 128 * 3)])
+def test_gemm_split_drain_matches_whole_drain(mnk, monkeypatch):
+    """The 512x256 pair kernel starts the next tile on the accumulator half its epilogue has already
+    drained; with F8B200_GEMM_SPLIT_DRAIN=0 it waits for the whole accumulator.  Every output element
+    is accumulated in the same order either way, so the outputs are bit-identical, and equal to the
+    256x256 pair kernel's."""
+    m, n, k = mnk
+    g = torch.Generator(device="cuda").manual_seed(m + 3 * n + k)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    sa, sb = torch.tensor(2.0, device="cuda"), torch.tensor(0.5, device="cuda")
+    monkeypatch.setenv("F8B200_GEMM_MODE", "2cta")
+    want = gemm(a, b, sa, sb)
+    monkeypatch.setenv("F8B200_GEMM_MODE", "pw")
+    for split in ("0", "1", "1"):
+        monkeypatch.setenv("F8B200_GEMM_SPLIT_DRAIN", split)
+        assert torch.equal(gemm(a, b, sa, sb).view(torch.int16), want.view(torch.int16)), split
+    rows = torch.tensor([0, 127, 128, 255, 256, 511, 512, m - 1], device="cuda")
+    check_gemm(want[rows].float(), a[rows].float() @ b.float().t())
+
+
 @pytest.mark.parametrize("layouts", [(False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("mnk", [(512, 768, 256), (4096, 2048 + 16, 1024 + 48), (8192, 4096, 16384 + 128)])
-@pytest.mark.parametrize("mode", ["2cta", "wide"])
+@pytest.mark.parametrize("mode", ["2cta", "wide", "pw"])
 def test_gemm_mn_major_operands(mnk, layouts, mode, monkeypatch):
     """An operand may be handed over as the transpose of the usual storage ([K, rows], rows
     contiguous): the result has to be bit-identical to the K-major call on the same values."""

@@ -164,24 +164,97 @@ def test_model_conversion_and_training_step():
         model(x)
 
 
-def test_inference_flows_on_gpu():
-    """Weight-only, dynamic and static activation casting (reference: test/test_inference_flows.py)."""
-    from float8_experimental_b200.inference import ActivationCasting, QuantConfig, quantize_to_float8
+class _FeedForward(nn.Module):
+    """The model of the reference's inference tests (test/test_inference_flows.py:35-49), at a
+    quarter of its width."""
+
+    def __init__(self, dim=1024, hidden=3584):
+        super().__init__()
+        self.w1 = nn.Linear(dim, hidden, bias=False)
+        self.w3 = nn.Linear(dim, hidden, bias=False)
+        self.w2 = nn.Linear(hidden, dim, bias=False)
+
+    def forward(self, x):
+        return self.w2(nn.functional.silu(self.w1(x)) * self.w3(x))
+
+
+def _inference_configs():
+    from float8_experimental_b200.inference import ActivationCasting, QuantConfig
+
+    return [QuantConfig(ActivationCasting.WEIGHT_ONLY), QuantConfig(ActivationCasting.DYNAMIC),
+            QuantConfig(ActivationCasting.STATIC, static_quantization_scale=torch.tensor([1.0], device="cuda"))]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_inference_flows_on_gpu(dtype):
+    """Weight-only, dynamic and static activation casting against the high-precision model: SQNR
+    above 20 dB, the reference's bar (test/test_inference_flows.py:51-58), same model, init, input
+    distribution and static scale."""
+    import copy
+
+    from float8_experimental_b200.inference import quantize_to_float8
 
     torch.manual_seed(0)
-    ref = nn.Sequential(nn.Linear(256, 512, bias=True), nn.Linear(512, 256, bias=False)).cuda().to(torch.bfloat16)
-    x = torch.randn(4, 64, 256, device="cuda", dtype=torch.bfloat16)
+    ref = _FeedForward().cuda().to(dtype)
+    x = torch.randn(4, 256, 1024, device="cuda", dtype=dtype)
     with torch.no_grad():
         y_ref = ref(x)
-    for cfg in (QuantConfig(ActivationCasting.WEIGHT_ONLY), QuantConfig(ActivationCasting.DYNAMIC),
-                QuantConfig(ActivationCasting.STATIC, static_quantization_scale=torch.tensor([60.0], device="cuda"))):
-        import copy
-
+    for cfg in _inference_configs():
         q = quantize_to_float8(copy.deepcopy(ref), cfg)
         with torch.no_grad():
             y = q(x)
-        assert y.shape == y_ref.shape and y.dtype == torch.bfloat16
-        assert compute_error(y_ref.float(), y.float()) > 15.0, cfg.activation_casting
+        assert y.shape == y_ref.shape and y.dtype == dtype
+        assert compute_error(y_ref.float(), y.float()) > 20.0, cfg.activation_casting
+    assert N_native.read_device_error() == 0
+
+
+def test_inference_linear_against_the_oracle():
+    """One quantised linear (with bias) per activation-casting mode against the CPU restatement
+    of the reference: weight bytes and scale bit-exact (quantize_weight = tensor_to_scale + cast,
+    inference.py:120-137), activation bytes bit-exact (dynamic: own amax; static: the given
+    scale, inference.py:179-211), output within the GEMM tolerance of the emulated product plus
+    bias (float8_ops.py:193-227); weight-only = a high-precision matmul with the dequantised
+    weight (inference.py:100-104)."""
+    from float8_experimental_b200.inference import ActivationCasting, Float8InferenceLinear
+
+    torch.manual_seed(3)
+    k, n, m = 512, 768, 384
+    lin = nn.Linear(k, n, bias=True, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+
+    def hp_bits(t):
+        return t.detach().contiguous().cpu().view(torch.int16).numpy().view(np.uint16)
+
+    w_amax = O.tensor_to_amax(hp_bits(lin.weight), O.BF16)
+    w_scale = O.amax_to_scale(w_amax, O.E4M3, O.BF16, O.BF16)
+    w_bytes = O.cast_to_fp8(hp_bits(lin.weight), O.BF16, w_scale, O.E4M3, O.BF16)
+    bias = lin.bias.detach().float().cpu().numpy()
+    for cfg in _inference_configs():
+        fresh = nn.Linear(k, n, bias=True, device="cuda", dtype=torch.bfloat16)
+        fresh.load_state_dict(lin.state_dict())
+        q = Float8InferenceLinear.from_float(fresh, cfg, True)
+        assert np.array_equal(bits(q.weight._data), w_bytes)
+        assert q.weight._scale.item() == float(w_scale)
+        with torch.no_grad():
+            y = q(x)
+        if cfg.activation_casting == ActivationCasting.WEIGHT_ONLY:
+            w_deq = torch.from_numpy(O.dequant(w_bytes, O.E4M3, w_scale, O.BF16)).cuda()  # bf16 values as fp32
+            assert torch.equal(q.weight.to_original_precision().float(), w_deq)
+            check((x.float() @ w_deq.t()).cpu(), y.float().cpu())
+            continue
+        if cfg.activation_casting == ActivationCasting.DYNAMIC:
+            x_scale = O.amax_to_scale(O.tensor_to_amax(hp_bits(x), O.BF16), O.E4M3, O.BF16, O.BF16)
+            x_bytes = O.cast_to_fp8(hp_bits(x), O.BF16, x_scale, O.E4M3, O.BF16)
+        else:  # a [1] scale multiplies in fp32 (type promotion of a bf16 tensor with a 1-element fp32 tensor)
+            x_scale = np.float32(1.0)
+            x_bytes = O.cast_to_fp8(hp_bits(x), O.BF16, x_scale, O.E4M3, O.FP32)
+        from float8_experimental_b200.inference import cast_to_float8_e4m3_inference
+
+        x8 = cast_to_float8_e4m3_inference(x, q.linear_mm_config, static_quantization_scale=q.static_quantization_scale)
+        assert np.array_equal(bits(x8._data), x_bytes), cfg.activation_casting
+        ref = O.mm_float8_emulated(x_bytes, O.E4M3, x_scale, w_bytes.T, O.E4M3, w_scale, O.FP32) + bias[None, :]
+        check(torch.from_numpy(ref), y.float().cpu())
+    assert N_native.read_device_error() == 0
 
 
 def test_autocast_sets_the_output_dtype():
