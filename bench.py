@@ -32,10 +32,28 @@ NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 # casts also write a transposed fp8 copy only when asked to (the GEMMs read either memory order)
 TRANSPOSED_COPIES = os.environ.get("F8B200_CAST_TRANSPOSED", "0") == "1"
-# dram__bytes_write of the cast kernel on a 16384x8192 bf16 tensor without the transposed copy
-# (profiles/cast_tile8_kernel_16384x8192_bf16.md; 134 MB are written, 78 MB have left L2 at kernel end)
-CAST_WRITE_TRAFFIC_1COPY = 78.2e6
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# f8b200_gemm_kernel_choice codes
+GEMM_KERNEL_NAMES = {0: "gemm_fp8_kernel (one CTA per 128x256 tile)", 1: "gemm_fp8_pair_kernel (CTA pair per 256x256 tile)",
+                     2: "gemm_fp8_wide_kernel (one CTA per 256x256 tile)",
+                     3: "gemm_fp8_pairwide_kernel (CTA pair per 512x256 tile, cta_group::2, 256x256 accumulator per CTA)"}
+GEMM_KERNEL_SHORT = {0: "1cta", 1: "2cta", 2: "wide", 3: "pw"}
+# (dram__bytes_read.sum, dram__bytes_write.sum) per launch from ncu captures of single launches at full size
+# (one capture per product and kernel, --clock-control none, bf16 output, K-major operands)
+GEMM_DRAM_TRAFFIC = {
+    "2cta": {"wo.fwd": (0.34e9, 0.25e9), "wo.wgrad": (0.89e9, 0.12e9), "w13.fwd": (2.10e9, 1.86e9),
+             "w13.dgrad": (10.46e9, 0.27e9), "w13.wgrad": (4.76e9, 0.93e9), "w2.fwd": (4.00e9, 0.26e9),
+             "w2.dgrad": (1.12e9, 0.92e9)},
+    "wide": {"wo.fwd": (0.43e9, 0.24e9), "wo.wgrad": (0.88e9, 0.12e9), "w13.fwd": (2.45e9, 1.86e9),
+             "w13.dgrad": (6.54e9, 0.26e9), "w13.wgrad": (5.46e9, 0.93e9), "w2.fwd": (2.93e9, 0.26e9),
+             "w2.dgrad": (1.34e9, 0.91e9)},
+    "pw": {"wqkv.fwd": (0.61e9, 0.31e9), "wqkv.dgrad": (0.87e9, 0.25e9), "wqkv.wgrad": (1.05e9, 0.16e9),
+           "wo.fwd": (0.48e9, 0.25e9), "wo.dgrad": (0.47e9, 0.25e9), "wo.wgrad": (0.82e9, 0.12e9),
+           "w13.fwd": (2.22e9, 1.86e9), "w13.dgrad": (7.74e9, 0.26e9), "w13.wgrad": (7.10e9, 0.93e9),
+           "w2.fwd": (3.42e9, 0.26e9), "w2.dgrad": (1.26e9, 0.92e9), "w2.wgrad": (3.01e9, 0.46e9)},
+}
+# amax launch read + cast launch read + cast launch write on one 16384 x 8192 bf16 tensor
+CAST_DRAM_TRAFFIC = {"plain": (268.4e6, 268.5e6, 78.2e6), "transposed": (268.4e6, 268.5e6, 211.9e6)}
 
 
 def layer_flops(k: int, n: int, m: int = M_TOKENS) -> float:
@@ -105,272 +123,148 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------
-# CPU arm: the oracle's restatement of the reference's emulate path
+# CPU arm: the reference's own emulate=True path (oracle/_ref, the unmodified package) when it is
+# there, else the restatement of that path in oracle/ ("port"), on a bounded sample of the workload
 # ---------------------------------------------------------------------------
-def cpu_sample_step(sample):
-    # C/OpenMP restatement of the casts + numpy BLAS for the three fp32 GEMMs
-    from oracle import f8_oracle_c as C
-
-    return C.float8_linear_fwd_bwd(sample["x"], sample["w"], sample["go"], "bf16")
+CPU_SAMPLE_ROWS = 2048
 
 
-def make_cpu_sample(rows: int = 2048):
-    """`rows` tokens of the `wo` layer (K = N = 8192)."""
+def use_all_host_threads() -> int:
+    """Launchers (torch.distributed.run) export OMP_NUM_THREADS=1 for their ranks.  The CPU arm runs
+    on ONE rank and is meant to use every host core, so the thread-count variables are set before
+    numpy / torch / the OpenMP runtime are loaded.  Returns the count asked for."""
+    cores = os.cpu_count() or 1
+    for var in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "OPENBLAS_NUM_THREADS"):
+        os.environ[var] = str(cores)
+    return cores
+
+
+def reference_package():
+    """The unmodified reference package placed under oracle/_ref by oracle/make_ref.py, or None."""
+    from oracle import make_ref
+
+    path = make_ref.ref_path()
+    if path is None:
+        return None
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    try:
+        import float8_experimental  # noqa: F401
+        from float8_experimental.float8_linear import Float8Linear  # noqa: F401
+    except Exception:  # noqa: BLE001
+        return None
+    return sys.modules["float8_experimental"]
+
+
+def _cpu_tensors(rows, k, n, seed=7):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+    go = (torch.randn(rows, n, generator=g) * 1e-3).to(torch.bfloat16)
+    return x, w, go
+
+
+def _reference_cpu_step_fn(rows, k, n):
+    """fwd+bwd of the reference's Float8Linear(emulate=True), dynamic scaling, on CPU tensors."""
+    import torch
+    from float8_experimental.config import Float8LinearConfig
+    from float8_experimental.float8_linear import Float8Linear
+
+    x, w, go = _cpu_tensors(rows, k, n)
+    lin = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    mod = Float8Linear.from_float(lin, Float8LinearConfig(emulate=True))
+    x.requires_grad_(True)
+
+    def step():
+        x.grad = None
+        mod.weight.grad = None
+        mod(x).backward(go)
+
+    return step
+
+
+def _port_cpu_step_fn(rows, k, n):
+    """The same step through the restatement: casts in C with OpenMP, fp32 GEMMs through numpy's BLAS."""
     import numpy as np
 
-    from oracle import f8_oracle as O
+    from oracle import f8_oracle_c as C
 
-    rng = np.random.default_rng(7)
-    k, n = SHAPES[1][1], SHAPES[1][2]
-    f = lambda a: O.f32_to_bf16_bits(a.astype(np.float32))  # noqa: E731
-    return {"x": f(rng.standard_normal((rows, k))), "w": f(rng.standard_normal((n, k)) * 0.02),
-            "go": f(rng.standard_normal((rows, n)) * 1e-3), "rows": rows, "k": k, "n": n,
-            "flops": layer_flops(k, n, rows),
-            "desc": f"wo layer (K=N=8192) fwd+bwd on {rows} of {M_TOKENS} token rows; port of the emulate=True path "
-                    "(casts in C with OpenMP, fp32 GEMMs through numpy BLAS, all host cores)"}
+    x, w, go = _cpu_tensors(rows, k, n)
+    bits = lambda t: t.view(__import__("torch").int16).numpy().view(np.uint16)  # noqa: E731
+    xb, wb, gb = bits(x), bits(w), bits(go)
+    return lambda: C.float8_linear_fwd_bwd(xb, wb, gb, "bf16")
 
 
-def time_cpu(sample, steps: int, warmup: int):
+def _time_host(step, steps, warmup):
     for _ in range(warmup):
-        cpu_sample_step(sample)
+        step()
     ts = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        cpu_sample_step(sample)
+        step()
         ts.append(time.perf_counter() - t0)
     return ts
 
 
+def time_cpu_arm(steps: int, warmup: int, extras: bool = True):
+    """Times the CPU arm: `steps` passes (after `warmup`) over the bounded sample, median.  The
+    sample is forward + backward of the `wo` layer (K = N = 8192) on 2048 of the 16384 token rows.
+    With `extras`: the reference's own CPU-runnable configuration in full (one Float8Linear 4096 ->
+    4096, 2048 tokens) and the other implementation of the arm as a cross-check."""
+    import torch
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    k, n = SHAPES[1][1], SHAPES[1][2]
+    ref = reference_package()
+    kind = "reference" if ref is not None else "port"
+    step = _reference_cpu_step_fn(CPU_SAMPLE_ROWS, k, n) if ref is not None else _port_cpu_step_fn(CPU_SAMPLE_ROWS, k, n)
+    ts = _time_host(step, steps, warmup)
+    flops = layer_flops(k, n, CPU_SAMPLE_ROWS)
+    med = statistics.median(ts)
+    what = ("the reference's Float8Linear (unmodified package, emulate=True, dynamic scaling) on CPU tensors"
+            if ref is not None else
+            "restatement of the emulate=True path (casts in C with OpenMP, fp32 GEMMs through numpy BLAS)")
+    out = {"value": flops / med / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+           "sample": f"wo layer (K=N=8192) fwd+bwd on {CPU_SAMPLE_ROWS} of {M_TOKENS} token rows; {what}; "
+                     f"median of {steps} after {warmup} warm-up",
+           "ms_per_step": med * 1e3, "statistic": "median"}
+    if extras:
+        try:
+            c1 = _reference_cpu_step_fn(2048, 4096, 4096) if ref is not None else _port_cpu_step_fn(2048, 4096, 4096)
+            t1 = statistics.median(_time_host(c1, 3, 1))
+            out["config1"] = {"what": "Float8Linear(4096, 4096), 2048 tokens, fwd+bwd, whole configuration", "ms": t1 * 1e3,
+                              "tflops": layer_flops(4096, 4096, 2048) / t1 / 1e12}
+            if ref is not None:
+                tp = statistics.median(_time_host(_port_cpu_step_fn(CPU_SAMPLE_ROWS, k, n), 3, 1))
+                out["port_cross_check_tflops"] = flops / tp / 1e12
+        except Exception as exc:  # noqa: BLE001
+            out["extras_error"] = f"{type(exc).__name__}: {exc}"[:200]
+    return out
+
+
 def run_reference_arm(args, rank: int, world: int):
+    """`--impl reference`: the CPU arm alone, on rank 0 (the other ranks of a multi-rank launch exit
+    without work), honouring --steps / --warmup, with every host thread."""
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
-    sample = make_cpu_sample()
-    ts = time_cpu(sample, steps, warmup)
-    tflops = sample["flops"] / statistics.median(ts) / 1e12
-    cores = os.cpu_count() or 1
+    cpu = time_cpu_arm(max(1, args.steps), max(0, args.warmup))
     line = {
-        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": statistics.median(ts) * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
-        "config": {"workload": "LLaMa-2-70B linear shapes, M=16384, dynamic scaling (CPU arm: bounded sample)",
-                   "sample": sample["desc"]},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample["desc"]},
-        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": max(1, args.steps), "warmup": max(0, args.warmup), "ms_per_step": cpu["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {"workload": "LLaMa-2-70B linear shapes (wqkv, wo, w13, w2), M=16384 tokens per GPU, Float8Linear "
+                               "fwd+bwd, dynamic scaling, bf16 in/out (CPU arm: bounded sample per step)",
+                   "sample": cpu["sample"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
-
-
-def measure_delayed(torch, f8, _native, dev, x):
-    """Config 3: one batched sync over 320 linears (960 rows, history 16) and the one-pass
-    delayed cast (amax + cast + transposed copy) of a [16384, 8192] bf16 activation."""
-    from float8_experimental_b200.float8_linear_utils import get_float8_layers
-
-    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
-    cfg = f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d)
-    model = torch.nn.Sequential(*[torch.nn.Linear(16, 16, bias=False, device=dev) for _ in range(320)])
-    f8.convert_to_float8_training(model, config=cfg)
-    layers = get_float8_layers(model)
-    g = torch.Generator(device=dev).manual_seed(3)
-    for m in layers:
-        m.last_seen_input_dtype = torch.bfloat16
-        for name, sigma in (("input", 1.0), ("weight", 0.02), ("grad_output", 1e-3)):
-            getattr(m, f"fp8_amax_history_{name}").copy_(torch.randn(16, device=dev, generator=g).abs() * 4 * sigma)
-            getattr(m, f"fp8_amax_{name}").copy_(torch.randn(1, device=dev, generator=g).abs() * 4 * sigma)
-    for _ in range(3):
-        f8.sync_float8_amax_and_scale_history(model, layers)
-    torch.cuda.synchronize()
-    _native.reset_counters()
-    _native.enable_kernel_events(True)
-    t0 = time.perf_counter()
-    for _ in range(20):
-        f8.sync_float8_amax_and_scale_history(model, layers)
-    torch.cuda.synchronize()
-    wall_us = (time.perf_counter() - t0) / 20 * 1e6
-    ev = _native.kernel_event_totals().get("sync", (0.0, 1))
-    _native.enable_kernel_events(False)
-    # one-pass delayed cast
-    from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_delayed
-
-    scale, amax = torch.ones(1, device=dev), torch.zeros(1, device=dev)
-    for _ in range(3):
-        hp_tensor_to_float8_delayed(x, scale, torch.float8_e4m3fn, amax)
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(20):
-        hp_tensor_to_float8_delayed(x, scale, torch.float8_e4m3fn, amax)
-    s1.record()
-    torch.cuda.synchronize()
-    cast_ms = s0.elapsed_time(s1) / 20
-    return {"sync_rows": 960, "sync_kernel_us": ev[0] / max(ev[1], 1) * 1e3, "sync_launches_per_call": 1,
-            "sync_wall_us_per_call": wall_us, "step": measure_delayed_step(torch, f8, dev),
-            "delayed_cast_ms_16384x8192": cast_ms,
-            "delayed_cast_gbs": (4.0 if TRANSPOSED_COPIES else 3.0) * x.numel() / (cast_ms * 1e-3) / 1e9,
-            "delayed_cast_bytes": ("4 B per element: 2 read + 1 fp8 + 1 transposed fp8, amax from the same read"
-                                   if TRANSPOSED_COPIES else "3 B per element: 2 read + 1 fp8, amax from the same read")}
-
-
-def measure_delayed_step(torch, f8, dev, steps: int = 10):
-    """The step of the timed region with delayed scaling for all three tensors (the reference's
-    third configuration): the same four linears, fwd+bwd, plus one
-    sync_float8_amax_and_scale_history over them per step.  Casts are one launch each (the amax
-    comes from the cast's own read), so the dynamic step's twelve amax launches disappear."""
-    from float8_experimental_b200.float8_linear import Float8Linear
-
-    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
-    cfg = f8.Float8LinearConfig(cast_config_input=d, cast_config_weight=d, cast_config_grad_output=d)
-    gen = torch.Generator(device=dev).manual_seed(77)
-    layers, xs, gos = [], [], []
-    for _, k, n in SHAPES:
-        lin = torch.nn.Linear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
-        with torch.no_grad():
-            lin.weight.normal_(0.0, 0.02, generator=gen)
-        layers.append(Float8Linear.from_float(lin, cfg))
-        xs.append(torch.randn(M_TOKENS, k, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True))
-        gos.append(torch.randn(M_TOKENS, n, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3))
-    model = torch.nn.ModuleList(layers)
-
-    def step():
-        for layer, x, go in zip(layers, xs, gos):
-            x.grad = None
-            layer.weight.grad = None
-            layer(x).backward(go)
-        f8.sync_float8_amax_and_scale_history(model, layers)
-
-    for _ in range(3):
-        step()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    flops = sum(layer_flops(k, n) for _, k, n in SHAPES)
-    return {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps,
-            "workload": "the four linears with delayed scaling x3, fwd+bwd, one sync per step"}
-
-
-def measure_fused_norm(torch, dev, x):
-    """RMSNorm fused into the dynamic cast (two launches, 5 B per element: x read twice, fp8
-    written once) against the unfused sequence on the same [16384, 8192] bf16 activation: RMSNorm
-    in eager mode, then this library's amax and cast kernels."""
-    from float8_experimental_b200.float8_scaling_utils import hp_tensor_to_float8_dynamic
-    from float8_experimental_b200.float8_tensor import LinearMMConfig
-    from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic
-
-    w = torch.ones(x.shape[-1], device=dev, dtype=x.dtype)
-    cfg = LinearMMConfig()
-
-    def unfused():
-        xf = x.float()
-        y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(x) * w
-        return hp_tensor_to_float8_dynamic(y, torch.float8_e4m3fn, cfg)
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(20):
-            fn()
-        s1.record()
-        torch.cuda.synchronize()
-        return s0.elapsed_time(s1) / 20
-
-    fused_ms = timed(lambda: rms_norm_to_float8_dynamic(x, w, 1e-6))
-    unfused_ms = timed(unfused)
-    # SwiGLU gate of the LLaMa-2-70B FFN: a, b = halves of the fused w1|w3 output [16384, 57344]
-    from float8_experimental_b200.fused_norm import swiglu_to_float8_dynamic
-
-    h = torch.randn(x.shape[0], 57344, device=dev, dtype=x.dtype)
-    a, b = h[:, :28672], h[:, 28672:]
-    glu_ms = timed(lambda: swiglu_to_float8_dynamic(a, b))
-    glu_recompute_ms = timed(lambda: swiglu_to_float8_dynamic(a, b, recompute=True))
-    glu_unfused_ms = timed(lambda: hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, cfg))
-    # backward of the two producers (CUDA kernels) against eager autograd of the same formulas
-    from float8_experimental_b200._ops import ops
-
-    rstd, _ = ops.rmsnorm_amax(x, w, 1e-6)
-    gy = torch.randn_like(x)
-    norm_bwd_ms = timed(lambda: ops.rmsnorm_bwd(x, gy, w, rstd))
-
-    def eager_norm_bwd():
-        xr = x.detach().requires_grad_(True)
-        wr = w.detach().requires_grad_(True)
-        xf = xr.float()
-        ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(xr) * wr).backward(gy)
-
-    norm_bwd_eager_ms = timed(eager_norm_bwd)
-    gg = torch.randn(a.shape, device=dev, dtype=x.dtype)
-    glu_bwd_ms = timed(lambda: ops.swiglu_bwd(a, b, gg))
-
-    def eager_glu_bwd():
-        ar, br = a.detach().requires_grad_(True), b.detach().requires_grad_(True)
-        (torch.nn.functional.silu(ar) * br).backward(gg)
-
-    glu_bwd_eager_ms = timed(eager_glu_bwd)
-    backward = {"rmsnorm_bwd_ms": norm_bwd_ms, "rmsnorm_bwd_gbs": 6.0 * x.numel() / (norm_bwd_ms * 1e-3) / 1e9,
-                "rmsnorm_eager_fwd_bwd_ms": norm_bwd_eager_ms,
-                "swiglu_bwd_ms": glu_bwd_ms, "swiglu_bwd_gbs": 10.0 * a.numel() / (glu_bwd_ms * 1e-3) / 1e9,
-                "swiglu_eager_fwd_bwd_ms": glu_bwd_eager_ms}
-    return {"shape": list(x.shape), "backward": backward,
-            "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
-            "fused_bytes": "5 B per element: 2 read (1/rms + amax pass) + 2 read + 1 fp8 written (cast pass)",
-            "unfused_eager_norm_then_cast_ms": unfused_ms,
-            "swiglu": {"shape": list(a.shape), "fused_ms": glu_ms, "fused_gbs": 9.0 * a.numel() / (glu_ms * 1e-3) / 1e9,
-                       "fused_bytes": "9 B per element: a and b read, gate output written (4 + 2); read back and cast "
-                                      "(2 + 1)",
-                       "fused_recompute_ms": glu_recompute_ms,
-                       "unfused_eager_silu_mul_then_cast_ms": glu_unfused_ms}}
-
-
-def measure_ffn_fragment(torch, f8, dev):
-    """RMSNorm -> w1|w3 -> SwiGLU -> w2 with a residual, forward + backward, at the LLaMa-2-70B FFN
-    size (16384 tokens, 8192 -> 2 x 28672 -> 8192; the fragment of the reference's benchmark model):
-    the two producers fused into the casts of the float8 linears that follow them, against the
-    same float8 linears fed by eager RMSNorm and silu * mul."""
-    from float8_experimental_b200.float8_linear import Float8Linear
-    from float8_experimental_b200.fused_norm import rms_norm_to_float8_dynamic, swiglu_to_float8_dynamic
-
-    dim, hidden = 8192, 28672
-    gen = torch.Generator(device=dev).manual_seed(5)
-    mk = lambda i, o: Float8Linear.from_float(  # noqa: E731
-        torch.nn.Linear(i, o, bias=False, device=dev, dtype=torch.bfloat16), f8.Float8LinearConfig())
-    w13, w2 = mk(dim, 2 * hidden), mk(hidden, dim)
-    nw = torch.ones(dim, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    x = torch.randn(M_TOKENS, dim, device=dev, dtype=torch.bfloat16, generator=gen).requires_grad_(True)
-    go = torch.randn(M_TOKENS, dim, device=dev, dtype=torch.bfloat16, generator=gen).mul_(1e-3)
-
-    def fused():
-        h = w13(rms_norm_to_float8_dynamic(x, nw, 1e-6, linear_mm_config=w13.linear_mm_config))
-        y = x + w2(swiglu_to_float8_dynamic(h[:, :hidden], h[:, hidden:], linear_mm_config=w2.linear_mm_config))
-        y.backward(go)
-
-    def unfused():
-        xf = x.float()
-        n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).type_as(x) * nw
-        h = w13(n)
-        y = x + w2(torch.nn.functional.silu(h[:, :hidden]) * h[:, hidden:])
-        y.backward(go)
-
-    out = {"shape": {"tokens": M_TOKENS, "dim": dim, "hidden": hidden}}
-    for name, fn in (("fused_ms", fused), ("unfused_ms", unfused)):
-        for _ in range(2):
-            x.grad = nw.grad = w13.weight.grad = w2.weight.grad = None
-            fn()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(5):
-            x.grad = nw.grad = w13.weight.grad = w2.weight.grad = None
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        out[name] = e0.elapsed_time(e1) / 5
-    return out
 
 
 # ---------------------------------------------------------------------------
@@ -382,13 +276,23 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 
     import float8_experimental_b200 as f8
     from float8_experimental_b200 import _native
+    from float8_experimental_b200.benchmarks import multi_gpu, single_gpu
     from float8_experimental_b200.float8_linear import Float8Linear
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     _native.load()
+    parity_n = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # the sharded paths are checked on the real NCCL / CUDA route before anything is timed
+        parity_n = multi_gpu.run_parity(dev, rank, world)
+        if any(v != "ok" for v in parity_n.values()):
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "parity_n": parity_n,
+                                  "error": "multi-GPU parity check failed; nothing was timed"}), flush=True)
+            dist.destroy_process_group()
+            sys.exit(3)
 
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)  # activations differ per rank
     wgen = torch.Generator(device=dev).manual_seed(99)           # weights are the same everywhere
@@ -425,7 +329,9 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         from torch.distributed.fsdp import fully_shard
 
         for layer in layers:
-            fully_shard(layer)
+            # --fsdp-reshard 0 (default): the gathered fp8 weight (1 byte per element, 0.94 GB for the four
+            # layers) stays for the backward pass instead of being cast and all-gathered a second time
+            fully_shard(layer, reshard_after_forward=bool(args.fsdp_reshard))
         if args.fsdp_root:
             fully_shard(holder)
         f8.precompute_float8_dynamic_scale_for_fsdp(holder)
@@ -467,6 +373,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     barrier()
     _native.enable_kernel_events(False)
     clocks = sampler.stop() if rank == 0 else None
+    _native.check_device_error()  # a bounded wait that gave up inside a GEMM voids the run
     ms_total = e0.elapsed_time(e1)
     launches = _native.launch_count()
     kernel_ms = _native.kernel_event_totals()  # {"gemm": (ms, calls), "cast": ..., "amax": ...}
@@ -494,27 +401,49 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     h2d_bytes = sum(hx.numel() * 2 + hg.numel() * 2 for hx, hg in host)
     d2h_bytes = result_host.numel() * 2
 
+    x_ready, go_ready = [None] * len(layers), [None] * len(layers)
+    if fsdp:
+        # each layer's forward waits for its own input only (a pre-forward hook on the GPU stream),
+        # the backward for the gradients: the copies of later layers overlap the earlier layers' work
+        def _make_hook(i):
+            def hook(mod, inputs):
+                if x_ready[i] is not None:
+                    torch.cuda.current_stream().wait_event(x_ready[i])
+            return hook
+
+        hook_handles = [layer.register_forward_pre_hook(_make_hook(i)) for i, layer in enumerate(layers)]
+
     def e2e_step():
         main = torch.cuda.current_stream()
-        ready = []
         copy_stream.wait_stream(main)  # previous step's readers are done with the buffers
         with torch.cuda.stream(copy_stream):
-            for (hx, hg), x, go in zip(host, xs, gos):
+            for i, ((hx, _), x) in enumerate(zip(host, xs)):
                 x.detach().copy_(hx, non_blocking=True)
+                x_ready[i] = torch.cuda.Event()
+                x_ready[i].record(copy_stream)
+            for i, ((_, hg), go) in enumerate(zip(host, gos)):
                 go.copy_(hg, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(copy_stream)
-                ready.append(ev)
-        if fsdp:
-            for ev in ready:
+                go_ready[i] = torch.cuda.Event()
+                go_ready[i].record(copy_stream)
+        for layer, x in zip(layers, xs):
+            x.grad = None
+            layer.weight.grad = None
+        if fsdp and args.fsdp_root:
+            outs = holder(xs)
+            for ev in go_ready:
                 main.wait_event(ev)
-            step()
-        for i, (layer, x, go) in enumerate(zip(layers, xs, gos)):
-            if not fsdp:
-                main.wait_event(ready[i])
-                x.grad = None
-                layer.weight.grad = None
-                layer(x).backward(go)
+            torch.autograd.backward(outs, gos)
+            f8.precompute_float8_dynamic_scale_for_fsdp(holder)
+        else:
+            for i, (layer, x, go) in enumerate(zip(layers, xs, gos)):
+                if not fsdp:
+                    main.wait_event(x_ready[i])
+                y = layer(x)
+                main.wait_event(go_ready[i])
+                y.backward(go)
+            if fsdp:
+                f8.precompute_float8_dynamic_scale_for_fsdp(holder)
+        for i, layer in enumerate(layers):
             g = layer.weight.grad
             g = g.to_local() if hasattr(g, "to_local") else g  # FSDP2 hands out DTensor gradients
             result_host[i].copy_(g[0, :8], non_blocking=True)
@@ -533,46 +462,67 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = t.item()
     e2e_value = world * flops_per_step / e2e_s / 1e12
+    _native.check_device_error()
+    if fsdp:
+        for h in hook_handles:
+            h.remove()
+        x_ready = [None] * len(layers)
 
-    # ---- delayed-scaling side measurements (the delayed-scaling configuration: 320 linears, history 16), outside the timed region ----
-    # Side measurements never cost the headline line: a failure is recorded in their place.
-    def side(fn, *a):
+    # ---- side measurements, outside every timed region ----------------------
+    # They never cost the headline line: a failure is recorded in their place.
+    def side(fn, *a, **kw):
         try:
-            return fn(*a)
+            return fn(*a, **kw)
         except Exception as exc:  # noqa: BLE001
             torch.cuda.synchronize()
             return {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
-    delayed = None
-    if rank == 0 and world == 1:
-        delayed = side(measure_delayed, torch, f8, _native, dev, xs[0].detach())
-    fused_norm = None
-    if rank == 0 and world == 1 and shapes[0][1] == 8192:
-        fused_norm = side(measure_fused_norm, torch, dev, xs[0].detach())
-        if args.layers is None and "error" not in fused_norm:
-            fused_norm["ffn_fragment"] = side(measure_ffn_fragment, torch, f8, dev)
-
-    # ---- library kernel to beat, outside every timed region -----------------
-    cublaslt = None
-    if rank == 0:
-        try:
-            k, n = SHAPES[1][1], SHAPES[1][2]
-            a = torch.randn(M_TOKENS, k, device=dev).to(torch.float8_e4m3fn)
-            b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
-            one = torch.tensor(1.0, device=dev)
-            f = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, use_fast_accum=True)  # noqa: E731
+    delayed = fused_norm = gemm_vs_cublaslt = fp8_peak_measured = reference_gpu = None
+    comm_split = tp_sp_ffn = llama3_fsdp = cast_all_gather = None
+    full = args.layers is None and not args.quick
+    if world == 1 and rank == 0:
+        # the delayed-scaling configuration (320 linears, history 16) and the fused producers
+        delayed = side(single_gpu.measure_delayed, torch, f8, _native, dev, xs[0].detach())
+        if shapes[0][1] == 8192:
+            fused_norm = side(single_gpu.measure_fused_norm, torch, dev, xs[0].detach())
+            if full and "error" not in fused_norm:
+                fused_norm["ffn_fragment"] = side(single_gpu.measure_ffn_fragment, torch, f8, dev)
+    if world > 1 and full:
+        # where the N > 1 step spends its device time (all ranks run the steps, rank 0 profiles)
+        if rank == 0:
+            comm_split = side(multi_gpu.profile_step_split, step, dev)
+        else:
             for _ in range(3):
-                f()
-            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
-            for _ in range(10):
-                f()
-            s1.record()
+                step()
             torch.cuda.synchronize()
-            cublaslt = 2.0 * M_TOKENS * k * n / (s0.elapsed_time(s1) / 10 * 1e-3) / 1e12
-            del a, b
-        except Exception as e:  # pragma: no cover
-            cublaslt = f"unavailable: {e}"
+    # the headline tensors are not needed any more
+    del layers, holder, xs, gos, host
+    torch.cuda.empty_cache()
+    if rank == 0 and full:
+        # the library kernels to beat and the reference's own GPU operator sequence
+        fp8_peak_measured = side(single_gpu.measure_fp8_peak, torch, dev)
+        if world == 1:
+            gemm_vs_cublaslt = side(single_gpu.measure_gemm_vs_cublaslt)
+            ref_linear = None
+            try:
+                if reference_package() is not None:
+                    from float8_experimental.config import Float8LinearConfig as RefConfig
+                    from float8_experimental.float8_linear import Float8Linear as RefLinear
+
+                    ref_linear = lambda lin: RefLinear.from_float(lin, RefConfig())  # noqa: E731
+            except Exception:  # noqa: BLE001
+                ref_linear = None
+            reference_gpu = side(single_gpu.measure_reference_gpu_path, torch, dev, 5, ref_linear)
+            if ref_linear is not None and "error" in reference_gpu:
+                first_error = reference_gpu["error"]
+                reference_gpu = side(single_gpu.measure_reference_gpu_path, torch, dev, 5, None)
+                reference_gpu["reference_module_error"] = first_error
+    if world > 1 and full:
+        # the tensor / sequence parallel and the Llama-3-8B FSDP2 configurations (all ranks take part)
+        tp_sp_ffn = side(multi_gpu.measure_tp_sp_ffn, dev, rank, world)
+        cast_all_gather = side(multi_gpu.measure_cast_all_gather, dev, rank, world)
+        llama3_fsdp = side(multi_gpu.measure_fsdp2_llama3_8b_linears, dev, rank, world)
+        _native.check_device_error()
 
     if rank != 0:
         if world > 1:
@@ -585,7 +535,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     amax_ms, amax_calls = kernel_ms.get("amax", (0.0, 0))
     gemm_flops = args.steps * flops_per_step
     gemm_tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]  # proxy: MEASURED_PEAKS holds no fp8 figure
+    fp8_lib = fp8_peak_measured if isinstance(fp8_peak_measured, float) else None
     # dynamic amax+cast of n bf16 elements: 2n (amax read) + 2n (cast read) + n (fp8) bytes, + n when the
     # transposed copy is emitted too (F8B200_CAST_TRANSPOSED=1; off by default: the GEMMs read
     # operands in either memory order).  Under FSDP2 each rank casts 1/world of every weight and
@@ -594,18 +545,30 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     act_elems = sum(M_TOKENS * k + M_TOKENS * n for _, k, n in shapes)
     w_elems = sum(n * k for _, k, n in shapes)
     cast_bytes = args.steps * (per_elem * act_elems + (5.0 * w_elems / world if fsdp else per_elem * w_elems))
-    if fsdp and args.fsdp_root:
-        # non-root FSDP2 modules reshard after forward: the shard is cast again for the backward all-gather
+    if fsdp and args.fsdp_root and args.fsdp_reshard:
+        # resharding after forward: the shard is cast again for the backward all-gather
         cast_bytes += args.steps * 3.0 * w_elems / world
     cast_gbs = cast_bytes / ((cast_ms + amax_ms) * 1e-3) / 1e9 if (cast_ms + amax_ms) > 0 else None
 
-    # bounded CPU sample (rank 0, N = 1 only)
+    # which GEMM kernel the library chose for the products of the step, and its DRAM traffic
+    products = single_gpu.gemm_products(shapes)
+    chosen = [_native.gemm_kernel_choice(m, n, k) for _, m, n, k, _ in products]
+    gemm_kernel_desc = ", ".join(f"{GEMM_KERNEL_NAMES[c]} x{chosen.count(c)}" for c in sorted(set(chosen))) + \
+        "; tcgen05.mma kind::f8f6f4, TMA loads and stores, fp32 accumulators in tensor memory"
+    known = [GEMM_DRAM_TRAFFIC.get(GEMM_KERNEL_SHORT[c], {}).get(name) for c, (name, *_r) in zip(chosen, products)]
+    traffic = sum(r + w for r, w in known) / len(known) if known and all(t is not None for t in known) else None
+    traffic_algo = sum(m * k + n * k + 2.0 * m * n for _, m, n, k, _ in products) / len(products)
+    traffic_src = ("mean over the GEMM launches of one step of ncu dram__bytes_read.sum + dram__bytes_write.sum per "
+                   "launch, one capture per product, for the kernel each product ran on" if traffic is not None else
+                   "no capture for this kernel choice")
+
+    # bounded CPU sample (rank 0, N = 1 only): the reference's emulate=True path on the host cores
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        sample = make_cpu_sample()
-        ts = time_cpu(sample, 6, 1)
-        cpu_baseline = {"value": sample["flops"] / min(ts) / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
-                        "kind": "port", "sample": sample["desc"]}
+        try:
+            cpu_baseline = time_cpu_arm(4, 1, extras=full)
+        except Exception as exc:  # noqa: BLE001
+            cpu_baseline = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -617,10 +580,11 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "shapes_KN": {name: [k, n] for name, k, n in shapes},
             "l2": "inputs larger than L2 (smallest tensor cast per layer is 134 MB; L2 is 126 MB)",
             "parallelism": (f"fsdp2 x{world}: " + (
-                "one root, fp8 weight all-gather (1 B/elem) before forward and again before backward, "
-                if args.fsdp_root else
-                "each layer its own FSDP2 root (a root keeps its gathered weight for backward): one fp8 weight "
-                "all-gather (1 B/elem) per layer and step, ") + "bf16 grad reduce-scatter, one amax all-reduce per step")
+                "one root, " if args.fsdp_root else "each layer its own FSDP2 root, ") + (
+                "fp8 weight all-gather (1 B/elem) before forward and again before backward, "
+                if (args.fsdp_root and args.fsdp_reshard) else
+                "one fp8 weight all-gather (1 B/elem) per layer and step (the gathered fp8 weight is kept for backward), ")
+                + "bf16 grad reduce-scatter, one amax all-reduce per step")
             if fsdp else "single GPU",
         },
         "clocks": clocks,
@@ -628,24 +592,22 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                 "ms_per_step": e2e_s * 1e3},
         "gpu_launches": launches,
         "roofline": {
-            "kernel": ("gemm_fp8_pair_kernel (K < 16384; tcgen05.mma.cta_group::2) + " +
-                       ("gemm_fp8_mc_kernel (K >= 16384; 2x1 clusters of 256x256 tiles, B multicast)"
-                        if _native._mc_cluster(16384, 8192, 16384) is not None else
-                        "gemm_fp8_wide_kernel (K >= 16384; cta_group::1, 256x256 per CTA)") + ", kind::f8f6f4"),
+            "kernel": gemm_kernel_desc,
             "bound": "tensor", "achieved": gemm_tflops,
             "peak": fp8_peak, "unit": "TFLOP/s", "frac": (gemm_tflops / fp8_peak) if gemm_tflops else None,
-            "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (fp8 issues at twice the bf16 rate)",
+            "peak_source": f"PROXY: 2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (no fp8 figure is "
+                           "recorded there; tcgen05 issues fp8 at twice the bf16 rate)",
+            "peak_fp8_measured": fp8_lib,
+            "peak_fp8_measured_how": "torch._scaled_mm (cuBLASLt) 8192^3 e4m3 x e4m3 -> bf16, back to back for 2 s, this "
+                                     "run, outside the timed region",
+            "frac_of_peak_fp8_measured": (gemm_tflops / fp8_lib) if (gemm_tflops and fp8_lib) else None,
             "frac_of_nominal_4500": (gemm_tflops / NOMINAL_FP8_TFLOPS) if gemm_tflops else None,
             "launches": gemm_calls,
-            # dram__bytes_read + dram__bytes_write per launch, mean of the three GEMMs of the wo layer (fwd and dgrad
-            # 16384x8192x8192 on the pair kernel, wgrad 8192x8192x16384 on the multicast kernel; 0.881 GB read on the wide kernel), from the ncu captures
-            # summarised in profiles/gemm_fp8_pair_kernel_wo_16384x8192x8192.md and
-            # profiles/gemm_fp8_wide_kernel_wo_w2_w13.md
-            "traffic": (0.346e9 + 0.249e9 + 0.425e9 + 0.249e9 + 0.820e9 + 0.120e9) / 3,
-            "traffic_algorithmic": (2 * (201.3e6 + 268.4e6) + (268.4e6 + 134.2e6)) / 3,
+            "traffic": traffic, "traffic_algorithmic": traffic_algo, "traffic_source": traffic_src,
         },
         "roofline_cast": {
-            "kernel": "amax_flat_kernel + cast_tile8_kernel (dynamic amax+cast with transposed copy)", "bound": "hbm",
+            "kernel": "amax_flat_kernel + cast_tile8_kernel (dynamic amax + cast" +
+                      (", with the transposed copy)" if TRANSPOSED_COPIES else ", no transposed copy)"), "bound": "hbm",
             "achieved": cast_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": (cast_gbs / peaks["hbm_gbs"]) if cast_gbs else None,
             "frac_of_nominal_8000": (cast_gbs / NOMINAL_HBM_GBS) if cast_gbs else None,
@@ -653,79 +615,41 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                                   if TRANSPOSED_COPIES else
                                   "5 bytes per bf16 element (2 amax read + 2 cast read + 1 fp8; no transposed copy)"),
             "launches": cast_calls + amax_calls,
-            # one 16384x8192 bf16 tensor, amax + cast launches, from profiles/cast_tile8_kernel_16384x8192_bf16.md
-            "traffic": 268.4e6 + 268.5e6 + (211.9e6 if TRANSPOSED_COPIES else CAST_WRITE_TRAFFIC_1COPY),
+            "traffic": sum(CAST_DRAM_TRAFFIC["transposed" if TRANSPOSED_COPIES else "plain"]),
             "traffic_algorithmic": (6 if TRANSPOSED_COPIES else 5) * 134.2e6,
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the amax and the cast launch on one "
+                              "16384 x 8192 bf16 tensor",
         },
         "time_share_ms_per_step": {"gemm": gemm_ms / args.steps, "cast": cast_ms / args.steps,
                                    "amax": amax_ms / args.steps},
-        "cublaslt_fp8_tflops_wo_fwd": cublaslt,
+        "gemm_vs_cublaslt": gemm_vs_cublaslt,
+        "reference_gpu_path": reference_gpu,
+        "vs_reference_gpu_path": (reference_gpu["ms_per_step"] / ms_per_step
+                                  if isinstance(reference_gpu, dict) and "ms_per_step" in reference_gpu else None),
         "delayed_scaling": delayed,
         "fused_rmsnorm_cast": fused_norm,
         "cpu_baseline": cpu_baseline,
     }
+    if world > 1:
+        line["parity_n"] = parity_n
+        line["step_split_ms"] = comm_split
+        line["tp_sp_ffn"] = tp_sp_ffn
+        line["cast_all_gather"] = cast_all_gather
+        line["fsdp2_llama3_8b_linears"] = llama3_fsdp
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
 def run_gemm_sweep(args):
-    """Sustained per-shape comparison of GEMM variants in ONE process (box-to-box variation is
-    larger than the differences between variants): every GEMM of the step runs for ~0.6 s with
-    each variant in turn.  Variants: 2cta, 1cta, wide (kernels of libf8b200.so), mc21 / mc22 / mc41
-    (the single-GPU multicast library: wide tiles in 2x1 / 2x2 clusters, two CTA pairs), auto (the default choice), cublaslt (torch._scaled_mm);
-    suffix -static = fixed tile stride, -direct = per-thread store epilogue."""
-    import torch
-
+    """`--gemm-sweep v1,v2,...`: sustained per-shape comparison of GEMM variants in one process
+    (`benchmarks.single_gpu.gemm_sweep`); one JSON line per GEMM, then the totals."""
     from float8_experimental_b200 import _native as N
+    from float8_experimental_b200.benchmarks import single_gpu
 
-    dev = torch.device("cuda", 0)
-    variants = args.gemm_sweep.split(",")
     shapes = [s for s in SHAPES if args.layers is None or s[0] in args.layers.split(",")]
-    one = torch.tensor(1.0, device=dev)
-    rows, totals = [], {v: 0.0 for v in variants}
-
-    def sustained(fn, seconds=0.6):
-        fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); fn(); e1.record(); torch.cuda.synchronize()
-        iters = max(3, int(seconds * 1e3 / e0.elapsed_time(e1)))
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters
-
-    for name, k_in, n_out in shapes:
-        for tag, m, n, k, a_dt in ((".fwd", M_TOKENS, n_out, k_in, torch.float8_e4m3fn),
-                                   (".dgrad", M_TOKENS, k_in, n_out, torch.float8_e5m2),
-                                   (".wgrad", n_out, k_in, M_TOKENS, torch.float8_e5m2)):
-            a = torch.randn(m, k, device=dev).to(a_dt)
-            b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
-            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-            row = {"gemm": name + tag, "m": m, "n": n, "k": k}
-            for v in variants:
-                if v == "cublaslt":
-                    fn = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
-                else:
-                    base = v.split("-")[0]
-                    os.environ["F8B200_GEMM_MC"] = base[2:] if base.startswith("mc") else "0"
-                    os.environ["F8B200_GEMM_MODE"] = "" if base in ("auto", "mc21", "mc22", "mc41") else base
-                    os.environ["F8B200_GEMM_STORE"] = "direct" if v.endswith("-direct") else "tma"
-                    os.environ["F8B200_GEMM_WS"] = "0" if v.endswith("-static") else "1"
-                    if base == "auto":
-                        os.environ.pop("F8B200_GEMM_MC", None)
-                    fn = lambda: N.gemm_fp8(a, k, b, k, one, one, None, out, n, m, n, k, False)  # noqa: E731
-                ms = sustained(fn)
-                totals[v] += ms
-                row[v] = {"ms": round(ms, 4), "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}
-            rows.append(row)
-            print(json.dumps(row), flush=True)
-            del a, b, out
-    print(json.dumps({"gemm_sweep_totals_ms": {v: round(t, 3) for v, t in totals.items()},
-                      "device_error": N.read_device_error()}), flush=True)
+    _, totals = single_gpu.gemm_sweep(args.gemm_sweep.split(","), shapes, emit=lambda row: print(json.dumps(row), flush=True))
+    print(json.dumps({"gemm_sweep_totals_ms": totals, "device_error": N.read_device_error()}), flush=True)
 
 
 def main():
@@ -741,7 +665,13 @@ def main():
                          "every weight is cast and all-gathered before forward and again before backward, and the "
                          "next layer's all-gather is prefetched under the current layer's GEMMs); 0 = each layer is "
                          "its own root (a root keeps its gathered weight: one all-gather per layer and step, nothing "
-                         "overlaps).  Measured at N=8: 41.0 against 41.2 ms/step.")
+                         "overlaps)")
+    ap.add_argument("--fsdp-reshard", type=int, default=0,
+                    help="N > 1: 1 = layers free their gathered fp8 weight after forward and gather it again before "
+                         "backward (FSDP2's default for non-root modules); 0 = they keep it until backward")
+    ap.add_argument("--quick", action="store_true",
+                    help="headline numbers only: skip the side measurements that need extra seconds (GEMM comparison "
+                         "with cuBLASLt, the reference's GPU path, the multi-GPU side configurations)")
     ap.add_argument("--gemm-sweep", default=None,
                     help="comma list of GEMM variants to compare per shape in one process (see run_gemm_sweep); "
                          "prints one JSON line per GEMM and the totals, then exits")
@@ -755,7 +685,9 @@ def main():
         run_gemm_sweep(args)
         return
     if args.impl == "reference":
-        run_reference_arm(args, rank, world)
+        if rank == 0:
+            use_all_host_threads()  # before numpy / torch load their thread pools
+            run_reference_arm(args, rank, world)
         return
     if args.warmup < 3 and not args.kernel_only:
         args.warmup = 3

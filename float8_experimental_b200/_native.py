@@ -36,6 +36,9 @@ EXPORTS = (
     "f8b200_gemm_fp8",
     "f8b200_gemm_fp8_ws",
     "f8b200_gemm_fp8_static_scratch",
+    "f8b200_gemm_kernel_choice",
+    "f8b200_gemm_fp8_scatter_rows",
+    "f8b200_sum_slots",
     "f8b200_rmsnorm_amax",
     "f8b200_rmsnorm_cast",
     "f8b200_swiglu_amax",
@@ -95,6 +98,10 @@ def load() -> ctypes.CDLL:
     lib.f8b200_swiglu_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     lib.f8b200_check_device_error.argtypes = []
+    lib.f8b200_gemm_kernel_choice.argtypes = [i64, i64, i64]
+    lib.f8b200_gemm_fp8_scatter_rows.argtypes = [vp, i32, i32, i64, vp, i32, i32, i64, vp, vp, vp, i32, ctypes.POINTER(vp),
+                                                 i32, i64, i64, i64, i64, i64, vp, i64, vp]
+    lib.f8b200_sum_slots.argtypes = [vp, i32, i64, i32, i64, vp, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is not ctypes.c_char_p and fn.restype is not i64:
@@ -315,25 +322,18 @@ def _single_gpu_job() -> bool:
 
 def _mc_cluster(m: int, n: int, k: int):
     """Cluster shape (tiles along M, along N) of the multicast GEMM for this product, or None
-    to use the kernels of libf8b200.so.  Only jobs on a single GPU use it (`_single_gpu_job`; the
-    C entry point checks on its side that every pointer is the current device's own memory), and
-    by default only where it measured faster: K >= 16384 (the products that otherwise run on the
-    wide kernel), 2 x 1 clusters (+1 to +4 % sustained; 2 x 2 clusters measured slower than 2 x 1).
-    F8B200_GEMM_MC=0 switches it off, =21 / =22 force a shape for every product; forcing a
-    kernel with F8B200_GEMM_MODE switches it off as well."""
-    mode = os.environ.get("F8B200_GEMM_MC", "auto")
-    if mode == "0" or not _single_gpu_job() or load_mc() is None:
+    to use the kernels of libf8b200.so.  Opt-in: F8B200_GEMM_MC=21 / 22 / 41 select 2 x 1 or
+    2 x 2 clusters of 256x256 tiles, or two CTA pairs sharing B; by default (and with
+    F8B200_GEMM_MC=0, or when F8B200_GEMM_MODE forces a kernel) nothing uses it, because the
+    512x256 pair kernel of libf8b200.so measured faster on every product.  Only jobs on a single
+    GPU may use it at all (`_single_gpu_job`; the C entry point checks on its side that every
+    pointer is the current device's own memory)."""
+    mode = os.environ.get("F8B200_GEMM_MC", "0")
+    if mode not in ("21", "22", "41") or not _single_gpu_job() or load_mc() is None:
         return None
-    if mode == "21":
-        return (2, 1)
-    if mode == "22":
-        return (2, 2)
-    if mode == "41":  # two CTA pairs sharing B; K-major operands only (others fall back)
-        return (4, 1)
-    forced = os.environ.get("F8B200_GEMM_MODE", "")
-    if forced[:1] in ("1", "2", "w", "p"):
+    if os.environ.get("F8B200_GEMM_MODE", "")[:1] in ("1", "2", "w", "p"):
         return None
-    return (2, 1) if k >= int(os.environ.get("F8B200_GEMM_WIDE_K", "16384")) else None
+    return {"21": (2, 1), "22": (2, 2), "41": (4, 1)}[mode]
 
 
 GEMM_WORKSPACE_BYTES = 256  # F8B200_GEMM_WORKSPACE_BYTES in include/f8b200.h
@@ -388,6 +388,41 @@ def gemm_fp8(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torc
                                           n, k, int(use_fast_accum), ws.data_ptr(), ws.numel(), stream),
                 "f8b200_gemm_fp8_ws",
             )
+
+
+def gemm_fp8_scatter_rows(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor,
+                          scale_b: torch.Tensor, out_dtype: torch.dtype, out_ptrs: Sequence[int], rows_per_block: int,
+                          ldo: int, m: int, n: int, k: int, a_mn_major: bool = False, b_mn_major: bool = False) -> None:
+    """`f8b200_gemm_fp8_scatter_rows`: the GEMM whose output row blocks go round-robin to the
+    addresses in `out_ptrs` (this device's own buffer and peer-mapped buffers of other devices)."""
+    _require_cuda(a, b, scale_a, scale_b)
+    stream = _stream(a)
+    ws = _gemm_workspace(a.device, stream)
+    arr = (ctypes.c_void_p * len(out_ptrs))(*[ctypes.c_void_p(p) for p in out_ptrs])
+    with _Launch("gemm", a.device):
+        _check(
+            load().f8b200_gemm_fp8_scatter_rows(a.data_ptr(), fp8_code(a.dtype), int(a_mn_major), lda, b.data_ptr(),
+                                                fp8_code(b.dtype), int(b_mn_major), ldb, scale_a.data_ptr(),
+                                                scale_b.data_ptr(), None, hp_code(out_dtype), arr, len(out_ptrs),
+                                                rows_per_block, ldo, m, n, k, ws.data_ptr(), ws.numel(), stream),
+            "f8b200_gemm_fp8_scatter_rows",
+        )
+
+
+def sum_slots(slots: torch.Tensor, n_slots: int, slot_stride: int, numel: int, out: torch.Tensor) -> None:
+    """`f8b200_sum_slots`: out = sum of the first `n_slots` slots of `slots` (fp32 accumulation)."""
+    _require_cuda(slots, out)
+    with _Launch("sum_slots", out.device):
+        _check(
+            load().f8b200_sum_slots(slots.data_ptr(), n_slots, slot_stride, hp_code(out.dtype), numel, out.data_ptr(),
+                                    _stream(out)),
+            "f8b200_sum_slots",
+        )
+
+
+def gemm_kernel_choice(m: int, n: int, k: int) -> int:
+    """Code of the kernel the library would run for this product (see include/f8b200.h)."""
+    return int(load().f8b200_gemm_kernel_choice(m, n, k))
 
 
 def gemm_fp8_static_scratch(a: torch.Tensor, lda: int, b: torch.Tensor, ldb: int, scale_a: torch.Tensor,

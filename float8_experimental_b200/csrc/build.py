@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libf8b200.so")
-SOURCES = ["capi.cu", "cast.cu", "gemm.cu", "norm.cu"]
+SOURCES = ["capi.cu", "cast.cu", "gemm.cu", "norm.cu", "reduce.cu"]
 # Single-GPU extra: the cluster-multicast GEMM lives in a library of its own, so that runs on
 # several GPUs can leave its source and binary out altogether (it includes gemm.cu).
 MC_LIB_PATH = os.path.join(LIB_DIR, "libf8b200_mc.so")

@@ -1,10 +1,12 @@
 // Scaled fp8 GEMM for sm_100a:  out[M,N] = (A[M,K] . B[N,K]^T) / (sa * sb) (+ bias).
 //
-// Three persistent, warp-specialised kernels share the device code of this file:
-//   pair kernel   (namespace pair, default for K < 16384) two CTAs per 256x256 tile,
+// Four persistent, warp-specialised kernels share the device code of this file:
+//   pair-wide kernel (namespace pairwide, the default) two CTAs per 512x256 tile, two
+//                 tcgen05.mma.cta_group::2 per k-step, one 256x256 accumulator per CTA drained by halves;
+//   pair kernel   (namespace pair, default for at most 256 rows) two CTAs per 256x256 tile,
 //                 tcgen05.mma.cta_group::2, accumulators double buffered in tensor memory;
-//   wide kernel   (namespace wide, default for K >= 16384) one CTA per 256x256 tile, two
-//                 M128 N256 MMAs per k-step, the accumulator fills tensor memory;
+//   wide kernel   (namespace wide) one CTA per 256x256 tile, two M128 N256 MMAs per k-step, the
+//                 accumulator fills tensor memory;
 //   one-CTA kernel (below) one CTA per 128x256 tile; kept as the simplest reference of the scheme.
 // Each operand is fp8 bytes, K-major (storage [rows, K]) or MN-major (storage [K, rows]).
 // Tiles are walked in L2-friendly bands, with a fixed stride per CTA or claimed from a counter
@@ -313,6 +315,26 @@ __device__ __forceinline__ void bulk_wait_read() {
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Row scatter of the output (used by the GEMM whose epilogue is the first half of a reduce-scatter):
+// output row i belongs to block i / rows_per_block; blocks go round-robin to the n destinations, so
+// row i lands in destination (block % n) at row (block / n) * rows_per_block + i % rows_per_block.
+// The destinations may be buffers of other GPUs mapped into this process (plain stores over NVLink).
+constexpr int MAX_SCATTER = 16;
+struct RowScatter {
+  void* base[MAX_SCATTER];
+  int n;
+  int rows_per_block;
+};
+struct NoScatter {};
+
+template <typename OutT>
+__device__ __forceinline__ OutT* scatter_row_ptr(const RowScatter& sc, int row, int64_t ldo) {
+  const int blk = row / sc.rows_per_block;
+  const int within = row - blk * sc.rows_per_block;
+  const int owner = blk % sc.n;
+  return static_cast<OutT*>(sc.base[owner]) + ((int64_t)(blk / sc.n) * sc.rows_per_block + within) * ldo;
+}
+
 template <typename OutT>
 struct EpilogueArgs {
   const OutT* bias;
@@ -325,6 +347,7 @@ struct EpilogueArgs {
   uint8_t* staging;  // this warp's two boxes, 1024-byte aligned
   float inv;
   int store_evict_first;  // the output is not read again by this kernel: do not let it displace operands in L2
+  const RowScatter* scatter;  // rows go to several destinations (direct-store path only); null = `out`
 };
 
 // Drains `ncol_total` accumulator columns starting at TMEM address `taddr` for the 32
@@ -622,7 +645,10 @@ __device__ __forceinline__ void drain_accumulator_1box(const EpilogueArgs<OutT>&
         if (i < ncols) v[i] += static_cast<float>(e.bias[col + i]);
     }
     if (!e.use_tma) {
-      if (row < e.m && ncols > 0) store_chunk<OutT>(e.out + (int64_t)row * e.ldo + col, v, ncols, e.out_vec_ok != 0);
+      if (row < e.m && ncols > 0) {
+        OutT* dst = e.scatter != nullptr ? scatter_row_ptr<OutT>(*e.scatter, row, e.ldo) : e.out + (int64_t)row * e.ldo;
+        store_chunk<OutT>(dst + col, v, ncols, e.out_vec_ok != 0);
+      }
       continue;
     }
     const int sub = c % CHUNKS_PER_BOX;
@@ -1297,13 +1323,14 @@ struct __align__(8) QBarriers {
 
 constexpr int QSMEM_BYTES = QSTAGES * QSTAGE_BYTES + 8 * EPI_BOX_BYTES + 1024 + (int)sizeof(QBarriers);
 
-template <typename OutT>
+template <typename OutT, bool SCATTER = false>
 __global__ void __launch_bounds__(QTHREADS, 1)
 gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_out, const float* __restrict__ scale_a,
                          const float* __restrict__ scale_b, const OutT* __restrict__ bias, OutT* __restrict__ out,
                          int64_t ldo, int m, int n, int k, uint32_t idesc, int out_vec_ok, int use_tma_store,
-                         int raster, uint32_t* sched) {
+                         int raster, uint32_t* sched,
+                         const __grid_constant__ std::conditional_t<SCATTER, RowScatter, NoScatter> scatter) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = tiles + QSTAGES * QSTAGE_BYTES;
@@ -1478,8 +1505,10 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const float sa = __ldg(scale_a), sb = __ldg(scale_b);
       inv = __fmul_rn(__fdiv_rn(1.0f, sa), __fdiv_rn(1.0f, sb));
     }
+    const RowScatter* sc = nullptr;
+    if constexpr (SCATTER) sc = &scatter;
     const EpilogueArgs<OutT> ea{bias, out, ldo, m, n, out_vec_ok, use_tma_store, &tma_out,
-                                staging + (warp - 2) * EPI_BOX_BYTES, inv, (raster >> 20) & 1};
+                                staging + (warp - 2) * EPI_BOX_BYTES, inv, (raster >> 20) & 1, sc};
     uint32_t boxes = 0;
     bool ok = true;
     int64_t local = 0;
@@ -1738,13 +1767,14 @@ static int launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   return check_launch();
 }
 
-template <typename OutT>
+template <typename OutT, bool SCATTER = false>
 static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                            const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n,
-                           int k, uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st) {
+                           int k, uint32_t idesc, int vec_ok, int layouts, uint32_t* sched, cudaStream_t st,
+                           const std::conditional_t<SCATTER, RowScatter, NoScatter>& scatter = {}) {
   static PerDeviceOnce setup;  // shared-memory opt-in and cluster occupancy, once per device
   int max_clusters = 0;
-  auto kernel = pairwide::gemm_fp8_pairwide_kernel<OutT>;
+  auto kernel = pairwide::gemm_fp8_pairwide_kernel<OutT, SCATTER>;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1786,27 +1816,28 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
     if (e[0] == '0') split = 0;
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
-                         choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched));
+                         choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched, scatter));
 }
 
-// Kernel choice: 0 = one CTA per 128x256 tile, 1 = CTA pairs (256x256, cta_group::2), 2 = one CTA per 256x256 tile.
-// The pair kernel hides its epilogue behind the next tile's MMAs (two accumulators in tensor memory) but its MMAs
-// read half of B from the peer's shared memory; the wide kernel reads only its own shared memory but drains its
-// single 256x256 accumulator with the tensor pipe idle.  That drain is a fixed cost per tile, so the wide kernel
-// wins once the K loop is long enough to amortise it: measured under sustained load the two tie at K = 16384, the
-// pair kernel is 4-6 % faster at K = 8192 and the wide kernel 3-8 % faster at K >= 28672.
-// F8B200_GEMM_MODE ("1cta" / "2cta" / "wide") forces one kernel and F8B200_GEMM_WIDE_K moves the threshold; both are
-// read at every call so that tests can exercise every kernel in one process.
-static int gemm_mode(int64_t k) {
+// Kernel choice: 0 = one CTA per 128x256 tile, 1 = CTA pairs on 256x256 tiles (cta_group::2, two accumulators),
+// 2 = one CTA per 256x256 tile, 3 = CTA pairs on 512x256 tiles (cta_group::2, one 256x256 accumulator per CTA).
+// Default: kernel 3 whenever the problem has more than 256 rows.  It moves 25 % fewer operand bytes from L2 per
+// flop than the others (48 KB per k-block for 256x256 of output against 64 KB), which on a power-capped part is
+// worth more than the fully hidden epilogue of kernel 1, and its split accumulator drain hides half of its own:
+// sustained over the twelve GEMMs of the LLaMa-2-70B step it measured 33.6 ms against 35.1 ms for kernel 1 alone
+// and 34.1 ms for the earlier rule (kernel 1 for K < 16384, kernel 2 above), ahead on every shape.  With at most
+// 256 rows a 512-row tile would be half empty: kernel 1.
+// F8B200_GEMM_MODE ("1cta" / "2cta" / "wide" / "pw") forces one kernel; F8B200_GEMM_WIDE_K=<k> restores the earlier
+// rule with that threshold.  Both are read at every call so that tests can exercise every kernel in one process.
+static int gemm_mode(int64_t m, int64_t k) {
   const char* e = getenv("F8B200_GEMM_MODE");
   if (e != nullptr && e[0] == '1') return 0;
   if (e != nullptr && e[0] == '2') return 1;
   if (e != nullptr && e[0] == 'w') return 2;
   if (e != nullptr && e[0] == 'p') return 3;
-  int64_t wide_k = 16384;
   const char* t = getenv("F8B200_GEMM_WIDE_K");
-  if (t != nullptr && t[0] != 0) wide_k = atoll(t);
-  return k >= wide_k ? 2 : 1;
+  if (t != nullptr && t[0] != 0) return k >= atoll(t) ? 2 : 1;
+  return m > 256 ? 3 : 1;
 }
 
 }  // namespace gemm
@@ -1886,7 +1917,7 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
     return b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb)
                     : gemm::encode_operand_map(&mb, b, n, k, ldb, box_rows_b > 0 ? box_rows_b : box_rows);
   };
-  int mode = gemm::gemm_mode(k);
+  int mode = gemm::gemm_mode(m, k);
   if (mode == 3) {
     // CTA pairs on 512x256 tiles: each CTA fetches a 256-row box of A and a 128-row box of B
     rc = encode_operands(256, 128);
@@ -2031,6 +2062,52 @@ extern "C" int f8b200_read_device_error(uint32_t* flags_out) {
   rc = record_cuda_error(cudaMemcpyToSymbol(g_device_error, &zero, sizeof(zero)));
   *flags_out = v;
   return rc;
+}
+
+extern "C" int f8b200_gemm_fp8_scatter_rows(const void* a, int a_kind, int a_layout, int64_t lda, const void* b,
+                                            int b_kind, int b_layout, int64_t ldb, const float* scale_a,
+                                            const float* scale_b, const void* bias, int out_dtype, void* const* outs,
+                                            int n_outs, int64_t rows_per_block, int64_t ldo, int64_t m, int64_t n,
+                                            int64_t k, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (outs == nullptr || n_outs < 1 || n_outs > gemm::MAX_SCATTER || rows_per_block < 1) return F8B200_ERR_BAD_ARG;
+  for (int i = 0; i < n_outs; ++i)
+    if (outs[i] == nullptr) return F8B200_ERR_BAD_ARG;
+  if (m % (rows_per_block * n_outs) != 0 || rows_per_block > 0x7FFFFFFFLL) return F8B200_ERR_BAD_ARG;
+  if (workspace != nullptr && (workspace_bytes < F8B200_GEMM_WORKSPACE_BYTES || reinterpret_cast<uintptr_t>(workspace) % 16 != 0))
+    return F8B200_ERR_BAD_ARG;
+  bool empty = false;
+  int rc = gemm_fp8_validate(a, a_kind, a_layout, lda, b, b_kind, b_layout, ldb, scale_a, scale_b, bias, out_dtype, outs[0],
+                             ldo, m, n, k, &empty);
+  if (rc != F8B200_OK || empty) return rc;
+  const int osz = out_dtype == F8B200_FP32 ? 4 : 2;
+  int vec_ok = (ldo * osz) % 16 == 0;
+  gemm::RowScatter sc = {};
+  sc.n = n_outs;
+  sc.rows_per_block = (int)rows_per_block;
+  for (int i = 0; i < n_outs; ++i) {
+    sc.base[i] = outs[i];
+    if (reinterpret_cast<uintptr_t>(outs[i]) % osz != 0) return F8B200_ERR_ALIGNMENT;
+    if (reinterpret_cast<uintptr_t>(outs[i]) % 16 != 0) vec_ok = 0;
+  }
+  CUtensorMap ma, mb, mo;
+  memset(&mo, 0, sizeof(mo));  // the scattered output is written with per-thread stores, not by TMA
+  rc = a_layout ? gemm::encode_operand_map_mn(&ma, a, m, k, lda) : gemm::encode_operand_map(&ma, a, m, k, lda, 256);
+  if (rc != F8B200_OK) return rc;
+  rc = b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb) : gemm::encode_operand_map(&mb, b, n, k, ldb, 128);
+  if (rc != F8B200_OK) return rc;
+  const int layouts = (a_layout << gemm::LAYOUT_A_MN_BIT) | (b_layout << gemm::LAYOUT_B_MN_BIT);
+  const uint32_t idq = gemm::pair::make_idesc_pair(a_kind, b_kind, a_layout, b_layout);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dispatch_out_dtype(out_dtype, [&](auto* tag) {
+    using OutT = std::remove_pointer_t<decltype(tag)>;
+    return gemm::launch_pairwide<OutT, true>(ma, mb, mo, 0, scale_a, scale_b, bias, outs[0], ldo, (int)m, (int)n, (int)k,
+                                             idq, vec_ok, layouts, static_cast<uint32_t*>(workspace), st, sc);
+  });
+}
+
+extern "C" int f8b200_gemm_kernel_choice(int64_t m, int64_t n, int64_t k) {
+  (void)n;
+  return gemm::gemm_mode(m, k);
 }
 
 extern "C" int f8b200_check_device_error(void) {

@@ -85,6 +85,8 @@ class Float8Linear(torch.nn.Linear):
         self.amax_and_scale_synced = not config.enable_amax_init
         self.last_seen_input_dtype = None
         self.enable_pre_and_post_forward = config.enable_pre_and_post_forward
+        # (GemmReduceScatter, output shard dimension), set by Float8RowwiseParallel(fused_reduce_scatter=...)
+        self._rowwise_reduce_scatter = None
 
     # -- delayed-scaling state --------------------------------------------
     def create_buffers(self):
@@ -186,7 +188,12 @@ class Float8Linear(torch.nn.Linear):
             self.float8_pre_forward(input)
         input_fp8 = self.cast_input_to_float8(input, self.is_amax_initialized)
         weight_fp8 = self.cast_weight_to_float8(self.weight, self.is_amax_initialized)
-        output = manual_float8_matmul.apply(input_fp8, weight_fp8.t())
+        if self._rowwise_reduce_scatter is not None and type(input_fp8).__name__ == "DTensor":
+            from .fused_reduce_scatter import rowwise_matmul_reduce_scatter
+
+            output = rowwise_matmul_reduce_scatter(input_fp8, weight_fp8.t(), *self._rowwise_reduce_scatter)
+        else:
+            output = manual_float8_matmul.apply(input_fp8, weight_fp8.t())
         output = self.cast_output_to_float8_in_bw(output)
         if self.bias is not None:
             output = output + self.bias.to(output.dtype)

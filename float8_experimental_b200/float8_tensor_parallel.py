@@ -69,7 +69,16 @@ class Float8ColwiseParallel(ColwiseParallel):
 
 class Float8RowwiseParallel(RowwiseParallel):
     """Row-parallel Float8Linear; the partial outputs are reduced in high precision
-    (reference: float8_tensor_parallel.py:92-142)."""
+    (reference: float8_tensor_parallel.py:92-142).
+
+    `fused_reduce_scatter` (not in the reference): a `fused_reduce_scatter.GemmReduceScatter` over
+    the mesh's process group.  With a sharded `output_layouts` the forward GEMM then stores its
+    partial product straight into the owners' receive buffers (peer memory) and the bf16
+    reduce-scatter of the reference disappears into the GEMM; the backward is unchanged."""
+
+    def __init__(self, *, input_layouts=None, output_layouts=None, use_local_output=True, fused_reduce_scatter=None):
+        super().__init__(input_layouts=input_layouts, output_layouts=output_layouts, use_local_output=use_local_output)
+        self.fused_reduce_scatter = fused_reduce_scatter
 
     @staticmethod
     def _prepare_input_fn(input_layouts, desired_input_layouts, mod, inputs, device_mesh):
@@ -81,7 +90,33 @@ class Float8RowwiseParallel(RowwiseParallel):
 
     def _apply(self, module: nn.Module, device_mesh: DeviceMesh) -> nn.Module:
         _check_module(module)
+        if self.fused_reduce_scatter is not None:
+            (layout,) = self.output_layouts
+            if device_mesh.ndim != 1 or not layout.is_shard():
+                raise ValueError("fused_reduce_scatter needs a 1-D mesh and a sharded output layout")
+            module._rowwise_reduce_scatter = (self.fused_reduce_scatter, layout.dim)
         return super()._apply(module, device_mesh)
+
+
+class _CastAllGatherInput(torch.autograd.Function):
+    """Sequence-parallel input -> replicated float8 DTensor through `CastAllGatherPool`: the cast
+    kernel's stores are the all-gather (peer memory), in place of cast + redistribute
+    (float8_experimental/float8_tensor_parallel.py:202-209).  Backward is the backward of that
+    redistribute: the gradient (partial sums of the column-parallel consumers) is reduce-scattered
+    back onto the input's sharding."""
+
+    @staticmethod
+    def forward(ctx, dt: DTensor, pool, linear_mm_config, shard_dim: int):
+        from torch.distributed._tensor import Replicate
+
+        ctx.placements = dt.placements
+        y8 = pool.gather_dim(dt.to_local(), shard_dim, linear_mm_config=linear_mm_config,
+                             gemm_input_role=GemmInputRole.INPUT)
+        return DTensor.from_local(y8, dt.device_mesh, (Replicate(),), run_check=False)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad.redistribute(placements=ctx.placements), None, None, None
 
 
 class PrepareFloat8ModuleInput(PrepareModuleInput):
@@ -91,11 +126,15 @@ class PrepareFloat8ModuleInput(PrepareModuleInput):
 
     Extra keywords: `float8_dtype` (only e4m3fn) and `fwd_config_submodule_fqn`, the
     submodule whose `linear_mm_config` tags the cast; when omitted every Float8Linear
-    below the module must share one config."""
+    below the module must share one config.  `cast_all_gather` (not in the reference): a
+    `fp8_all_gather.CastAllGatherPool` over the mesh's process group; a sharded -> replicated
+    input then goes through the cast whose stores are the all-gather (peer memory over NVLink)
+    instead of cast + NCCL all-gather.  Same bytes and scale; the pool's `depth` bounds how many
+    gathered inputs may be alive at once."""
 
     def __init__(self, *, input_layouts=None, desired_input_layouts=None, input_kwarg_layouts=None,
                  desired_input_kwarg_layouts=None, use_local_output=False, float8_dtype=torch.float8_e4m3fn,
-                 fwd_config_submodule_fqn=None):
+                 fwd_config_submodule_fqn=None, cast_all_gather=None):
         super().__init__(
             input_layouts=input_layouts,
             desired_input_layouts=desired_input_layouts,
@@ -108,6 +147,7 @@ class PrepareFloat8ModuleInput(PrepareModuleInput):
         self.float8_dtype = float8_dtype
         self.linear_mm_config = None
         self.fwd_config_submodule_fqn = fwd_config_submodule_fqn
+        self.cast_all_gather = cast_all_gather
 
     def _prepare_input_arg(self, input, mesh, input_layout, desired_layout):
         if input_layout is None:
@@ -117,6 +157,11 @@ class PrepareFloat8ModuleInput(PrepareModuleInput):
         else:
             assert isinstance(input, torch.Tensor), "expecting input to be a torch.Tensor!"
             dt = DTensor.from_local(input, mesh, (input_layout,), run_check=False)
+        if (self.cast_all_gather is not None and mesh.ndim == 1 and desired_layout is not None
+                and desired_layout.is_replicate() and input_layout.is_shard() and dt.is_cuda
+                and input_layout.dim < dt.dim() - 1):
+            dt = _CastAllGatherInput.apply(dt, self.cast_all_gather, self.linear_mm_config, input_layout.dim)
+            return dt.to_local() if self.use_local_output else dt
         dt = hp_tensor_to_float8_dynamic(dt, e4m3_dtype, self.linear_mm_config, gemm_input_role=GemmInputRole.INPUT)
         if desired_layout is not None and input_layout != desired_layout:
             dt = dt.redistribute(placements=(desired_layout,))

@@ -208,6 +208,43 @@ int f8b200_gemm_fp8_ws(const void* a, int a_kind, int a_layout, int64_t lda, con
                        void* stream);
 
 /*
+ * Reduce-scatter of a row-parallel linear's output, fused into the GEMM: replaces
+ * `outputs.redistribute(placements=output_layouts)` of Float8RowwiseParallel
+ * (float8_experimental/float8_tensor_parallel.py:116-128; the bf16 reduce-scatter of the partial
+ * products) together with the GEMM before it (float8_python_api.py:24-64).
+ *
+ * f8b200_gemm_fp8_scatter_rows   f8b200_gemm_fp8_ws whose output rows go to n_outs destinations:
+ *     row i belongs to block i / rows_per_block; blocks go round-robin to the destinations, so row i
+ *     is stored in outs[block % n_outs] at row (block / n_outs) * rows_per_block + i % rows_per_block
+ *     (row pitch ldo).  With outs[r] = this rank's slot in rank r's receive buffer (peer-mapped
+ *     memory, plain stores over NVLink from the epilogue warps; no TMA touches a destination), the
+ *     GEMM's stores ARE the scatter.  `outs` is a HOST array of device pointers, n_outs <= 16, m a
+ *     multiple of rows_per_block * n_outs.  bias must be NULL for a partial product that will be
+ *     summed (it would be added once per rank).  The caller orders the stores against the reader
+ *     (one collective on the same stream after the call).
+ * f8b200_sum_slots               out[i] = RN_T(sum over s < n_slots of slots[s * slot_stride + i]) for
+ *     i < numel, accumulated in fp32 in slot order (deterministic): the owner's half of the
+ *     reduce-scatter.  16-byte aligned pointers and slot pitch.
+ */
+int f8b200_gemm_fp8_scatter_rows(const void* a, int a_kind, int a_layout, int64_t lda, const void* b, int b_kind,
+                                 int b_layout, int64_t ldb, const float* scale_a, const float* scale_b,
+                                 const void* bias, int out_dtype, void* const* outs, int n_outs,
+                                 int64_t rows_per_block, int64_t ldo, int64_t m, int64_t n, int64_t k,
+                                 void* workspace, int64_t workspace_bytes, void* stream);
+int f8b200_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int hp_dtype, int64_t numel,
+                     void* out, void* stream);
+
+/*
+ * Which kernel f8b200_gemm_fp8 / _ws would run for an m x n x k product with the current
+ * environment: 0 = one CTA per 128x256 tile, 1 = CTA pair per 256x256 tile, 2 = one CTA per
+ * 256x256 tile, 3 = CTA pair per 512x256 tile (the default above 256 rows).  All four return
+ * the same bits; the choice is a matter of speed.  Reporting aid for benchmarks; host only, no
+ * CUDA call.  (cuBLASLt's heuristic behind torch._scaled_mm, float8_python_api.py:43-63, is the
+ * reference-side counterpart.)
+ */
+int f8b200_gemm_kernel_choice(int64_t m, int64_t n, int64_t k);
+
+/*
  * f8b200_gemm_fp8_ws without the workspace argument: the scheduling words live in a file-scope
  * `static __device__` array of F8B200_STATIC_SCRATCH_BYTES (4096) bytes inside the library, one
  * F8B200_GEMM_WORKSPACE_BYTES slot per stream.  This entry point has NO counterpart in the

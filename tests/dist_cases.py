@@ -213,7 +213,24 @@ class _Toy(nn.Module):
         return self.ffn(x)
 
 
-def case_tensor_parallel(rank, world, port, sequence_parallel):
+class _StubReduceScatter:
+    """Stands in for `GemmReduceScatter` where there is no peer memory (CPU ranks): the local
+    product through the ordinary op, an all-reduce, and this rank's slice.  What the test then
+    covers is the host side of the fused route: the autograd function, its backward (fp8 all-gather
+    of the gradient, the two float8 products) and the parallel style's wiring."""
+
+    def __call__(self, x8, w8_t, shard_dim):
+        from float8_experimental_b200.float8_python_api import addmm_float8_unwrapped
+
+        lead = tuple(x8.shape[:-1])
+        y = addmm_float8_unwrapped(x8._data.reshape(-1, x8.shape[-1]), x8._scale, w8_t._data, w8_t._scale,
+                                   output_dtype=x8._orig_dtype)
+        dist.all_reduce(y)
+        y = y.reshape(*lead, y.shape[-1])
+        return y.chunk(dist.get_world_size(), dim=shard_dim)[dist.get_rank()].contiguous()
+
+
+def case_tensor_parallel(rank, world, port, sequence_parallel, fused_reduce_scatter=False):
     """TP (and SP) float8 FFN == the unsharded float8 FFN
     (the reference's criterion, test/test_dtensor.py:189-231)."""
     _init(rank, world, port)
@@ -240,7 +257,8 @@ def case_tensor_parallel(rank, world, port, sequence_parallel):
         plan = {
             "ffn": PrepareFloat8ModuleInput(input_layouts=Shard(1), desired_input_layouts=Replicate()),
             "ffn.w1": Float8ColwiseParallel(),
-            "ffn.w2": Float8RowwiseParallel(output_layouts=Shard(1)),
+            "ffn.w2": Float8RowwiseParallel(output_layouts=Shard(1),
+                                            fused_reduce_scatter=_StubReduceScatter() if fused_reduce_scatter else None),
             "ffn.w3": Float8ColwiseParallel(),
         }
     else:
@@ -289,65 +307,6 @@ def case_tensor_parallel(rank, world, port, sequence_parallel):
     dist.destroy_process_group()
 
 
-def case_tensor_parallel_ffn_timing(rank, world, port):
-    """Sequence-parallel float8 FFN at the size of the reference's tensor-parallel configuration
-    (8192 -> 2 x 28672 -> 8192, 2 x 8192 tokens sequence-sharded): forward + backward time per
-    step, printed by rank 0.  GPU only."""
-    _init(rank, world, port)
-    from torch.distributed._tensor import Replicate, Shard
-    from torch.distributed.device_mesh import init_device_mesh
-    from torch.distributed.tensor.parallel import parallelize_module
-
-    import float8_experimental_b200 as f8
-    from float8_experimental_b200.float8_tensor_parallel import (
-        Float8ColwiseParallel,
-        Float8RowwiseParallel,
-        PrepareFloat8ModuleInput,
-    )
-
-    dim, hidden, batch, seq = 8192, 28672, 2, 8192
-    mesh = init_device_mesh(DEVICE, (world,))
-    torch.manual_seed(5)
-    model = _Toy(dim, hidden).to(torch.bfloat16)
-    f8.convert_to_float8_training(model, config=f8.Float8LinearConfig())
-    plan = {
-        "ffn": PrepareFloat8ModuleInput(input_layouts=Shard(1), desired_input_layouts=Replicate()),
-        "ffn.w1": Float8ColwiseParallel(),
-        "ffn.w2": Float8RowwiseParallel(output_layouts=Shard(1)),
-        "ffn.w3": Float8ColwiseParallel(),
-    }
-    model = parallelize_module(model, mesh, plan)
-    x = torch.randn(batch, seq // world, dim, dtype=torch.bfloat16, requires_grad=True)
-    go = torch.randn(batch, seq // world, dim, dtype=torch.bfloat16) * 1e-3
-
-    def step():
-        x.grad = None
-        for p in model.parameters():
-            p.grad = None
-        y = model(x)
-        y = y.to_local() if hasattr(y, "to_local") else y
-        y.backward(go)
-
-    for _ in range(3):
-        step()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0.record()
-    for _ in range(5):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / 5], device="cuda")
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        flops = 3 * 6.0 * batch * seq * dim * hidden
-        print(f"TP_FFN_TIMING world={world} tokens={batch * seq} ffn {dim}->2x{hidden}->{dim}: "
-              f"{ms.item():.2f} ms/step, {flops / ms.item() / 1e9:.0f} TFLOP/s over {world} GPUs", flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
-
-
 def case_cast_all_gather_over_peer_memory(rank, world, port):
     """The cast that scatters its result into every rank's gathered buffer (peer stores) gives
     the bytes and the scale of cast-then-NCCL-all-gather; repeated calls reuse the buffers.
@@ -370,33 +329,32 @@ def case_cast_all_gather_over_peer_memory(rank, world, port):
         assert got._scale.item() == ref_local._scale.item()
         assert got._data.shape == (world * rows, cols)
         assert torch.equal(got._data.view(torch.uint8), ref)
-    # timing of the two routes on the [8192, 8192] shard (events on this rank, after warm-up)
-    x = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
-    ref = torch.empty(world * 8192, 8192, dtype=torch.uint8, device="cuda")
+    dist.barrier()
+    dist.destroy_process_group()
 
-    def fused():
-        gather(x)
 
-    def unfused():
-        r = hp_tensor_to_float8_dynamic(x, torch.float8_e4m3fn, cfg, reduce_amax=True)
-        dist.all_gather_into_tensor(ref, r._data.view(torch.uint8))
+def case_package_parity(rank, world, port, name):
+    """The parity checks the benchmark runs before it times anything on several GPUs
+    (`float8_experimental_b200.benchmarks.multi_gpu`), one by one.  GPU only."""
+    _init(rank, world, port)
+    from float8_experimental_b200.benchmarks import multi_gpu
 
-    out = {}
-    for name, fn in (("fused", fused), ("unfused", unfused)):
-        for _ in range(3):
-            fn()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        dist.barrier()
-        s0.record()
-        for _ in range(10):
-            fn()
-        s1.record()
-        torch.cuda.synchronize()
-        out[name] = s0.elapsed_time(s1) / 10
-    if rank == 0:
-        print(f"CAST_ALL_GATHER world={world} shard=8192x8192 bf16: fused {out['fused']:.3f} ms, "
-              f"cast + NCCL all-gather {out['unfused']:.3f} ms", flush=True)
+    dev = torch.device("cuda", rank)
+    fn = {
+        "fsdp2": lambda: multi_gpu.parity_fsdp2(dev, rank, world),
+        "tp": lambda: multi_gpu.parity_tensor_parallel(dev, rank, world, False),
+        "sp": lambda: multi_gpu.parity_tensor_parallel(dev, rank, world, True),
+        "delayed_sync": lambda: multi_gpu.parity_delayed_sync(dev, rank, world),
+        "cast_all_gather": lambda: multi_gpu.parity_cast_all_gather(dev, rank, world),
+        "sp_cast_all_gather": lambda: multi_gpu.parity_tensor_parallel(dev, rank, world, True, cast_all_gather=True),
+        "sp_fused_reduce_scatter": lambda: multi_gpu.parity_tensor_parallel(dev, rank, world, True,
+                                                                            fused_reduce_scatter=True),
+    }[name]
+    assert fn() == "ok"
+    torch.cuda.synchronize()
+    from float8_experimental_b200 import _native
+
+    assert _native.read_device_error() == 0
     dist.barrier()
     dist.destroy_process_group()
 

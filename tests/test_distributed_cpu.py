@@ -47,3 +47,9 @@ def test_fsdp2_delayed_weight_scaling():
 @pytest.mark.parametrize("sequence_parallel", [False, True])
 def test_tensor_parallel_matches_unsharded(sequence_parallel):
     _run("case_tensor_parallel", sequence_parallel)
+
+
+def test_sequence_parallel_with_fused_reduce_scatter_route():
+    """The row-parallel layer's fused GEMM + reduce-scatter route (host side; the peer-memory GEMM is
+    replaced by a stand-in on CPU ranks) still equals the unsharded model."""
+    _run("case_tensor_parallel", True, True)

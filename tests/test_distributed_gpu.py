@@ -57,6 +57,8 @@ def test_cast_all_gather_over_peer_memory():
     _run("case_cast_all_gather_over_peer_memory")
 
 
-def test_tensor_parallel_ffn_timing_at_full_size():
-    """Not a parity case: runs the sequence-parallel FFN at full size and prints its step time."""
-    _run("case_tensor_parallel_ffn_timing")
+@pytest.mark.parametrize("name", ["fsdp2", "tp", "sp", "delayed_sync", "cast_all_gather", "sp_cast_all_gather",
+                                  "sp_fused_reduce_scatter"])
+def test_benchmark_parity_checks(name):
+    """Each check of the block that `bench.py --gpus N` runs before timing (N > 1), here on two ranks."""
+    _run("case_package_parity", name)

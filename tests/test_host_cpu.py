@@ -397,17 +397,17 @@ def test_gemm_operand_layout_selection():
 
 
 def test_multicast_gemm_selection_rules(monkeypatch):
-    """The single-GPU multicast library is used only when present, only in single-process runs,
-    by default only for K >= 16384, and never when a kernel is forced."""
+    """The single-GPU multicast library is opt-in (F8B200_GEMM_MC=21/22/41), used only when
+    present, only in single-GPU jobs, and never when a kernel is forced."""
     from float8_experimental_b200 import _native as N
 
     monkeypatch.setattr(N, "load_mc", lambda: object())
     monkeypatch.setattr(N, "_single_gpu_job", lambda: True)
     monkeypatch.delenv("F8B200_GEMM_MC", raising=False)
     monkeypatch.delenv("F8B200_GEMM_MODE", raising=False)
-    monkeypatch.delenv("F8B200_GEMM_WIDE_K", raising=False)
+    assert N._mc_cluster(8192, 8192, 16384) is None  # not by default
+    monkeypatch.setenv("F8B200_GEMM_MC", "21")
     assert N._mc_cluster(8192, 8192, 16384) == (2, 1)
-    assert N._mc_cluster(16384, 8192, 8192) is None
     monkeypatch.setenv("F8B200_GEMM_MODE", "wide")
     assert N._mc_cluster(8192, 8192, 16384) is None
     monkeypatch.delenv("F8B200_GEMM_MODE")
@@ -415,13 +415,12 @@ def test_multicast_gemm_selection_rules(monkeypatch):
     assert N._mc_cluster(16384, 8192, 8192) == (2, 2)
     monkeypatch.setenv("F8B200_GEMM_MC", "0")
     assert N._mc_cluster(8192, 8192, 16384) is None
-    monkeypatch.delenv("F8B200_GEMM_MC")
+    monkeypatch.setenv("F8B200_GEMM_MC", "21")
     monkeypatch.setattr(N, "load_mc", lambda: None)  # library not shipped (runs on several GPUs)
     assert N._mc_cluster(8192, 8192, 16384) is None
     # ... and never in a job that may use a second GPU, whatever was shipped or forced
     monkeypatch.setattr(N, "load_mc", lambda: object())
     monkeypatch.setattr(N, "_single_gpu_job", lambda: False)
-    monkeypatch.setenv("F8B200_GEMM_MC", "21")
     assert N._mc_cluster(8192, 8192, 16384) is None
 
 
