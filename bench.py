@@ -284,7 +284,11 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     _native.load()
     parity_n = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that fails a parity check ends the run with an error within
+        # minutes instead of leaving the others waiting for it
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
         # the sharded paths are checked on the real NCCL / CUDA route before anything is timed
         parity_n = multi_gpu.run_parity(dev, rank, world)
         if any(v != "ok" for v in parity_n.values()):

@@ -31,6 +31,7 @@ EXPORTS = (
     "f8b200_amax_to_scale",
     "f8b200_cast",
     "f8b200_cast_scatter",
+    "f8b200_multi_cast",
     "f8b200_transpose_u8",
     "f8b200_delayed_sync",
     "f8b200_gemm_fp8",
@@ -82,6 +83,7 @@ def load() -> ctypes.CDLL:
     lib.f8b200_cast.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, vp, i64, vp, i64, vp, i32, vp]
     lib.f8b200_cast_scatter.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, ctypes.POINTER(vp), i32, i64,
                                         vp]
+    lib.f8b200_multi_cast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(i64), i32, i32, vp, i32, i32, ctypes.POINTER(vp), vp]
     lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
     lib.f8b200_gemm_fp8.argtypes = [vp, i32, i64, vp, i32, i64, vp, vp, vp, i32, vp, i64, i64, i64, i64, i32, vp]
@@ -253,6 +255,25 @@ def cast(x: torch.Tensor, rows: int, cols: int, ld_x: int, scale_src: int, scale
                                ld_out_t, _ptr(amax_out), int(reverse), _stream(x)),
             "f8b200_cast",
         )
+
+
+def multi_cast(xs: Sequence[torch.Tensor], scales: torch.Tensor, product_fp32: bool, fp8_kind: int,
+               outs: Sequence[torch.Tensor]) -> None:
+    """`f8b200_multi_cast`: every contiguous tensor of `xs` cast with its own scale (`scales[i]`) into
+    `outs[i]`, one launch per 96 tensors."""
+    n = len(xs)
+    if n == 0:
+        return
+    _require_cuda(scales, *xs, *outs)
+    dt = xs[0].dtype
+    if any(t.dtype != dt for t in xs):
+        raise F8B200Error("multi_cast needs tensors of one dtype")
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in xs])
+    optrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in outs])
+    numels = (ctypes.c_int64 * n)(*[t.numel() for t in xs])
+    with _Launch("cast", scales.device, (n + 95) // 96):
+        _check(load().f8b200_multi_cast(ptrs, numels, n, hp_code(dt), scales.data_ptr(), int(product_fp32), fp8_kind,
+                                        optrs, _stream(scales)), "f8b200_multi_cast")
 
 
 def transpose_u8(src: torch.Tensor, rows: int, cols: int, ld_in: int, dst: torch.Tensor, ld_out: int) -> None:

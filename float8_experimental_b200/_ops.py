@@ -11,6 +11,7 @@ Ops (namespace `f8b200`):
   amax_to_scale(amax, kind, amax_dtype, orig_dtype)       f8b200_amax_to_scale
   cast_from_amax(x, amax, kind, with_t) -> (data, data_t, scale)   f8b200_cast, scale_src=1
   cast_with_scale(x, scale, kind, product_fp32, with_t, amax_out!) -> (data, data_t)
+  multi_cast_with_scales(xs, scales, kind, product_fp32) -> fp8 tensors   f8b200_multi_cast
   transpose_fp8(x) -> x^T contiguous                      f8b200_transpose_u8
   delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out!, hist_out!)
   scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum) -> out
@@ -37,6 +38,7 @@ _lib.define(
     "cast_with_scale(Tensor x, Tensor scale, int fp8_kind, bool product_fp32, bool with_transpose, "
     "Tensor(a!)? amax_out) -> (Tensor, Tensor)"
 )
+_lib.define("multi_cast_with_scales(Tensor[] xs, Tensor scales, int fp8_kind, bool product_fp32) -> Tensor[]")
 _lib.define("transpose_fp8(Tensor x) -> Tensor")
 _lib.define(
     "delayed_sync(Tensor amax, Tensor hist, int n_e4m3, int orig_dtype, Tensor(a!) scale_out, "
@@ -123,6 +125,14 @@ def _cast_with_scale_cuda(x, scale, fp8_kind: int, product_fp32: bool, with_tran
     N.cast(xm, rows, cols, ld, 0, s, None, product_fp32, fp8_kind, data, cols,
            data_t if with_transpose else None, rows, amax_out, False)
     return data, data_t
+
+
+def _multi_cast_with_scales_cuda(xs: List[torch.Tensor], scales: torch.Tensor, fp8_kind: int, product_fp32: bool):
+    xs = [t if t.is_contiguous() else t.contiguous() for t in xs]
+    s = scales if (scales.dtype == torch.float32 and scales.is_contiguous()) else scales.float().contiguous()
+    outs = [torch.empty(t.shape, dtype=N.FP8_DTYPE[fp8_kind], device=t.device) for t in xs]
+    N.multi_cast(xs, s, product_fp32, fp8_kind, outs)
+    return outs
 
 
 def _transpose_fp8_cuda(x: torch.Tensor) -> torch.Tensor:
@@ -222,13 +232,6 @@ def _swiglu_cast_cuda(a, b, amax, fp8_kind: int):
     return data, scale
 
 
-def fused_bwd_supported(x: torch.Tensor, max_cols: int = 0) -> bool:
-    """Whether the backward kernels of the fused producers cover this tensor (16-bit dtype, last
-    dimension a multiple of 8 and, for RMSNorm, at most 8192)."""
-    cols = x.shape[-1]
-    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and cols % 8 == 0 and (max_cols == 0 or cols <= max_cols)
-
-
 def _rmsnorm_bwd_cuda(x, grad_y, weight, rstd):
     xm, rows, cols, ld = _as_matrix(x.contiguous())
     gm, _, _, ldg = _as_matrix(grad_y.contiguous())
@@ -240,7 +243,7 @@ def _rmsnorm_bwd_cuda(x, grad_y, weight, rstd):
 
 def _swiglu_bwd_cuda(a, b, grad_y):
     am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
-    gm, _, _, ldg = _as_matrix(grad_y.contiguous())
+    gm, _, _, ldg = _as_matrix(grad_y.reshape(a.shape).contiguous())
     da = torch.empty(a.shape, dtype=a.dtype, device=a.device)
     db = torch.empty(a.shape, dtype=a.dtype, device=a.device)
     N.swiglu_bwd(am, bm, gm, rows, cols, lda, ldb, ldg, da, db)
@@ -259,6 +262,7 @@ _lib.impl("amax_to_scale", _amax_to_scale_cuda, "CUDA")
 _lib.impl("cast_from_amax", _cast_from_amax_cuda, "CUDA")
 _lib.impl("cast_with_scale", _cast_with_scale_cuda, "CUDA")
 _lib.impl("transpose_fp8", _transpose_fp8_cuda, "CUDA")
+_lib.impl("multi_cast_with_scales", _multi_cast_with_scales_cuda, "CUDA")
 _lib.impl("delayed_sync", _delayed_sync_cuda, "CUDA")
 _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 
@@ -331,6 +335,11 @@ def _cast_from_amax_fake(x, amax, fp8_kind, with_transpose):
 @torch.library.register_fake("f8b200::cast_with_scale")
 def _cast_with_scale_fake(x, scale, fp8_kind, product_fp32, with_transpose, amax_out):
     return _fake_cast_outputs(x, fp8_kind, with_transpose)
+
+
+@torch.library.register_fake("f8b200::multi_cast_with_scales")
+def _multi_cast_with_scales_fake(xs, scales, fp8_kind, product_fp32):
+    return [t.new_empty(t.shape, dtype=N.FP8_DTYPE[fp8_kind]) for t in xs]
 
 
 @torch.library.register_fake("f8b200::transpose_fp8")

@@ -416,18 +416,22 @@ def measure_fsdp2_llama3_8b_linears(dev, rank, world, steps: int = 3, n_blocks: 
     weights = sum(p.numel() for p in model.parameters()) * world  # parameters are sharded DTensors
     per_block = 4096 * 4096 * 2 + 4096 * 1024 * 2 + 3 * 4096 * 14336
 
-    def step():
-        x.grad = None
-        for p in model.parameters():
-            p.grad = None
-        model(x).backward(go)
-        f8.precompute_float8_dynamic_scale_for_fsdp(model)
-
-    ms = _timed_steps(step, steps, dev)
     flops = 6.0 * seq * per_block * n_blocks
-    return {"blocks": n_blocks, "linears": 7 * n_blocks, "tokens_per_gpu": seq, "ms_per_step": ms,
-            "tflops_all_gpus": world * flops / ms / 1e9, "fp8_weight_bytes_gathered_per_pass": per_block * n_blocks,
-            "local_weight_elements": weights // world}
+    out = {"blocks": n_blocks, "linears": 7 * n_blocks, "tokens_per_gpu": seq,
+           "fp8_weight_bytes_gathered_per_pass": per_block * n_blocks, "local_weight_elements": weights // world}
+    # the reference's schedule (each shard cast when its all-gather is issued, twice per step), and all
+    # shards cast once per step by one multi-tensor launch right after the scales are known
+    for name, cast_now in (("cast_per_all_gather", False), ("cast_all_shards_at_once", True)):
+        def step():
+            x.grad = None
+            for p in model.parameters():
+                p.grad = None
+            model(x).backward(go)
+            f8.precompute_float8_dynamic_scale_for_fsdp(model, cast_now=cast_now)
+
+        ms = _timed_steps(step, steps, dev)
+        out[name] = {"ms_per_step": ms, "tflops_all_gpus": world * flops / ms / 1e9}
+    return out
 
 
 def measure_cast_all_gather(dev, rank, world, rows: int = 8192, cols: int = 8192):

@@ -516,6 +516,62 @@ __global__ void __launch_bounds__(256) cast_generic_kernel(const CastParams p) {
 }
 
 // ---------------------------------------------------------------------------
+// multi-tensor cast: n contiguous tensors, one scale each, one launch
+// ---------------------------------------------------------------------------
+constexpr int kMultiCastMax = 96;  // tensors per launch (kernel parameters stay below 4 KB)
+struct MultiCastArgs {
+  const void* x[kMultiCastMax];
+  uint8_t* out[kMultiCastMax];
+  int64_t numel[kMultiCastMax];
+  const float* scales;  // scales[first + t] belongs to tensor t of this launch
+  int first;
+  int product_fp32;
+};
+
+// blockIdx.y picks the tensor, blockIdx.x strides over its 16-byte input vectors.  Same arithmetic as
+// the tiled cast: product in fp32, rounded to the tensor's dtype unless product_fp32, saturating RNE.
+template <int HP, int KIND>
+__global__ void __launch_bounds__(256) multi_cast_kernel(const MultiCastArgs a) {
+  constexpr int ES = (HP == F8B200_FP32) ? 4 : 2;
+  constexpr int V = 16 / ES;
+  const int t = blockIdx.y;
+  const int64_t n = a.numel[t];
+  const float s = a.scales[a.first + t];
+  const bool round_to_hp = !a.product_fp32;
+  const char* src = static_cast<const char*>(a.x[t]);
+  uint8_t* dst = a.out[t];
+  const bool vec = (reinterpret_cast<uintptr_t>(src) % 16 == 0) && (reinterpret_cast<uintptr_t>(dst) % (V / 4 * 4) == 0);
+  const int64_t nvec = vec ? n / V : 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+    if constexpr (ES == 2) {
+      float f0, f1, f2, f3;
+      unpack2<HP>(v.x, f0, f1);
+      unpack2<HP>(v.y, f2, f3);
+      const uint32_t lo = cast4<HP, KIND>(__fmul_rn(f0, s), __fmul_rn(f1, s), __fmul_rn(f2, s), __fmul_rn(f3, s), round_to_hp);
+      unpack2<HP>(v.z, f0, f1);
+      unpack2<HP>(v.w, f2, f3);
+      const uint32_t hi = cast4<HP, KIND>(__fmul_rn(f0, s), __fmul_rn(f1, s), __fmul_rn(f2, s), __fmul_rn(f3, s), round_to_hp);
+      reinterpret_cast<uint2*>(dst)[i] = make_uint2(lo, hi);
+    } else {
+      reinterpret_cast<uint32_t*>(dst)[i] =
+          cast4<HP, KIND>(__fmul_rn(__uint_as_float(v.x), s), __fmul_rn(__uint_as_float(v.y), s),
+                          __fmul_rn(__uint_as_float(v.z), s), __fmul_rn(__uint_as_float(v.w), s), false);
+    }
+  }
+  for (int64_t i = nvec * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float f;
+    if constexpr (HP == F8B200_FP32) f = static_cast<const float*>(a.x[t])[i];
+    else if constexpr (HP == F8B200_BF16) f = __uint_as_float((uint32_t)static_cast<const uint16_t*>(a.x[t])[i] << 16);
+    else f = __half2float(__ushort_as_half(static_cast<const uint16_t*>(a.x[t])[i]));
+    float pr = __fmul_rn(f, s);
+    if (round_to_hp) pr = round_hp<HP>(pr);
+    dst[i] = (uint8_t)(cvt_pair<KIND>(pr, 0.0f) & 0xFFu);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // fp8 transpose
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_u8_tile_kernel(const uint8_t* in, int64_t rows, int64_t cols,
@@ -806,6 +862,52 @@ extern "C" int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t co
                            void* stream) {
   return cast_impl(x, hp_dtype, rows, cols, ld_x, scale_src, scale_in, scale_out, product_fp32, fp8_kind, out, ld_out,
                    out_t, ld_out_t, amax_out, reverse, nullptr, 0, stream);
+}
+
+extern "C" int f8b200_multi_cast(const void* const* xs, const int64_t* numels, int n, int hp_dtype, const float* scales,
+                                 int product_fp32, int fp8_kind, void* const* outs, void* stream) {
+  if (n < 0 || hp_dtype < 0 || hp_dtype > 2 || fp8_kind < 0 || fp8_kind > 1) return F8B200_ERR_BAD_ARG;
+  if (n == 0) return F8B200_OK;
+  if (xs == nullptr || numels == nullptr || outs == nullptr || scales == nullptr) return F8B200_ERR_BAD_ARG;
+  const int es = hp_size_of(hp_dtype);
+  int64_t largest = 0;
+  for (int i = 0; i < n; ++i) {
+    if (numels[i] < 0 || (numels[i] > 0 && (xs[i] == nullptr || outs[i] == nullptr))) return F8B200_ERR_BAD_ARG;
+    if (!aligned_to(xs[i], es)) return F8B200_ERR_ALIGNMENT;
+    if (numels[i] > largest) largest = numels[i];
+  }
+  if (!aligned_to(scales, 4)) return F8B200_ERR_ALIGNMENT;
+  int rc = f8b200_device_check();
+  if (rc != F8B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int first = 0; first < n; first += kMultiCastMax) {
+    const int cnt = (n - first) < kMultiCastMax ? (n - first) : kMultiCastMax;
+    MultiCastArgs a = {};
+    int64_t big = 0;
+    for (int t = 0; t < cnt; ++t) {
+      a.x[t] = xs[first + t];
+      a.out[t] = static_cast<uint8_t*>(outs[first + t]);
+      a.numel[t] = numels[first + t];
+      if (a.numel[t] > big) big = a.numel[t];
+    }
+    a.scales = scales;
+    a.first = first;
+    a.product_fp32 = product_fp32;
+    // enough CTAs for the largest tensor of the launch, capped so that the grid stays a few waves
+    int64_t bx = (big / (16 / es) + 255) / 256;
+    const int64_t cap = ((int64_t)sm_count() * 8 + cnt - 1) / cnt;
+    if (bx > cap) bx = cap;
+    if (bx < 1) bx = 1;
+    const dim3 grid((unsigned)bx, (unsigned)cnt);
+    rc = dispatch_hp(hp_dtype, [&](auto hp) {
+      constexpr int HP = decltype(hp)::value;
+      if (fp8_kind == F8B200_E4M3) multi_cast_kernel<HP, F8B200_E4M3><<<grid, 256, 0, st>>>(a);
+      else multi_cast_kernel<HP, F8B200_E5M2><<<grid, 256, 0, st>>>(a);
+      return check_launch();
+    });
+    if (rc != F8B200_OK) return rc;
+  }
+  return F8B200_OK;
 }
 
 extern "C" int f8b200_cast_scatter(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,

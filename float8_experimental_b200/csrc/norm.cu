@@ -804,12 +804,62 @@ swiglu_bwd_kernel(const char* __restrict__ a, const char* __restrict__ b, const 
   }
 }
 
+// Generic variants (any column count, fp32 as well as the 16-bit types, any row pitch): one CTA per
+// row, the row is read twice (the second sweep hits L2), dw goes through the same per-CTA partial
+// sums (each CTA owns one row of `dw_partial`, which it zeroes first).  Same formulas and roundings.
+template <int HP>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_generic_kernel(const char* __restrict__ x, int64_t ldx, const char* __restrict__ g, int64_t ldg, int64_t rows,
+                           int64_t cols, const char* __restrict__ weight, const float* __restrict__ rstd_in,
+                           char* __restrict__ dx, int64_t lddx, float* __restrict__ dw_partial) {
+  __shared__ float red[kNormThreads / 32];
+  constexpr int ESZ = HP == F8B200_FP32 ? 4 : 2;
+  float* mine = dw_partial + (int64_t)blockIdx.x * cols;
+  for (int64_t c = threadIdx.x; c < cols; c += kNormThreads) mine[c] = 0.0f;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const char* xrow = x + r * ldx * ESZ;
+    const char* grow = g + r * ldg * ESZ;
+    const float rstd = __ldg(rstd_in + r);
+    float dot = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += kNormThreads) {  // each thread owns its columns: no race on `mine`
+      const float xv = load_hp<HP>(xrow, c), gv = load_hp<HP>(grow, c), wv = load_hp<HP>(weight, c);
+      const float n = xv * rstd;
+      dot = fmaf(round_hp<HP>(gv * wv), n, dot);
+      mine[c] = fmaf(gv, round_hp<HP>(n), mine[c]);
+    }
+    const float cmean = block_sum_fixed(dot, red) / (float)cols;
+    char* orow = dx + r * lddx * ESZ;
+    for (int64_t c = threadIdx.x; c < cols; c += kNormThreads) {
+      const float xv = load_hp<HP>(xrow, c), gv = load_hp<HP>(grow, c), wv = load_hp<HP>(weight, c);
+      store_hp<HP>(orow, c, rstd * (round_hp<HP>(gv * wv) - xv * rstd * cmean));
+    }
+  }
+}
+
+template <int HP>
+__global__ void __launch_bounds__(kGluThreads)
+swiglu_bwd_generic_kernel(const char* __restrict__ a, const char* __restrict__ b, const char* __restrict__ g, int64_t lda,
+                          int64_t ldb, int64_t ldg, int64_t rows, int64_t cols, char* __restrict__ da,
+                          char* __restrict__ db, int64_t ldo) {
+  constexpr int ESZ = HP == F8B200_FP32 ? 4 : 2;
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * kGluThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGluThreads) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float av = load_hp<HP>(a + r * lda * ESZ, c), bv = load_hp<HP>(b + r * ldb * ESZ, c);
+    const float gv = load_hp<HP>(g + r * ldg * ESZ, c);
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-av)));
+    const float ds = round_hp<HP>(gv * bv);
+    store_hp<HP>(da + r * ldo * ESZ, c, ds * (sig * (1.0f + av * (1.0f - sig))));
+    store_hp<HP>(db + r * ldo * ESZ, c, gv * round_hp<HP>(silu_f32(av)));
+  }
+}
+
 }  // namespace
 }  // namespace f8b200
 
-// 16-bit dtypes, cols a multiple of 8 and at most 8192, 16-byte aligned rows: anything else returns
-// F8B200_ERR_UNSUPPORTED and the caller uses framework ops.  `workspace` holds the per-CTA partial
-// sums of dw: f8b200_rmsnorm_bwd_workspace_bytes(cols) bytes of device memory, fp32.
+// The fast kernels cover 16-bit dtypes, cols a multiple of 8 (RMSNorm: at most 8192) and 16-byte
+// aligned rows; every other shape or dtype runs on the generic kernels above.  `workspace` holds the
+// per-CTA partial sums of dw: f8b200_rmsnorm_bwd_workspace_bytes(cols) bytes of device memory, fp32.
 static int norm_bwd_grid(int64_t rows) {
   const int64_t cap = (int64_t)sm_count() * 2;  // two CTAs of the backward kernel fit an SM
   return (int)(rows < cap ? rows : cap);
@@ -827,11 +877,10 @@ extern "C" int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtyp
       dweight == nullptr || workspace == nullptr)
     return F8B200_ERR_BAD_ARG;
   if (rows <= 0 || cols <= 0 || ld_x < cols || ld_g < cols || ld_dx < cols) return F8B200_ERR_BAD_ARG;
-  if (hp_dtype != F8B200_BF16 && hp_dtype != F8B200_FP16) return F8B200_ERR_UNSUPPORTED;
+  if (hp_dtype < 0 || hp_dtype > 2) return F8B200_ERR_BAD_ARG;
   auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-  if (cols % 8 != 0 || cols > 8192 || ld_x % 8 != 0 || ld_g % 8 != 0 || ld_dx % 8 != 0 || !al16(x) || !al16(grad_y) ||
-      !al16(weight) || !al16(dx) || !al16(workspace))
-    return F8B200_ERR_UNSUPPORTED;
+  const bool fast = hp_dtype != F8B200_FP32 && cols % 8 == 0 && cols <= 8192 && ld_x % 8 == 0 && ld_g % 8 == 0 &&
+                    ld_dx % 8 == 0 && al16(x) && al16(grad_y) && al16(weight) && al16(dx) && al16(workspace);
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
   const int grid = norm_bwd_grid(rows);
@@ -842,6 +891,22 @@ extern "C" int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtyp
   const char* wp = static_cast<const char*>(weight);
   char* dxp = static_cast<char*>(dx);
   float* part = static_cast<float*>(workspace);
+  const unsigned blocks = (unsigned)((cols + 31) / 32);
+  if (!fast) {
+#define F8_RMS_BWD_GEN(HP)                                                                                         \
+  do {                                                                                                             \
+    rmsnorm_bwd_generic_kernel<HP><<<grid, kNormThreads, 0, st>>>(xp, ld_x, gp, ld_g, rows, cols, wp, rstd, dxp,   \
+                                                                  ld_dx, part);                                    \
+    rc = check_launch();                                                                                           \
+    if (rc != F8B200_OK) return rc;                                                                                \
+    rmsnorm_dw_reduce_kernel<HP><<<blocks, 256, 0, st>>>(part, grid, cols, static_cast<char*>(dweight));           \
+  } while (0)
+    if (hp_dtype == F8B200_BF16) F8_RMS_BWD_GEN(F8B200_BF16);
+    else if (hp_dtype == F8B200_FP16) F8_RMS_BWD_GEN(F8B200_FP16);
+    else F8_RMS_BWD_GEN(F8B200_FP32);
+#undef F8_RMS_BWD_GEN
+    return check_launch();
+  }
 #define F8_RMS_BWD(HP, CH)                                                                                        \
   rmsnorm_bwd_kernel<HP, CH><<<grid, kNormThreads, 0, st>>>(xp, ld_x * 2, gp, ld_g * 2, rows, cols, wp, rstd, dxp, \
                                                             ld_dx * 2, part)
@@ -856,7 +921,6 @@ extern "C" int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtyp
 #undef F8_RMS_BWD
   rc = check_launch();
   if (rc != F8B200_OK) return rc;
-  const unsigned blocks = (unsigned)((cols + 31) / 32);
   if (hp_dtype == F8B200_BF16)
     rmsnorm_dw_reduce_kernel<F8B200_BF16><<<blocks, 256, 0, st>>>(part, grid, cols, static_cast<char*>(dweight));
   else
@@ -869,14 +933,25 @@ extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_
                                  int64_t ld_out, void* stream) {
   if (a == nullptr || b == nullptr || grad_y == nullptr || da == nullptr || db == nullptr) return F8B200_ERR_BAD_ARG;
   if (rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols || ld_g < cols || ld_out < cols) return F8B200_ERR_BAD_ARG;
-  if (hp_dtype != F8B200_BF16 && hp_dtype != F8B200_FP16) return F8B200_ERR_UNSUPPORTED;
+  if (hp_dtype < 0 || hp_dtype > 2) return F8B200_ERR_BAD_ARG;
   auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-  if (cols % 8 != 0 || ld_a % 8 != 0 || ld_b % 8 != 0 || ld_g % 8 != 0 || ld_out % 8 != 0 || !al16(a) || !al16(b) ||
-      !al16(grad_y) || !al16(da) || !al16(db))
-    return F8B200_ERR_UNSUPPORTED;
+  const bool fast = hp_dtype != F8B200_FP32 && cols % 8 == 0 && ld_a % 8 == 0 && ld_b % 8 == 0 && ld_g % 8 == 0 &&
+                    ld_out % 8 == 0 && al16(a) && al16(b) && al16(grad_y) && al16(da) && al16(db);
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!fast) {
+    const int ggrid = glu_grid(rows * cols);
+#define F8_GLU_BWD_GEN(HP)                                                                                             \
+  swiglu_bwd_generic_kernel<HP><<<ggrid, kGluThreads, 0, st>>>(                                                        \
+      static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a, ld_b, ld_g, rows, \
+      cols, static_cast<char*>(da), static_cast<char*>(db), ld_out)
+    if (hp_dtype == F8B200_BF16) F8_GLU_BWD_GEN(F8B200_BF16);
+    else if (hp_dtype == F8B200_FP16) F8_GLU_BWD_GEN(F8B200_FP16);
+    else F8_GLU_BWD_GEN(F8B200_FP32);
+#undef F8_GLU_BWD_GEN
+    return check_launch();
+  }
   const int64_t cpr = cols / 8;
   const int grid = glu_grid(rows * cpr);
   if (hp_dtype == F8B200_BF16)

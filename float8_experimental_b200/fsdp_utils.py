@@ -28,7 +28,7 @@ from .float8_utils import e4m3_dtype, EPS
 
 
 @torch.no_grad()
-def precompute_float8_dynamic_scale_for_fsdp(module: nn.Module) -> None:
+def precompute_float8_dynamic_scale_for_fsdp(module: nn.Module, cast_now: bool = False) -> None:
     """Computes the dynamic scale of every FSDP-sharded float8 weight after an optimizer
     step with ONE multi-tensor amax launch over all local shards, ONE all-reduce (MAX)
     over the [n_weights] amax vector and ONE scale kernel
@@ -37,7 +37,14 @@ def precompute_float8_dynamic_scale_for_fsdp(module: nn.Module) -> None:
 
         model(input).sum().backward(); optim.step()
         precompute_float8_dynamic_scale_for_fsdp(model)
-    """
+
+    `cast_now=True` (not in the reference) also casts every local shard right away, all of them
+    in one multi-tensor launch (per 96 weights), and keeps the fp8 bytes on the weight wrappers:
+    the all-gathers of the following forward AND backward then hand over those bytes without
+    launching anything, where the reference casts each weight once per all-gather
+    (fsdp_utils.py:168-185).  Same bytes and scales.  The cached bytes belong to the weights as
+    they are at this call, exactly like the precomputed scales: call it after every optimizer
+    step, before the next forward."""
     from torch.distributed._tensor import DTensor
 
     from .config import ScalingType
@@ -64,8 +71,14 @@ def precompute_float8_dynamic_scale_for_fsdp(module: nn.Module) -> None:
     scales = ops.amax_to_scale(amaxes, N.E4M3, code, code)  # fp32 [n]
     if w_dtype != torch.float32:
         scales = scales.to(w_dtype)  # the reference's scale tensor has the weights' dtype
+    fp8_shards = None
+    if cast_now:
+        # product rounded to the weights' dtype: the precomputed scale is a 0-dim tensor of that dtype
+        fp8_shards = ops.multi_cast_with_scales(shards, scales.float(), N.E4M3, False)
     for i, m in enumerate(targets):
-        m.weight._local_tensor._precomputed_scale = scales[i]
+        w = m.weight._local_tensor
+        w._precomputed_scale = scales[i]
+        w._precomputed_fp8 = fp8_shards[i] if fp8_shards is not None else None
 
 
 # FSDP pads, slices and copies its local shards; these ops must hand back the wrapper
@@ -128,6 +141,9 @@ class WeightWithDynamicFloat8CastTensor(torch.Tensor):
         self._tensor = tensor
         self._linear_mm_config = linear_mm_config
         self._precomputed_scale = precomputed_scale
+        # fp8 bytes of `tensor` under `precomputed_scale`, set by precompute(cast_now=True); like the
+        # scale it lives on this wrapper object only (every op that makes a new wrapper drops it)
+        self._precomputed_fp8 = None
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args, kwargs=None):
@@ -164,6 +180,8 @@ class WeightWithDynamicFloat8CastTensor(torch.Tensor):
 
     @torch.no_grad()  # the transposed copy for backward GEMMs is pointless on a shard
     def fsdp_pre_all_gather(self, mesh):
+        if self._precomputed_scale is not None and self._precomputed_fp8 is not None:
+            return (self._precomputed_fp8.view(torch.uint8),), (self._precomputed_scale,)
         if self._precomputed_scale is not None:
             fp8 = hp_tensor_and_scale_to_float8(
                 self._tensor, self._precomputed_scale, torch.float8_e4m3fn, self._linear_mm_config,

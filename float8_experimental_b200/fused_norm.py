@@ -21,7 +21,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from ._ops import fused_bwd_supported, ops
+from ._ops import ops
 from .float8_tensor import Float8Tensor, GemmInputRole, LinearMMConfig
 from .float8_utils import _kind, e4m3_dtype
 
@@ -45,16 +45,8 @@ class _RMSNormToFloat8(torch.autograd.Function):
         # the cast is transparent to autograd (float8_experimental/float8_tensor.py:193-195); what is
         # left is the RMSNorm backward, in fp32 from the saved x and 1/rms
         x, weight, rstd = ctx.saved_tensors
-        if fused_bwd_supported(x, 8192) and g.dtype == x.dtype:
-            dx, dw = ops.rmsnorm_bwd(x, g, weight, rstd)
-            return dx, dw, None, None, None, None, None
-        cols = x.shape[-1]
-        g32 = g.reshape(-1, cols).float()
-        n = x.reshape(-1, cols).float() * rstd[:, None]
-        dn = g32 * weight.float()
-        dx = rstd[:, None] * (dn - n * (dn * n).mean(-1, keepdim=True))
-        dw = (g32 * n.to(x.dtype).float()).sum(0)
-        return dx.to(x.dtype).reshape(x.shape), dw.to(weight.dtype), None, None, None, None, None
+        dx, dw = ops.rmsnorm_bwd(x, g if g.dtype == x.dtype else g.to(x.dtype), weight, rstd)
+        return dx, dw, None, None, None, None, None
 
 
 def rms_norm_to_float8_dynamic(
@@ -112,15 +104,8 @@ class _SwiGLUToFloat8(torch.autograd.Function):
     def backward(ctx, g):
         # y = silu(a) * b:  dy/db = silu(a),  dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))
         a, b = ctx.saved_tensors
-        if fused_bwd_supported(a) and g.dtype == a.dtype:
-            da, db = ops.swiglu_bwd(a, b, g)
-            return da, db, None, None, None, None, None
-        a32, g32 = a.float(), g.reshape(a.shape).float()
-        sig = torch.sigmoid(a32)
-        silu = a32 * sig
-        da = g32 * b.float() * (sig * (1 + a32 * (1 - sig)))
-        db = g32 * silu.to(a.dtype).float()
-        return da.to(a.dtype), db.to(b.dtype), None, None, None, None, None
+        da, db = ops.swiglu_bwd(a, b, g if g.dtype == a.dtype else g.to(a.dtype))
+        return da, db, None, None, None, None, None
 
 
 def swiglu_to_float8_dynamic(

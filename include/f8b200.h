@@ -128,6 +128,19 @@ int f8b200_cast_scatter(const void* x, int hp_dtype, int64_t rows, int64_t cols,
                         int fp8_kind, void* const* outs, int n_outs, int64_t ld_out, void* stream);
 
 /*
+ * The saturating cast of f8b200_cast(scale_src = 0) for n separate CONTIGUOUS tensors in one
+ * launch: outs[i] = fp8(clamp(RN_P(xs[i] * scales[i]))), numels[i] elements each, scales a device
+ * array of n fp32 words.  `xs`, `numels`, `outs` are HOST arrays of length n (device pointers
+ * inside).  With the scale vector that f8b200_multi_amax + one all-reduce + f8b200_amax_to_scale
+ * produce after an optimizer step, this casts every FSDP weight shard of a model with one launch
+ * (per 96 tensors) instead of one cast per weight per all-gather
+ * (float8_experimental/fsdp_utils.py:168-185, fsdp_pre_all_gather).
+ */
+int f8b200_multi_cast(const void* const* xs, const int64_t* numels, int n, int hp_dtype,
+                      const float* scales, int product_fp32, int fp8_kind, void* const* outs,
+                      void* stream);
+
+/*
  * out[c, r] = in[r, c] for an fp8 (byte) matrix [rows, cols].  Replaces the
  * `.contiguous()` / `.t().contiguous().t()` fix-ups in
  * float8_experimental/float8_ops.py:150-153 when no transposed copy was emitted by
@@ -340,8 +353,9 @@ int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows,
  * f8b200_swiglu_bwd   da = RN_T(RN_T(g * b) * sig(a) * (1 + a * (1 - sig(a)))), db = RN_T(g * RN_T(silu(a))).
  *                     Reads a, b, grad_y, writes da, db with row pitch ld_out (10 bytes per element).
  *
- * Both cover 16-bit dtypes, cols a multiple of 8 (RMSNorm: at most 8192) and 16-byte aligned rows;
- * anything else returns F8B200_ERR_UNSUPPORTED and the caller falls back to framework ops.
+ * Any of the three dtypes, any column count and row pitch: 16-bit dtypes with cols a multiple of 8
+ * (RMSNorm: at most 8192) and 16-byte aligned rows run on the vectorised kernels, everything else on
+ * element-wise variants with the same formulas and roundings.
  */
 int64_t f8b200_rmsnorm_bwd_workspace_bytes(int64_t cols);
 int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtype, int64_t rows, int64_t cols,

@@ -90,7 +90,7 @@ class _MLP(nn.Module):
         return x
 
 
-def case_fsdp2_fp8_all_gather(rank, world, port, precompute):
+def case_fsdp2_fp8_all_gather(rank, world, port, precompute, cast_now=False):
     """FSDP2 with fp8 weight all-gather reproduces, loss for loss, an unsharded float8
     model whose gradients are averaged by hand (the reference's parity criterion,
     test/test_fsdp2/test_fsdp2_common.py:17-54); the all-gather carries 1 byte per
@@ -137,7 +137,7 @@ def case_fsdp2_fp8_all_gather(rank, world, port, precompute):
                         p.grad.div_(world)
                 opt.step()
                 if model is fsdp_model and precompute:
-                    f8.precompute_float8_dynamic_scale_for_fsdp(model)
+                    f8.precompute_float8_dynamic_scale_for_fsdp(model, cast_now=cast_now)
                 losses.append(loss.detach())
             if DEVICE == "cpu":
                 assert torch.equal(losses[0], losses[1]), (step, losses)
@@ -153,6 +153,13 @@ def case_fsdp2_fp8_all_gather(rank, world, port, precompute):
     if precompute:
         w = fsdp_model.layers[0][0].weight._local_tensor
         assert w._precomputed_scale is not None and w._precomputed_scale.dim() == 0
+        assert (w._precomputed_fp8 is not None) == bool(cast_now)
+        if cast_now:  # the cached bytes are the bytes a cast at all-gather time would produce
+            from float8_experimental_b200.float8_tensor import GemmInputRole, hp_tensor_and_scale_to_float8
+
+            again = hp_tensor_and_scale_to_float8(w._tensor, w._precomputed_scale, torch.float8_e4m3fn,
+                                                  w._linear_mm_config, GemmInputRole.WEIGHT)
+            assert torch.equal(again._data.view(torch.uint8), w._precomputed_fp8.view(torch.uint8))
     dist.destroy_process_group()
 
 

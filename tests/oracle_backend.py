@@ -124,6 +124,32 @@ def _rmsnorm_cast(x, weight, rstd, amax, fp8_kind):
     return from_np(bits.reshape(tuple(x.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
 
 
+def _multi_cast_with_scales(xs, scales, fp8_kind, product_fp32):
+    return [_cast_with_scale(x, scales[i], fp8_kind, product_fp32, False, None)[0] for i, x in enumerate(xs)]
+
+
+def _rmsnorm_bwd(x, grad_y, weight, rstd):
+    """Gradient of `RN_T(RN_T(x * rstd) * w)` as eager autograd evaluates it for a tensor of dtype T
+    (float8_experimental/benchmarks/profile_linear_float8.py:69-74), in fp32 from x and 1/rms."""
+    cols = x.shape[-1]
+    g32 = grad_y.reshape(-1, cols).float()
+    n = x.reshape(-1, cols).float() * rstd[:, None]
+    dn = (g32 * weight.float()).to(x.dtype).float()
+    dx = rstd[:, None] * (dn - n * (dn * n).mean(-1, keepdim=True))
+    dw = (g32 * n.to(x.dtype).float()).sum(0)
+    return dx.to(x.dtype).reshape(x.shape), dw.to(weight.dtype)
+
+
+def _swiglu_bwd(a, b, grad_y):
+    """Gradient of `silu(a) * b` (profile_linear_float8.py:117-118):
+    dy/db = silu(a), dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))."""
+    a32, g32 = a.float(), grad_y.reshape(a.shape).float()
+    sig = torch.sigmoid(a32)
+    da = (g32 * b.float()).to(a.dtype).float() * (sig * (1 + a32 * (1 - sig)))
+    db = g32 * (a32 * sig).to(a.dtype).float()
+    return da.to(a.dtype), db.to(b.dtype)
+
+
 def _swiglu_amax(a, b, write_y):
     name = _HP[a.dtype]
     y = O.swiglu(to_np(a), to_np(b), name)
@@ -158,5 +184,8 @@ def install() -> None:
     lib.impl("swiglu_cast", _swiglu_cast, "CPU")
     lib.impl("rmsnorm_amax", _rmsnorm_amax, "CPU")
     lib.impl("rmsnorm_cast", _rmsnorm_cast, "CPU")
+    lib.impl("multi_cast_with_scales", _multi_cast_with_scales, "CPU")
+    lib.impl("rmsnorm_bwd", _rmsnorm_bwd, "CPU")
+    lib.impl("swiglu_bwd", _swiglu_bwd, "CPU")
     install._lib = lib  # keep the registrations alive
     _installed = True

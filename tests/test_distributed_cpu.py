@@ -40,6 +40,12 @@ def test_fsdp2_fp8_all_gather_matches_unsharded(precompute):
     _run("case_fsdp2_fp8_all_gather", precompute)
 
 
+def test_fsdp2_precompute_that_also_casts_all_shards_at_once():
+    """precompute(cast_now=True): one multi-tensor cast after the optimizer step, the all-gathers
+    hand over the cached bytes; still loss for loss the unsharded model."""
+    _run("case_fsdp2_fp8_all_gather", True, True)
+
+
 def test_fsdp2_delayed_weight_scaling():
     _run("case_fsdp2_delayed")
 

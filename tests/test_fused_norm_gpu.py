@@ -144,6 +144,33 @@ def test_fused_norm_backward_kernel_matches_eager_autograd(dtype, shape):
     assert _sqnr(w2.grad, w.grad) > (40 if dtype == torch.bfloat16 else 55)
 
 
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (64, 1024)), (torch.float32, (5, 33)),
+                                         (torch.bfloat16, (40, 1001)), (torch.float16, (9, 12288)),
+                                         (torch.bfloat16, (24, 8200))])
+def test_fused_norm_backward_generic_shapes(dtype, shape):
+    """fp32 tensors, column counts that are not multiples of 8 and rows wider than 8192 run on the
+    element-wise backward kernels: same formulas, same tolerances (fp32: only summation order differs)."""
+    torch.manual_seed(shape[-1])
+    x = (torch.randn(shape, device="cuda") * 2).to(dtype).requires_grad_(True)
+    w = (1 + 0.2 * torch.randn(shape[-1], device="cuda")).to(dtype).requires_grad_(True)
+    g = torch.randn(shape, device="cuda").to(dtype)
+    rms_norm_to_float8_dynamic(x, w, 1e-6).backward(g)
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    reference_rmsnorm(x2, w2, 1e-6).backward(g)
+    floor = {torch.float32: 100, torch.bfloat16: 40, torch.float16: 55}[dtype]
+    assert x.grad.dtype == dtype and w.grad.dtype == dtype
+    assert _sqnr(x2.grad, x.grad) > floor + (5 if dtype != torch.float32 else 0)
+    assert _sqnr(w2.grad, w.grad) > floor
+    # the gate's backward on the same kinds of shapes
+    a = (torch.randn(shape, device="cuda") * 2).to(dtype).requires_grad_(True)
+    b = torch.randn(shape, device="cuda").to(dtype).requires_grad_(True)
+    swiglu_to_float8_dynamic(a, b).backward(g)
+    a2, b2 = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    (torch.nn.functional.silu(a2) * b2).backward(g)
+    for got, ref in ((a.grad, a2.grad), (b.grad, b2.grad)):
+        assert got.dtype == dtype and _sqnr(ref, got) > floor + (10 if dtype != torch.float32 else 0)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(512, 4096), (3, 40, 264)])
 def test_fused_swiglu_backward_kernel_matches_eager_autograd(dtype, shape):

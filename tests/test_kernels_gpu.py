@@ -182,6 +182,32 @@ def test_delayed_sync_matches_reference(golden_dir):
         assert np.array_equal(h.cpu().numpy(), rolled)
 
 
+@pytest.mark.parametrize("dname", [O.BF16, O.FP16, O.FP32])
+def test_multi_tensor_cast_matches_single_casts(dname):
+    """One launch casting many contiguous tensors, each with its own scale, returns the bytes of
+    one f8b200_cast per tensor (which are pinned against the reference): every size class (empty,
+    shorter than a vector, ragged tails, large), more tensors than one launch holds, both
+    product-rounding routes."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    sizes = [0, 1, 7, 8, 9, 1000, 4096, 12345, 1 << 20, 3 * 1024 * 512 + 5] + [257 + 13 * i for i in range(100)]
+    xs = [(torch.randn(n, device="cuda", generator=g) * (1 + i % 5)).to(DT[dname]) for i, n in enumerate(sizes)]
+    scales = (torch.rand(len(sizes), device="cuda", generator=g) * 100 + 0.5).to(DT[dname]).float()
+    for product_fp32 in (False, True):
+        outs = [torch.full((n,), 0x55, dtype=torch.uint8, device="cuda") for n in sizes]
+        N.multi_cast(xs, scales, product_fp32, N.E4M3, outs)
+        torch.cuda.synchronize()
+        for i, (x, n) in enumerate(zip(xs, sizes)):
+            if n == 0:
+                continue
+            want = torch.empty(1, n, dtype=torch.uint8, device="cuda")
+            N.cast(x.view(1, n), 1, n, n, 0, scales[i:i + 1], None, product_fp32, N.E4M3, want, n, None, 0, None, False)
+            assert torch.equal(outs[i], want[0]), (dname, product_fp32, i, n)
+        # and against the oracle directly on one of them
+        i = 5
+        ref = O.cast_to_fp8(host_bits(xs[i]), dname, np.float32(scales[i].item()), O.E4M3, O.FP32 if product_fp32 else dname)
+        assert nan_class_equal(outs[i].cpu().numpy(), ref)
+
+
 def test_transpose_u8():
     for shape in ((128, 128), (130, 260), (5, 3), (1024, 16), (16, 1024)):
         x = torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda")
