@@ -269,7 +269,8 @@ def gemm_sweep(variants, shapes=None, seconds: float = 0.6, emit=None):
     larger than the differences between variants): every GEMM of the step runs for `seconds` with
     each variant in turn.  Variants: 2cta, pw, 1cta, wide (kernels of libf8b200.so), mc21 / mc22 /
     mc41 (the single-GPU multicast library), auto (the default choice), cublaslt (torch._scaled_mm);
-    suffix -static = fixed tile stride, -direct = per-thread store epilogue.  Returns (rows,
+    suffix -static = fixed tile stride, -direct = per-thread store epilogue, -tma / -smem = TMA-store epilogue /
+    warp-written whole lines after staging in shared memory (default: TMA stores).  Returns (rows,
     totals_ms); `emit(row)` is called per GEMM."""
     import torch
 
@@ -292,7 +293,8 @@ def gemm_sweep(variants, shapes=None, seconds: float = 0.6, emit=None):
                     base = v.split("-")[0]
                     os.environ["F8B200_GEMM_MC"] = base[2:] if base.startswith("mc") else "0"
                     os.environ["F8B200_GEMM_MODE"] = "" if base in ("auto", "mc21", "mc22", "mc41") else base
-                    os.environ["F8B200_GEMM_STORE"] = "direct" if v.endswith("-direct") else "tma"
+                    os.environ["F8B200_GEMM_STORE"] = ("direct" if v.endswith("-direct") else
+                                                       "tma" if v.endswith("-tma") else "smem" if v.endswith("-smem") else "")
                     os.environ["F8B200_GEMM_WS"] = "0" if v.endswith("-static") else "1"
                     if base == "auto":
                         os.environ.pop("F8B200_GEMM_MC", None)

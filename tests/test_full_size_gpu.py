@@ -76,10 +76,11 @@ FULL_GEMMS = {
 }
 
 
-@pytest.mark.parametrize("mode", ["2cta", "wide", "pw"])
+@pytest.mark.parametrize("mode", ["2cta", "wide", "pw", "pw-smem"])
 @pytest.mark.parametrize("name", list(FULL_GEMMS))
 def test_long_gemms_on_sampled_rows_and_columns(name, mode, monkeypatch):
-    monkeypatch.setenv("F8B200_GEMM_MODE", mode)
+    monkeypatch.setenv("F8B200_GEMM_MODE", mode.split("-")[0])
+    monkeypatch.setenv("F8B200_GEMM_STORE", "smem" if mode.endswith("-smem") else "")
     m, n, k, a_dt = FULL_GEMMS[name]
     g = torch.Generator(device="cuda").manual_seed(m + n + k)
     a = torch.randn(m, k, device="cuda", generator=g).mul_(0.5).to(a_dt)

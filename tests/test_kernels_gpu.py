@@ -217,11 +217,13 @@ def test_transpose_u8():
 
 
 # ---------------------------------------------------------------------------
-@pytest.fixture(params=["2cta", "1cta", "wide", "pw", "2cta-direct", "1cta-direct", "wide-direct", "pw-direct"])
+@pytest.fixture(params=["2cta", "1cta", "wide", "pw", "2cta-direct", "1cta-direct", "wide-direct", "pw-direct",
+                        "wide-smem", "pw-smem"])
 def gemm_mode(request, monkeypatch):
     """The four GEMM kernels (CTA pairs on 256x256 tiles; one CTA per 128x256 tile; one CTA per
     256x256 tile; CTA pairs on 512x256 tiles), each with the TMA-store epilogue and with the
-    per-thread store epilogue."""
+    per-thread store epilogue; the two kernels whose accumulator fills tensor memory also with
+    their third epilogue (whole lines written by the warps after staging in shared memory)."""
     mode, _, store = request.param.partition("-")
     monkeypatch.setenv("F8B200_GEMM_MODE", mode)
     monkeypatch.setenv("F8B200_GEMM_STORE", store or "tma")

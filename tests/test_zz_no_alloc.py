@@ -47,6 +47,22 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(mnk):
     assert torch.equal(second.view(torch.int16), want.view(torch.int16))
 
 
+def test_refused_and_empty_calls_take_no_slot():
+    """A call that fails its argument checks, or has nothing to compute, neither looks the array up
+    nor claims one of the 16 per-stream slots: twenty such calls on twenty fresh streams leave room
+    for the streams of the next test."""
+    a, b, sa, sb = _operands(256, 256, 128, seed=9)
+    out = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    for _ in range(20):
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            with pytest.raises(N.F8B200Error, match="bad argument"):
+                N.gemm_fp8_static_scratch(a, 64, b, 128, sa, sb, None, out, 256, 256, 256, 128, False)  # lda < k
+            N.gemm_fp8_static_scratch(a, 128, b, 128, sa, sb, None, out, 256, 0, 256, 128, False)      # m == 0
+    torch.cuda.synchronize()
+    assert N.read_device_error() == 0
+
+
 def test_static_scratch_refuses_more_streams_than_slots():
     a, b, sa, sb = _operands(512, 512, 128, seed=3)
     out = torch.empty(512, 512, dtype=torch.bfloat16, device="cuda")
