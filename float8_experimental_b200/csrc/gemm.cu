@@ -1682,6 +1682,16 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 // box = [128 k rows] x [128 bytes of rows], 128B swizzle.
 static int encode_operand_map_mn(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld);
 
+// L2 promotion of the operand maps: how much L2 fetches from HBM around a requested 128-byte row piece.
+// 256 bytes (the next k-block of the same row comes along) is the default; F8B200_GEMM_L2PROMO=0/64/128/256.
+static CUtensorMapL2promotion operand_l2_promotion() {
+  const char* e = getenv("F8B200_GEMM_L2PROMO");
+  if (e == nullptr || e[0] == 0) return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  const int v = atoi(e);
+  return v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+       : v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
+
 // 2-D byte tensor [rows, k] with row stride ld, box = [box_rows, 128 bytes], 128B swizzle.
 static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
   auto fn = get_encode_fn();
@@ -1691,7 +1701,7 @@ static int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, 
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, operand_l2_promotion(),
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
 }
@@ -1704,7 +1714,7 @@ static int encode_operand_map_mn(CUtensorMap* map, const void* base, int64_t row
   const cuuint32_t box[2] = {128u, (cuuint32_t)BK};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, operand_l2_promotion(),
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? F8B200_OK : F8B200_ERR_DRIVER;
 }

@@ -200,3 +200,4 @@ def sync_float8_amax_and_scale_history(model: torch.nn.Module, fp8_layers=None) 
     )
     for m in fp8_layers:
         m.amax_and_scale_synced = True
+    N.poll_errors_if_enabled()

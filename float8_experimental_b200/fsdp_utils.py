@@ -79,6 +79,7 @@ def precompute_float8_dynamic_scale_for_fsdp(module: nn.Module, cast_now: bool =
         w = m.weight._local_tensor
         w._precomputed_scale = scales[i]
         w._precomputed_fp8 = fp8_shards[i] if fp8_shards is not None else None
+    N.poll_errors_if_enabled()
 
 
 # FSDP pads, slices and copies its local shards; these ops must hand back the wrapper

@@ -265,9 +265,12 @@ int f8b200_gemm_kernel_choice(int64_t m, int64_t n, int64_t k);
  * cannot pass device memory of their own.  It allocates and frees nothing, on the host or the
  * device, and returns the same bits as f8b200_gemm_fp8 / f8b200_gemm_fp8_ws.
  *
- *   set-up      The first call on each device looks the array up with cudaGetSymbolAddress and
- *               keeps the address.  That call must happen outside any stream capture; make one
- *               call per device before capturing a CUDA graph that contains this entry point.
+ *   set-up      The first call on each device that passes the argument checks looks the array up
+ *               with cudaGetSymbolAddress and keeps the address.  That call must happen outside any
+ *               stream capture; make one call per device before capturing a CUDA graph that
+ *               contains this entry point.  A lookup that fails is not remembered: the next call
+ *               tries again.  Calls that fail their argument checks or have nothing to compute
+ *               (m == 0 or n == 0) neither look the array up nor take a slot.
  *   size limit  A stream gets its slot at its first call and keeps it for the life of the
  *               process (slots are not recycled when a stream is destroyed; a new stream that
  *               happens to get the same handle reuses the old slot, which is safe).  The array
