@@ -691,12 +691,13 @@ rmsnorm_bwd_kernel(const char* __restrict__ x, int64_t ldx_bytes, const char* __
                    char* __restrict__ dx, int64_t lddx_bytes, float* __restrict__ dw_partial) {
   __shared__ float red[kNormThreads / 32];
   const int chunks = (int)(cols / 8);
-  uint4 wq[CH];
+  // The weight row (at most 16 KB) is re-read from L1 for every row instead of being held in registers:
+  // with the packed rows of x and g (2 x CH x 4 registers) and the CH x 8 dw accumulators that keeps the
+  // 8192-column instantiation inside the 128 registers two CTAs per SM allow (it used to spill).
+  const uint4* wrow = reinterpret_cast<const uint4*>(weight);
   float dw[CH][8];
 #pragma unroll
   for (int i = 0; i < CH; ++i) {
-    const int c = threadIdx.x + i * kNormThreads;
-    wq[i] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(weight) + c) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw[i][j] = 0.0f;
   }
@@ -715,10 +716,11 @@ rmsnorm_bwd_kernel(const char* __restrict__ x, int64_t ldx_bytes, const char* __
     float dot = 0.0f;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
       float xv[8], gv[8], wv[8];
       widen8<HP>(qx[i], xv);
       widen8<HP>(qg[i], gv);
-      widen8<HP>(wq[i], wv);
+      widen8<HP>(c < chunks ? __ldg(wrow + c) : make_uint4(0u, 0u, 0u, 0u), wv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float n = xv[j] * rstd;
@@ -735,7 +737,7 @@ rmsnorm_bwd_kernel(const char* __restrict__ x, int64_t ldx_bytes, const char* __
         float xv[8], gv[8], wv[8], o[8];
         widen8<HP>(qx[i], xv);
         widen8<HP>(qg[i], gv);
-        widen8<HP>(wq[i], wv);
+        widen8<HP>(__ldg(wrow + c), wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (round_hp<HP>(gv[j] * wv[j]) - xv[j] * rstd * cmean);
         orow[c] = make_uint4(pack_round2<HP>(o[0], o[1]), pack_round2<HP>(o[2], o[3]), pack_round2<HP>(o[4], o[5]),
