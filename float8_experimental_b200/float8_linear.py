@@ -8,6 +8,8 @@ from typing import Optional
 
 import torch
 
+from . import _native as N
+from ._ops import ops
 from .config import Float8LinearConfig, ScalingType
 from .float8_scaling_utils import (
     _maybe_initialize_amaxes_scales_for_float8_cast,
@@ -48,6 +50,58 @@ class manual_float8_matmul(torch.autograd.Function):
         x2d = input_fp8.reshape(-1, input_fp8.shape[-1])
         grad_weight = torch.mm(go2d.t(), x2d)
         return grad_input, grad_weight.t()
+
+
+def _inner_dim_ok(k: int, mm_cfg: ScaledMMConfig) -> None:
+    if k % 16 != 0 and not mm_cfg.pad_inner_dim:
+        # same contract as the reference, whose cuBLASLt path needs K % 16 == 0 unless it pads
+        raise RuntimeError(
+            f"float8 GEMM needs the inner dimension to be a multiple of 16, got {k}; "
+            "set Float8LinearConfig.pad_inner_dim=True"
+        )
+
+
+@torch._dynamo.allow_in_graph
+class _float8_linear_dynamic(torch.autograd.Function):
+    """Forward + backward of a Float8Linear whose three tensors use dynamic scaling, for plain CUDA
+    tensors: the same kernels with the same arguments in the same order as the general route
+    (amax, cast, GEMM for the output; amax, cast and two GEMMs for the gradients), launched from
+    ONE autograd node on raw tensors.  The general route builds three `Float8Tensor`s, runs
+    three extra autograd nodes and goes through `__torch_dispatch__` for every product; with
+    hundreds of small layers per step that host work, not the GPU, sets the step time.  Results
+    are bit-identical to the general route (`test_fast_path_matches_general_route`)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, mm_cfg: LinearMMConfig):
+        lead, k = x.shape[:-1], x.shape[-1]
+        x2 = x.reshape(-1, k)
+        _inner_dim_ok(k, mm_cfg.output)
+        x8, _, sx = ops.cast_from_amax(x2, ops.amax(x2), N.E4M3, False)
+        if isinstance(weight, Float8Tensor):  # FSDP2 delivered fp8 bytes and their scale
+            w8, sw = weight._data, weight._scale
+        else:
+            w8, _, sw = ops.cast_from_amax(weight, ops.amax(weight), N.E4M3, False)
+        y = ops.scaled_mm(x8, w8, sx, sw, None, x.dtype, mm_cfg.output.use_fast_accum)
+        ctx.save_for_backward(x8, sx, w8, sw)
+        ctx.mm_cfg = mm_cfg
+        return y.reshape(*lead, y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, go):
+        x8, sx, w8, sw = ctx.saved_tensors
+        cfg = ctx.mm_cfg
+        lead, n = go.shape[:-1], go.shape[-1]
+        go2 = go.reshape(-1, n)
+        g8, _, sg = ops.cast_from_amax(go2, ops.amax(go2), N.E5M2, False)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:  # dX = dY @ W: W [N, K] read as the transposed operand it is
+            _inner_dim_ok(n, cfg.grad_input)
+            dx = ops.scaled_mm(g8, w8.t(), sg, sw, None, go.dtype, cfg.grad_input.use_fast_accum)
+            dx = dx.reshape(*lead, dx.shape[-1])
+        if ctx.needs_input_grad[1]:  # dW = dY^T @ X: both operands read where they lie
+            _inner_dim_ok(g8.shape[0], cfg.grad_weight)
+            dw = ops.scaled_mm(g8.t(), x8.t(), sg, sx, None, go.dtype, cfg.grad_weight.use_fast_accum)
+        return dx, dw, None
 
 
 class Float8Linear(torch.nn.Linear):
@@ -183,7 +237,32 @@ class Float8Linear(torch.nn.Linear):
         self.is_amax_initialized = True
         self.amax_and_scale_synced = False
 
+    def _single_node_route(self, input: torch.Tensor) -> bool:
+        """Whether this call can take `_float8_linear_dynamic`: dynamic scaling throughout, a plain
+        tensor as input (not a DTensor, not already float8), a plain or FSDP2-delivered float8 weight,
+        no autocast, no transposed copies asked for.  F8B200_LINEAR_SINGLE_NODE=0 switches it off."""
+        if self.has_any_delayed_scaling or self._rowwise_reduce_scatter is not None:
+            return False
+        if type(input) is not torch.Tensor or torch.is_autocast_enabled(input.device.type):
+            return False
+        w = self.weight
+        if not (type(w) in (torch.nn.Parameter, torch.Tensor) or isinstance(w, Float8Tensor)):
+            return False
+        if isinstance(w, Float8Tensor) and (w._data.dim() != 2 or w._orig_dtype != input.dtype):
+            return False
+        if not isinstance(w, Float8Tensor) and w.dtype != input.dtype:
+            return False
+        import os
+
+        return os.environ.get("F8B200_LINEAR_SINGLE_NODE", "1") != "0" and \
+            os.environ.get("F8B200_CAST_TRANSPOSED", "0") != "1"
+
     def forward(self, input: torch.Tensor) -> torch.Tensor:
+        if self._single_node_route(input):
+            output = _float8_linear_dynamic.apply(input, self.weight, self.linear_mm_config)
+            if self.bias is not None:
+                output = output + self.bias.to(output.dtype)
+            return output
         if self.has_any_delayed_scaling:
             self.float8_pre_forward(input)
         input_fp8 = self.cast_input_to_float8(input, self.is_amax_initialized)

@@ -300,11 +300,16 @@ def test_mm_config_mismatch_message():
         torch.mm(a, b.t())
 
 
-def test_gemms_read_the_cast_outputs_where_they_lie(monkeypatch):
+@pytest.mark.parametrize("single_node", ["1", "0"])
+def test_gemms_read_the_cast_outputs_where_they_lie(monkeypatch, single_node):
     """Forward, dgrad and wgrad hand the GEMM views of the three cast results: no transposed
-    or contiguous copy of an fp8 tensor is made on the way."""
+    or contiguous copy of an fp8 tensor is made on the way, on the single-node route as on the
+    general one."""
+    import float8_experimental_b200.float8_linear as fl
     import float8_experimental_b200.float8_python_api as api
     import float8_experimental_b200.float8_tensor as ft
+
+    monkeypatch.setenv("F8B200_LINEAR_SINGLE_NODE", single_node)
 
     cast_ptrs, operand_ptrs = set(), []
 
@@ -330,8 +335,13 @@ def test_gemms_read_the_cast_outputs_where_they_lie(monkeypatch):
         if name == "scaled_mm":
             operand_ptrs.extend([args[0].data_ptr(), args[1].data_ptr()])
 
+    def on_both(name, args, out):
+        on_cast(name, args, out)
+        on_mm(name, args, out)
+
     monkeypatch.setattr(ft, "ops", Spy(on_cast))
     monkeypatch.setattr(api, "ops", Spy(on_mm))
+    monkeypatch.setattr(fl, "ops", Spy(on_both))
     m = make_linear(torch.randn(48, 32, dtype=torch.bfloat16), f8.Float8LinearConfig())
     x = torch.randn(2, 8, 32, dtype=torch.bfloat16, requires_grad=True)
     m(x).sum().backward()
@@ -451,3 +461,51 @@ def test_single_gpu_job_rules(monkeypatch):
     monkeypatch.setattr(torch.distributed, "is_initialized", lambda: True)
     monkeypatch.setattr(torch.distributed, "get_world_size", lambda *a, **k: 2)
     assert not N._single_gpu_job()
+
+
+def test_single_node_route_matches_general_route(monkeypatch):
+    """A dynamic-scaling Float8Linear on plain tensors runs as ONE autograd node on raw tensors; with
+    F8B200_LINEAR_SINGLE_NODE=0 it takes the general route (Float8Tensor operands, one node per cast
+    and per product).  Same kernels, same arguments: outputs and gradients are bit-identical, with and
+    without bias, for 2-D and 3-D inputs, and when only one of the two gradients is needed."""
+    import copy
+
+    import torch
+    import torch.nn as nn
+
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.float8_linear import Float8Linear
+
+    torch.manual_seed(3)
+    for bias, shape in ((False, (32, 64)), (True, (2, 16, 64))):
+        lin = nn.Linear(64, 48, bias=bias).to(torch.bfloat16)
+        x = torch.randn(*shape).to(torch.bfloat16)
+        go = (torch.randn(*shape[:-1], 48) * 1e-2).to(torch.bfloat16)
+        results = []
+        for route in ("1", "0"):
+            monkeypatch.setenv("F8B200_LINEAR_SINGLE_NODE", route)
+            m = Float8Linear.from_float(copy.deepcopy(lin), f8.Float8LinearConfig())
+            assert m._single_node_route(x) == (route == "1")
+            xr = x.clone().requires_grad_(True)
+            y = m(xr)
+            y.backward(go)
+            results.append((y.detach(), xr.grad, m.weight.grad, m.bias.grad if bias else None))
+        for a, b in zip(*results):
+            assert (a is None and b is None) or torch.equal(a, b)
+    # frozen weight: only the input gradient is computed
+    monkeypatch.setenv("F8B200_LINEAR_SINGLE_NODE", "1")
+    m = Float8Linear.from_float(nn.Linear(64, 48, bias=False).to(torch.bfloat16), f8.Float8LinearConfig())
+    m.weight.requires_grad_(False)
+    xr = torch.randn(16, 64).to(torch.bfloat16).requires_grad_(True)
+    m(xr).sum().backward()
+    assert xr.grad is not None and m.weight.grad is None
+    # delayed scaling, autocast and DTensor inputs keep the general route
+    d = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    md = Float8Linear.from_float(nn.Linear(64, 48), f8.Float8LinearConfig(cast_config_input=d))
+    assert not md._single_node_route(torch.randn(4, 64))
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        assert not m._single_node_route(xr.detach())
+    # K that is not a multiple of 16 is refused exactly as on the general route
+    odd = Float8Linear.from_float(nn.Linear(72, 48, bias=False).to(torch.bfloat16), f8.Float8LinearConfig())
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        odd(torch.randn(16, 72).to(torch.bfloat16))

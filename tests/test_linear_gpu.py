@@ -257,6 +257,30 @@ def test_inference_linear_against_the_oracle():
     assert N_native.read_device_error() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_single_node_route_matches_general_route(dtype, monkeypatch):
+    """The single autograd node that runs a dynamic-scaling Float8Linear on raw tensors launches the
+    kernels of the general route with the same arguments: y, dX, dW and db are bit-identical."""
+    import copy
+
+    torch.manual_seed(17)
+    lin = nn.Linear(1024, 768, bias=True, device="cuda", dtype=dtype)
+    x = torch.randn(4, 96, 1024, device="cuda", dtype=dtype)
+    go = torch.randn(4, 96, 768, device="cuda", dtype=dtype) * 1e-2
+    results = []
+    for route in ("1", "0"):
+        monkeypatch.setenv("F8B200_LINEAR_SINGLE_NODE", route)
+        m = Float8Linear.from_float(copy.deepcopy(lin), f8.Float8LinearConfig())
+        assert m._single_node_route(x) == (route == "1")
+        xr = x.clone().requires_grad_(True)
+        y = m(xr)
+        y.backward(go)
+        results.append((y.detach(), xr.grad, m.weight.grad, m.bias.grad))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert N_native.read_device_error() == 0
+
+
 def test_autocast_sets_the_output_dtype():
     """Under autocast the input is cast to the autocast dtype and the output follows it
     (reference: test/test_base.py:268-317)."""
