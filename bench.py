@@ -481,7 +481,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             torch.cuda.synchronize()
             return {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
-    delayed = fused_norm = gemm_vs_cublaslt = fp8_peak_measured = reference_gpu = None
+    delayed = fused_norm = gemm_vs_cublaslt = fp8_peak_measured = reference_gpu = llama3_one_gpu = None
     comm_split = tp_sp_ffn = llama3_fsdp = cast_all_gather = None
     full = args.layers is None and not args.quick
     if world == 1 and rank == 0:
@@ -521,6 +521,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                 first_error = reference_gpu["error"]
                 reference_gpu = side(single_gpu.measure_reference_gpu_path, torch, dev, 5, None)
                 reference_gpu["reference_module_error"] = first_error
+            ref_convert = None
+            if ref_linear is not None:
+                from float8_experimental.float8_linear_utils import convert_to_float8_training as ref_convert
+            llama3_one_gpu = side(single_gpu.measure_llama3_8b_linears, torch, dev, 3, 32, 8192, ref_convert)
     if world > 1 and full:
         # the tensor / sequence parallel and the Llama-3-8B FSDP2 configurations (all ranks take part)
         tp_sp_ffn = side(multi_gpu.measure_tp_sp_ffn, dev, rank, world)
@@ -630,6 +634,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         "reference_gpu_path": reference_gpu,
         "vs_reference_gpu_path": (reference_gpu["ms_per_step"] / ms_per_step
                                   if isinstance(reference_gpu, dict) and "ms_per_step" in reference_gpu else None),
+        "llama3_8b_linears": llama3_one_gpu,
         "delayed_scaling": delayed,
         "fused_rmsnorm_cast": fused_norm,
         "cpu_baseline": cpu_baseline,

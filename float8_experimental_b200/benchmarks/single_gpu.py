@@ -413,3 +413,73 @@ def measure_reference_gpu_path(torch, dev, steps: int = 5, reference_linear=None
             "kind": "reference module (Float8Linear of the reference, emulate=False)" if reference_linear is not None
                     else "eager operator sequence of the reference, restated with torch ops",
             "what": "eager abs/max, scale, mul, clamp, .to(fp8), transposed copies, torch._scaled_mm x3 per layer"}
+
+
+def measure_llama3_8b_linears(torch, dev, steps: int = 3, n_blocks: int = 32, seq: int = 8192, reference_convert=None):
+    """The 224 float8 linears of a Llama-3-8B-shaped decoder (32 blocks x 7 linears, seq 8192, batch 1)
+    on one GPU, forward + backward: many small layers per step, where the host work per layer counts as
+    much as the kernels.  `reference_convert(model)`, when given, converts a second copy of the model with
+    the reference's own `convert_to_float8_training` for the same measurement."""
+    import float8_experimental_b200 as f8
+
+    from .models import Llama3Block
+
+    per_block = 4096 * 4096 * 2 + 4096 * 1024 * 2 + 3 * 4096 * 14336
+    flops = 6.0 * seq * per_block * n_blocks
+    g = torch.Generator(device=dev).manual_seed(200)
+    x = torch.randn(1, seq, 4096, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
+    go = torch.randn(1, seq, 4096, device=dev, dtype=torch.bfloat16, generator=g) * 1e-3
+    out = {"blocks": n_blocks, "linears": 7 * n_blocks, "tokens": seq, "flops_per_step": flops}
+
+    def build():
+        torch.manual_seed(11)
+        blocks = []
+        for _ in range(n_blocks):
+            blk = Llama3Block().to(device=dev, dtype=torch.bfloat16)
+            for p in blk.parameters():
+                torch.nn.init.normal_(p, 0.0, 0.02)
+            blocks.append(blk)
+        return torch.nn.Sequential(*blocks)
+
+    def timed(model):
+        def step():
+            x.grad = None
+            for p in model.parameters():
+                p.grad = None
+            model(x).backward(go)
+
+        for _ in range(2):
+            step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        host_ms = (time.perf_counter() - t0) / steps * 1e3  # time to ENQUEUE a step: above the device time = host-bound
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"ms_per_step": ms, "tflops": flops / ms / 1e9, "host_enqueue_ms_per_step": host_ms}
+
+    model = build()
+    f8.convert_to_float8_training(model, config=f8.Float8LinearConfig())
+    out["ours"] = timed(model)
+    os.environ["F8B200_LINEAR_SINGLE_NODE"] = "0"
+    try:
+        out["ours_general_route"] = timed(model)
+    finally:
+        os.environ.pop("F8B200_LINEAR_SINGLE_NODE", None)
+    del model
+    torch.cuda.empty_cache()
+    if reference_convert is not None:
+        try:
+            ref = build()
+            reference_convert(ref)
+            out["reference_module"] = timed(ref)
+            del ref
+        except Exception as exc:  # noqa: BLE001
+            torch.cuda.synchronize()
+            out["reference_module"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+    return out
