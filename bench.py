@@ -417,18 +417,35 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
 
         hook_handles = [layer.register_forward_pre_hook(_make_hook(i)) for i, layer in enumerate(layers)]
 
+    # Without FSDP the layers are independent: each layer's input and gradient are copied together and the
+    # layers run in descending order of work, so that what is left to compute after the last copy has
+    # landed (the step is bound by the host link) is the smallest layer.  Under the FSDP2 root the forward of
+    # all layers precedes the backward: inputs are copied first, gradients after them.
+    order = sorted(range(len(layers)), key=lambda i: -layer_flops(shapes[i][1], shapes[i][2]))
+
     def e2e_step():
         main = torch.cuda.current_stream()
         copy_stream.wait_stream(main)  # previous step's readers are done with the buffers
         with torch.cuda.stream(copy_stream):
-            for i, ((hx, _), x) in enumerate(zip(host, xs)):
-                x.detach().copy_(hx, non_blocking=True)
+            def copy_x(i):
+                xs[i].detach().copy_(host[i][0], non_blocking=True)
                 x_ready[i] = torch.cuda.Event()
                 x_ready[i].record(copy_stream)
-            for i, ((_, hg), go) in enumerate(zip(host, gos)):
-                go.copy_(hg, non_blocking=True)
+
+            def copy_go(i):
+                gos[i].copy_(host[i][1], non_blocking=True)
                 go_ready[i] = torch.cuda.Event()
                 go_ready[i].record(copy_stream)
+
+            if fsdp and args.fsdp_root:
+                for i in range(len(layers)):
+                    copy_x(i)
+                for i in reversed(range(len(layers))):  # backward runs from the last layer to the first
+                    copy_go(i)
+            else:
+                for i in order:
+                    copy_x(i)
+                    copy_go(i)
         for layer, x in zip(layers, xs):
             x.grad = None
             layer.weight.grad = None
@@ -439,12 +456,12 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             torch.autograd.backward(outs, gos)
             f8.precompute_float8_dynamic_scale_for_fsdp(holder)
         else:
-            for i, (layer, x, go) in enumerate(zip(layers, xs, gos)):
+            for i in order:
                 if not fsdp:
                     main.wait_event(x_ready[i])
-                y = layer(x)
+                y = layers[i](xs[i])
                 main.wait_event(go_ready[i])
-                y.backward(go)
+                y.backward(gos[i])
             if fsdp:
                 f8.precompute_float8_dynamic_scale_for_fsdp(holder)
         for i, layer in enumerate(layers):

@@ -30,6 +30,7 @@ EXPORTS = (
     "f8b200_multi_amax",
     "f8b200_amax_to_scale",
     "f8b200_cast",
+    "f8b200_cast_dynamic",
     "f8b200_cast_scatter",
     "f8b200_multi_cast",
     "f8b200_transpose_u8",
@@ -83,6 +84,7 @@ def load() -> ctypes.CDLL:
     lib.f8b200_cast.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, vp, i64, vp, i64, vp, i32, vp]
     lib.f8b200_cast_scatter.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, ctypes.POINTER(vp), i32, i64,
                                         vp]
+    lib.f8b200_cast_dynamic.argtypes = [vp, i32, i64, i64, i32, vp, vp, vp, vp]
     lib.f8b200_multi_cast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(i64), i32, i32, vp, i32, i32, ctypes.POINTER(vp), vp]
     lib.f8b200_transpose_u8.argtypes = [vp, i64, i64, i64, vp, i64, vp]
     lib.f8b200_delayed_sync.argtypes = [vp, vp, i64, i64, i32, i64, i32, vp, vp, i64, vp]
@@ -255,6 +257,15 @@ def cast(x: torch.Tensor, rows: int, cols: int, ld_x: int, scale_src: int, scale
                                ld_out_t, _ptr(amax_out), int(reverse), _stream(x)),
             "f8b200_cast",
         )
+
+
+def cast_dynamic(x: torch.Tensor, rows: int, cols: int, fp8_kind: int, amax_out: torch.Tensor, scale_out: torch.Tensor,
+                 out: torch.Tensor) -> None:
+    """`f8b200_cast_dynamic`: amax + cast of a contiguous matrix in one host call (two launches)."""
+    _require_cuda(x, amax_out, scale_out, out)
+    with _Launch("cast", x.device, 2):
+        _check(load().f8b200_cast_dynamic(x.data_ptr(), hp_code(x.dtype), rows, cols, fp8_kind, amax_out.data_ptr(),
+                                          scale_out.data_ptr(), out.data_ptr(), _stream(x)), "f8b200_cast_dynamic")
 
 
 def multi_cast(xs: Sequence[torch.Tensor], scales: torch.Tensor, product_fp32: bool, fp8_kind: int,

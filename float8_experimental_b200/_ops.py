@@ -11,6 +11,7 @@ Ops (namespace `f8b200`):
   amax_to_scale(amax, kind, amax_dtype, orig_dtype)       f8b200_amax_to_scale
   cast_from_amax(x, amax, kind, with_t) -> (data, data_t, scale)   f8b200_cast, scale_src=1
   cast_with_scale(x, scale, kind, product_fp32, with_t, amax_out!) -> (data, data_t)
+  cast_dynamic(x, kind) -> (data, scale)                  f8b200_cast_dynamic (amax + cast, one call)
   multi_cast_with_scales(xs, scales, kind, product_fp32) -> fp8 tensors   f8b200_multi_cast
   transpose_fp8(x) -> x^T contiguous                      f8b200_transpose_u8
   delayed_sync(amax, hist, n_e4m3, orig_dtype, scale_out!, hist_out!)
@@ -38,6 +39,7 @@ _lib.define(
     "cast_with_scale(Tensor x, Tensor scale, int fp8_kind, bool product_fp32, bool with_transpose, "
     "Tensor(a!)? amax_out) -> (Tensor, Tensor)"
 )
+_lib.define("cast_dynamic(Tensor x, int fp8_kind) -> (Tensor, Tensor)")
 _lib.define("multi_cast_with_scales(Tensor[] xs, Tensor scales, int fp8_kind, bool product_fp32) -> Tensor[]")
 _lib.define("transpose_fp8(Tensor x) -> Tensor")
 _lib.define(
@@ -125,6 +127,20 @@ def _cast_with_scale_cuda(x, scale, fp8_kind: int, product_fp32: bool, with_tran
     N.cast(xm, rows, cols, ld, 0, s, None, product_fp32, fp8_kind, data, cols,
            data_t if with_transpose else None, rows, amax_out, False)
     return data, data_t
+
+
+def _cast_dynamic_cuda(x, fp8_kind: int):
+    """amax + cast with the scale derived from the amax, one host call: (fp8 data, scale)."""
+    if not x.is_contiguous():
+        x = x.contiguous()
+    cols = x.shape[-1] if x.dim() > 0 else 1
+    rows = x.numel() // cols if cols > 0 else 0
+    if rows == 0 or cols == 0:
+        raise RuntimeError("amax of an empty tensor is undefined")
+    data = torch.empty(x.shape, dtype=N.FP8_DTYPE[fp8_kind], device=x.device)
+    amax_scale = torch.empty(2, dtype=torch.float32, device=x.device)
+    N.cast_dynamic(x, rows, cols, fp8_kind, amax_scale[0], amax_scale[1], data)
+    return data, amax_scale[1]
 
 
 def _multi_cast_with_scales_cuda(xs: List[torch.Tensor], scales: torch.Tensor, fp8_kind: int, product_fp32: bool):
@@ -263,6 +279,7 @@ _lib.impl("cast_from_amax", _cast_from_amax_cuda, "CUDA")
 _lib.impl("cast_with_scale", _cast_with_scale_cuda, "CUDA")
 _lib.impl("transpose_fp8", _transpose_fp8_cuda, "CUDA")
 _lib.impl("multi_cast_with_scales", _multi_cast_with_scales_cuda, "CUDA")
+_lib.impl("cast_dynamic", _cast_dynamic_cuda, "CUDA")
 _lib.impl("delayed_sync", _delayed_sync_cuda, "CUDA")
 _lib.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
 
@@ -335,6 +352,11 @@ def _cast_from_amax_fake(x, amax, fp8_kind, with_transpose):
 @torch.library.register_fake("f8b200::cast_with_scale")
 def _cast_with_scale_fake(x, scale, fp8_kind, product_fp32, with_transpose, amax_out):
     return _fake_cast_outputs(x, fp8_kind, with_transpose)
+
+
+@torch.library.register_fake("f8b200::cast_dynamic")
+def _cast_dynamic_fake(x, fp8_kind):
+    return x.new_empty(x.shape, dtype=N.FP8_DTYPE[fp8_kind]), x.new_empty((), dtype=torch.float32)
 
 
 @torch.library.register_fake("f8b200::multi_cast_with_scales")

@@ -910,6 +910,15 @@ extern "C" int f8b200_multi_cast(const void* const* xs, const int64_t* numels, i
   return F8B200_OK;
 }
 
+extern "C" int f8b200_cast_dynamic(const void* x, int hp_dtype, int64_t rows, int64_t cols, int fp8_kind, float* amax_out,
+                                   float* scale_out, void* out, void* stream) {
+  if (amax_out == nullptr || out == nullptr || rows <= 0 || cols <= 0) return F8B200_ERR_BAD_ARG;
+  int rc = f8b200_amax(x, hp_dtype, rows * cols, amax_out, stream);
+  if (rc != F8B200_OK) return rc;
+  return cast_impl(x, hp_dtype, rows, cols, cols, 1, amax_out, scale_out, 0, fp8_kind, out, cols, nullptr, 0, nullptr, 1,
+                   nullptr, 0, stream);
+}
+
 extern "C" int f8b200_cast_scatter(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_x, int scale_src,
                                    const float* scale_in, float* scale_out, int product_fp32, int fp8_kind,
                                    void* const* outs, int n_outs, int64_t ld_out, void* stream) {

@@ -112,6 +112,16 @@ int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t
                 float* amax_out, int reverse, void* stream);
 
 /*
+ * The whole dynamic cast of a CONTIGUOUS [rows, cols] tensor in one call: f8b200_amax into amax_out,
+ * then f8b200_cast(scale_src = 1, reverse = 1) from that amax (scale stored to scale_out when not
+ * NULL).  Two kernels and a 4-byte memset on `stream`, one host call: hp_tensor_to_float8_dynamic of
+ * float8_experimental/float8_scaling_utils.py:33-62 (about ten operator launches in the reference).
+ * With hundreds of small layers per step the host calls, not the kernels, bound the step time.
+ */
+int f8b200_cast_dynamic(const void* x, int hp_dtype, int64_t rows, int64_t cols, int fp8_kind,
+                        float* amax_out, float* scale_out, void* out, void* stream);
+
+/*
  * f8b200_cast whose row-major result goes to n_outs destinations at once (1 <= n_outs <=
  * F8B200_CAST_MAX_EXTRA + 1, all with row pitch ld_out; `outs` is a HOST array of device
  * pointers).  With the destinations being this rank's slot in the gathered buffer of every

@@ -124,6 +124,11 @@ def _rmsnorm_cast(x, weight, rstd, amax, fp8_kind):
     return from_np(bits.reshape(tuple(x.shape)), N.FP8_DTYPE[fp8_kind]), torch.tensor(float(scale), dtype=torch.float32)
 
 
+def _cast_dynamic(x, fp8_kind):
+    data, _, scale = _cast_from_amax(x, _amax(x), fp8_kind, False)
+    return data, scale
+
+
 def _multi_cast_with_scales(xs, scales, fp8_kind, product_fp32):
     return [_cast_with_scale(x, scales[i], fp8_kind, product_fp32, False, None)[0] for i, x in enumerate(xs)]
 
@@ -185,6 +190,7 @@ def install() -> None:
     lib.impl("rmsnorm_amax", _rmsnorm_amax, "CPU")
     lib.impl("rmsnorm_cast", _rmsnorm_cast, "CPU")
     lib.impl("multi_cast_with_scales", _multi_cast_with_scales, "CPU")
+    lib.impl("cast_dynamic", _cast_dynamic, "CPU")
     lib.impl("rmsnorm_bwd", _rmsnorm_bwd, "CPU")
     lib.impl("swiglu_bwd", _swiglu_bwd, "CPU")
     install._lib = lib  # keep the registrations alive

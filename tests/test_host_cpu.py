@@ -328,7 +328,7 @@ def test_gemms_read_the_cast_outputs_where_they_lie(monkeypatch, single_node):
             return wrapped
 
     def on_cast(name, args, out):
-        if name == "cast_from_amax":
+        if name in ("cast_from_amax", "cast_dynamic"):
             cast_ptrs.add(out[0].data_ptr())
 
     def on_mm(name, args, out):

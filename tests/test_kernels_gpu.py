@@ -208,6 +208,22 @@ def test_multi_tensor_cast_matches_single_casts(dname):
         assert nan_class_equal(outs[i].cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("dname", [O.BF16, O.FP16, O.FP32])
+@pytest.mark.parametrize("shape", [(256, 512), (77, 264), (5, 3), (4096, 4096)])
+def test_one_call_dynamic_cast_matches_the_oracle(dname, shape):
+    """f8b200_cast_dynamic (amax + cast in one host call): amax, scale and bytes of the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(shape[0] + shape[1])
+    x = (torch.randn(shape, device="cuda", generator=g) * 3).to(DT[dname])
+    for fname in (O.E4M3, O.E5M2):
+        out = torch.full(shape, 0x55, dtype=torch.uint8, device="cuda")
+        amax, scale = torch.zeros((), device="cuda"), torch.zeros((), device="cuda")
+        N.cast_dynamic(x, shape[0], shape[1], KIND[fname], amax, scale, out)
+        torch.cuda.synchronize()
+        bits, rscale, ramax = O.cast_dynamic(host_bits(x), dname, fname)
+        assert amax.item() == float(ramax) and scale.item() == float(rscale)
+        assert np.array_equal(out.cpu().numpy(), bits)
+
+
 def test_transpose_u8():
     for shape in ((128, 128), (130, 260), (5, 3), (1024, 16), (16, 1024)):
         x = torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda")
