@@ -107,7 +107,13 @@ def parity_fsdp2(dev, rank, world):
                 if model is fsdp_model:
                     f8.precompute_float8_dynamic_scale_for_fsdp(model)
                 losses.append(loss.detach())
-            torch.testing.assert_close(losses[0], losses[1], rtol=1e-5, atol=0, msg=f"fsdp2 step {step}: {losses}")
+            # Two ranks add two numbers: reduce-scatter and all-reduce give the same sums and the losses agree to
+            # rounding of the loss itself.  From four ranks on the two collectives add in different orders, the
+            # fp32 gradients differ in their last bits, and after an Adam step a few weights fall on the other
+            # side of an fp8 rounding boundary: the losses then agree to ~1e-4, not to the last bit.
+            rtol = 1e-5 if world <= 2 else 1e-3
+            torch.testing.assert_close(losses[0], losses[1], rtol=rtol, atol=0,
+                                       msg=f"fsdp2 step {step}: {[float(v) for v in losses]}")
     finally:
         dist.all_gather_into_tensor = real_ag
     per_block = (512 * 256 + 256 * 512) // world
@@ -269,12 +275,12 @@ def run_parity(dev, rank, world):
         except Exception as exc:  # noqa: BLE001
             results[name] = f"FAILED: {type(exc).__name__}: {exc}"[:300]
         # agree on the outcome before the next case: a rank that failed must not leave the others
-        # waiting inside a collective of the following case
-        bad = torch.tensor([0.0 if results[name] == "ok" else 1.0], device=dev)
-        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
-        if bad.item() != 0.0:
-            if results[name] == "ok":
-                results[name] = "FAILED on another rank"
+        # waiting inside a collective of the following case; every rank learns what failed where
+        outcomes = [None] * world
+        dist.all_gather_object(outcomes, results[name])
+        bad = [f"rank {r}: {o}" for r, o in enumerate(outcomes) if o != "ok"]
+        if bad:
+            results[name] = "; ".join(bad)[:600]
             break
     torch.cuda.synchronize()
     return results

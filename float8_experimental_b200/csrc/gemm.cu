@@ -114,17 +114,25 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-// L2 eviction-priority policies for the bulk tensor copies (0 = normal, 1 = evict first,
-// 2 = evict last).
+// L2 eviction-priority policies for the bulk tensor copies (0 = normal, 1 = evict first, 2 = evict last).
+// Kind 0 returns 0, which the load wrappers below take as "issue the copy WITHOUT a cache-hint operand".
+// That matters: operand loads that carry an explicit policy, even the evict-normal one, are not merged by
+// the L2 request coalescer, while plain loads of the same 128-byte lines by several SMs at about the same
+// time are served by one L2 lookup (ncu: lrc__average_xbar2gpc_sectors_op_read.ratio 1.00 with the hint,
+// 1.15-1.29 without; L2 lookups of the wo forward GEMM 6.56 -> 5.11 GB, die-to-die L2 traffic 1.29 -> 0.74
+// GB, and 1.5 % less time over the twelve GEMMs of the LLaMa-2-70B step).
 __device__ __forceinline__ uint64_t l2_policy(int kind) {
-  uint64_t p;
+  uint64_t p = 0;
   if (kind == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   else if (kind == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
 __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
                                                  uint64_t policy) {
+  if (policy == 0) {  // default L2 policy: no hint operand (see l2_policy)
+    tma_load_2d(smem_dst, map, x, y, bar);
+    return;
+  }
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], "
       "[%4], %5;" ::"r"(smem_u32(smem_dst)),
@@ -1123,8 +1131,21 @@ __device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uin
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+// The same load without an L2 cache-hint operand (default L2 policy).
+__device__ __forceinline__ void tma_load_2d_pair_plain(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                       uint32_t mbar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_cluster_addr)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
                                                  uint32_t mbar_cluster_addr, uint64_t policy) {
+  if (policy == 0) {  // default L2 policy: no hint operand (see l2_policy)
+    tma_load_2d_pair_plain(smem_dst, map, x, y, mbar_cluster_addr);
+    return;
+  }
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
       "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
@@ -1487,7 +1508,9 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tma_b)) : "memory");
-      const uint64_t pol = l2_policy(0);
+      auto load = [&](void* dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+        tma_load_2d_pair_plain(dst, map, x, y, bar);  // no cache-hint operand: see l2_policy
+      };
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -1506,12 +1529,12 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * QSTAGE_BYTES);
           const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
           if (!a_mn) {  // one box of 256 rows x 128 bytes of K
-            tma_load_2d_pair(sa, &tma_a, kb * BK, row_a, full_in_leader, pol);
+            load(sa, &tma_a, kb * BK, row_a, full_in_leader);
           } else {  // two boxes of [128 k rows] x [128 M positions]
-            tma_load_2d_pair(sa, &tma_a, row_a, kb * BK, full_in_leader, pol);
-            tma_load_2d_pair(sa + 128 * BK, &tma_a, row_a + 128, kb * BK, full_in_leader, pol);
+            load(sa, &tma_a, row_a, kb * BK, full_in_leader);
+            load(sa + 128 * BK, &tma_a, row_a + 128, kb * BK, full_in_leader);
           }
-          tma_load_2d_pair(sa + QA_BYTES, &tma_b, b_mn ? row_b : kb * BK, b_mn ? kb * BK : row_b, full_in_leader, pol);
+          load(sa + QA_BYTES, &tma_b, b_mn ? row_b : kb * BK, b_mn ? kb * BK : row_b, full_in_leader);
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;

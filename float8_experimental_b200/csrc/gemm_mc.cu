@@ -35,6 +35,14 @@ using namespace wide;
 
 __device__ __forceinline__ void tma_load_2d_mcast(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
                                                   uint16_t cta_mask, uint64_t policy) {
+  if (policy == 0) {  // default L2 policy: no hint operand (see l2_policy in gemm.cu)
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "h"(cta_mask)
+        : "memory");
+    return;
+  }
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster.L2::cache_hint "
       "[%0], [%1, {%2, %3}], [%4], %5, %6;" ::"r"(smem_u32(smem_dst)),
@@ -385,6 +393,10 @@ constexpr uint32_t PAIR_BIT_MASK = 0xFEFFFFFFu;  // clears the bit that tells th
 // cta_group::2 loads: `leader_bar` is the local barrier address with the pair bit cleared.
 __device__ __forceinline__ void tma_load_2d_pair_local(void* smem_dst, const CUtensorMap* map, int x, int y,
                                                        uint32_t leader_bar, uint64_t policy) {
+  if (policy == 0) {
+    tma_load_2d_pair_plain(smem_dst, map, x, y, leader_bar);
+    return;
+  }
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
       "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
@@ -393,6 +405,14 @@ __device__ __forceinline__ void tma_load_2d_pair_local(void* smem_dst, const CUt
 }
 __device__ __forceinline__ void tma_load_2d_pair_mcast(void* smem_dst, const CUtensorMap* map, int x, int y,
                                                        uint32_t leader_bar, uint16_t cta_mask, uint64_t policy) {
+  if (policy == 0) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster"
+        " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar), "h"(cta_mask)
+        : "memory");
+    return;
+  }
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster"
       ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5, %6;" ::"r"(smem_u32(smem_dst)),
