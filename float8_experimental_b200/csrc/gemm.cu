@@ -355,7 +355,7 @@ struct EpilogueArgs {
   uint8_t* staging;  // this warp's two boxes, 1024-byte aligned
   float inv;
   int store_evict_first;  // the output is not read again by this kernel: do not let it displace operands in L2
-  const RowScatter* scatter;  // rows go to several destinations (direct-store path only); null = `out`
+  const RowScatter* scatter;  // rows go to several destinations (per-thread and warp-written store paths); null = `out`
 };
 
 // Drains `ncol_total` accumulator columns starting at TMEM address `taddr` for the 32
@@ -849,7 +849,7 @@ __device__ __forceinline__ void drain_accumulator_coalesced(const EpilogueArgs<O
       const uint4 val = *reinterpret_cast<const uint4*>(box + rr * 128 + ((p ^ (rr & 7)) << 4));
       const int grow = row0 + rr;
       if (grow < e.m && gcol < e.n) {
-        OutT* dst = e.out + (int64_t)grow * e.ldo + gcol;
+        OutT* dst = (e.scatter != nullptr ? scatter_row_ptr<OutT>(*e.scatter, grow, e.ldo) : e.out + (int64_t)grow * e.ldo) + gcol;
         if (gcol + PIECE <= e.n) {
           __stcs(reinterpret_cast<uint4*>(dst), val);
         } else {
@@ -2243,7 +2243,14 @@ extern "C" int f8b200_gemm_fp8_scatter_rows(const void* a, int a_kind, int a_lay
     if (reinterpret_cast<uintptr_t>(outs[i]) % 16 != 0) vec_ok = 0;
   }
   CUtensorMap ma, mb, mo;
-  memset(&mo, 0, sizeof(mo));  // the scattered output is written with per-thread stores, not by TMA
+  memset(&mo, 0, sizeof(mo));  // the scattered output is written by the epilogue warps themselves, not by TMA
+  // Store path: whole 128-byte lines per row, written by the warp after staging in shared memory (eight
+  // lanes per line), when rows are 16-byte aligned; a store that crosses NVLink is one packet per 32-byte
+  // sector a thread touches, and the per-thread path (each lane 16 bytes of its own row) sends four times
+  // as many.  F8B200_GEMM_SCATTER_STORE=direct restores the per-thread path (read at every call).
+  int store_mode = vec_ok ? 2 : 0;
+  if (const char* e = getenv("F8B200_GEMM_SCATTER_STORE"))
+    if (e[0] == 'd') store_mode = 0;
   rc = a_layout ? gemm::encode_operand_map_mn(&ma, a, m, k, lda) : gemm::encode_operand_map(&ma, a, m, k, lda, 256);
   if (rc != F8B200_OK) return rc;
   rc = b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb) : gemm::encode_operand_map(&mb, b, n, k, ldb, 128);
@@ -2253,7 +2260,7 @@ extern "C" int f8b200_gemm_fp8_scatter_rows(const void* a, int a_kind, int a_lay
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return dispatch_out_dtype(out_dtype, [&](auto* tag) {
     using OutT = std::remove_pointer_t<decltype(tag)>;
-    return gemm::launch_pairwide<OutT, true>(ma, mb, mo, 0, scale_a, scale_b, bias, outs[0], ldo, (int)m, (int)n, (int)k,
+    return gemm::launch_pairwide<OutT, true>(ma, mb, mo, store_mode, scale_a, scale_b, bias, outs[0], ldo, (int)m, (int)n, (int)k,
                                              idq, vec_ok, layouts, static_cast<uint32_t*>(workspace), st, sc);
   });
 }

@@ -349,6 +349,34 @@ def test_gemm_split_drain_matches_whole_drain(mnk, monkeypatch):
     check_gemm(want[rows].float(), a[rows].float() @ b.float().t())
 
 
+@pytest.mark.parametrize("store", ["", "direct"])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("mnk_dests_rows", [((2048, 1024, 256), 2, 256), ((4096, 2048 + 24, 1024 + 16), 4, 128),
+                                            ((1536, 512, 128), 3, 512), ((1024, 768, 384), 1, 1024)])
+def test_gemm_scatter_rows_matches_plain_gemm(mnk_dests_rows, out_dtype, store, monkeypatch):
+    """`f8b200_gemm_fp8_scatter_rows` sends output row block i to destination i % n at block row i // n.
+    Put back in order, the destinations hold the bits of the plain GEMM, with the warp-written whole-line
+    stores (the default) as with per-thread stores."""
+    (m, n, k), dests, rpb = mnk_dests_rows
+    g = torch.Generator(device="cuda").manual_seed(m + 5 * n + k + dests)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e5m2)
+    sa, sb = torch.tensor(2.0, device="cuda"), torch.tensor(0.25, device="cuda")
+    want = gemm(a, b, sa, sb, out_dtype=out_dtype)
+    blocks = m // rpb
+    assert blocks % dests == 0
+    outs = [torch.full((blocks // dests * rpb, n), float("nan"), dtype=out_dtype, device="cuda") for _ in range(dests)]
+    monkeypatch.setenv("F8B200_GEMM_SCATTER_STORE", store)
+    for _ in range(2):
+        N.gemm_fp8_scatter_rows(a, k, b, k, sa, sb, out_dtype, [o.data_ptr() for o in outs], rpb, n, m, n, k)
+    got = torch.empty_like(want)
+    for blk in range(blocks):
+        src = outs[blk % dests][(blk // dests) * rpb:(blk // dests + 1) * rpb]
+        got[blk * rpb:(blk + 1) * rpb] = src
+    as_int = torch.int16 if out_dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(got.view(as_int), want.view(as_int))
+
+
 @pytest.mark.parametrize("layouts", [(False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("mnk", [(512, 768, 256), (4096, 2048 + 16, 1024 + 48), (8192, 4096, 16384 + 128)])
 @pytest.mark.parametrize("mode", ["2cta", "wide", "pw"])
