@@ -1421,11 +1421,13 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
 // and release them (tmem_empty[0]), then columns 256..511 (tmem_empty[1]); the MMA thread starts the
 // next tile's h = 0 MMAs for the first k-blocks (as many as there are stages) as soon as the first
 // half is free, catches up with h = 1 on the same stages when the second half is free, and only then
-// releases those stages.  Accumulation order per output element is unchanged (k ascending), so the
-// result is bit-identical to the other kernels.
+// releases those stages.  The end of a tile mirrors that: on the last k-blocks (as many as there are
+// stages) the h = 0 MMAs are issued first and half 0 is handed to the epilogue (tmem_full[0]) while the
+// h = 1 MMAs on the same stages still run (tmem_full[1] follows).  Accumulation order per output element
+// is unchanged (k ascending), so the result is bit-identical to the other kernels.
 //   full[s]        lives in the leader; both CTAs' TMA loads complete_tx on it (96 KB per stage)
 //   empty[s]       one per CTA; released by a multicast tcgen05.commit from the leader
-//   tmem_full      one per CTA; same multicast commit when a tile's MMAs are done
+//   tmem_full[h]   per CTA; same multicast commit when the MMAs of a tile into accumulator half h are done
 //   tmem_empty[h]  live in the leader; 16 arrivals each (8 epilogue warps of each CTA)
 // No TMA load here uses cluster multicast.
 // ===========================================================================
@@ -1441,11 +1443,12 @@ constexpr int QB_BYTES = 128 * BK;
 constexpr int QSTAGE_BYTES = QA_BYTES + QB_BYTES;
 constexpr int QTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int SPLIT_DRAIN_BIT = 26;  // bit of the packed `raster` word: overlap the epilogue by halves
+constexpr int SPLIT_TAIL_BIT = 27;   // and finish accumulator half 0 ahead of half 1 at the end of a tile
 
 struct __align__(8) QBarriers {
   uint64_t full[QSTAGES];
   uint64_t empty[QSTAGES];
-  uint64_t tmem_full;
+  uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   TileRing ring;  // written in both CTAs by the leader's producer thread
   uint32_t tmem_base;
@@ -1477,6 +1480,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int64_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
   const bool split_drain = (raster >> SPLIT_DRAIN_BIT) & 1;
+  const bool split_tail = (raster >> SPLIT_TAIL_BIT) & 1;
   const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
 
   if (threadIdx.x == 0) {
@@ -1484,7 +1488,8 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    mbar_init(&bars->tmem_full, 1);
+    mbar_init(&bars->tmem_full[0], 1);
+    mbar_init(&bars->tmem_full[1], 1);
     mbar_init(&bars->tmem_empty[0], 16);
     mbar_init(&bars->tmem_empty[1], 16);
     for (int r = 0; r < RING; ++r) mbar_init(&bars->ring.full[r], 1);
@@ -1608,7 +1613,11 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           tc_commit_pair(&bars->empty[stage]);
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
         }
-        for (int kb = head; kb < num_kb; ++kb) {
+        // tail of the tile: half 0 finishes its last k-blocks first and is handed to the epilogue while
+        // half 1 still runs them
+        int tail = split_tail ? (num_kb - head < QSTAGES ? num_kb - head : QSTAGES) : 0;
+        if (tail < 0) tail = 0;
+        for (int kb = head; kb < num_kb - tail; ++kb) {
           if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u)) { ok = false; break; }
           tc_fence_after();
           issue_half(stage, kb, 0);
@@ -1617,7 +1626,24 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit_pair(&bars->tmem_full);
+        {
+          int st = stage;
+          uint32_t ph = phase;
+          for (int kb = num_kb - tail; kb < num_kb; ++kb) {
+            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u)) { ok = false; break; }
+            tc_fence_after();
+            issue_half(st, kb, 0);
+            if (++st == QSTAGES) { st = 0; ph ^= 1u; }
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(&bars->tmem_full[0]);
+        for (int kb = num_kb - tail; kb < num_kb; ++kb) {  // these stages are known to be full
+          issue_half(stage, kb, 1);
+          tc_commit_pair(&bars->empty[stage]);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        tc_commit_pair(&bars->tmem_full[1]);
         if (sched != nullptr) {
           const int32_t v = pair_ring_read(bars, (uint32_t)local, peer, 16u, 0u);
           if (v == -2) { ok = false; break; }
@@ -1648,12 +1674,12 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     int64_t t = cluster_id;
     for (; ok && t < num_tiles; ++local) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n, raster);
-      int got = 1;
-      if (lane == 0) got = pair_wait(&bars->tmem_full, (uint32_t)(local & 1), bars, peer, 8u, 256u) ? 1 : 0;
-      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
-      tc_fence_after();
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
+        int got = 1;
+        if (lane == 0) got = pair_wait(&bars->tmem_full[h], (uint32_t)(local & 1), bars, peer, 8u, 256u) ? 1 : 0;
+        if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
+        tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 256 + part * 128);
         wide::drain_wide<OutT>(ea, taddr, tc.m * QBM + (int)rank * 256 + h * 128 + quarter * 32, tc.n * QBN + part * 128,
                                128, boxes);
@@ -1661,6 +1687,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[h]), 0u));
       }
+      if (!ok) break;
       if (sched != nullptr) {
         int v = 0;
         if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, 64u);
@@ -1954,9 +1981,12 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
     if (e != cudaSuccess) return record_cuda_error(e);
   }
   // F8B200_GEMM_SPLIT_DRAIN=0 makes the MMA thread wait for the whole accumulator (read at every call)
-  int split = 1 << pairwide::SPLIT_DRAIN_BIT;
-  if (const char* e = getenv("F8B200_GEMM_SPLIT_DRAIN"))
+  // ("head": only the start of the next tile overlaps the drain, not the end of the current one)
+  int split = (1 << pairwide::SPLIT_DRAIN_BIT) | (1 << pairwide::SPLIT_TAIL_BIT);
+  if (const char* e = getenv("F8B200_GEMM_SPLIT_DRAIN")) {
     if (e[0] == '0') split = 0;
+    if (e[0] == 'h') split = 1 << pairwide::SPLIT_DRAIN_BIT;
+  }
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
                          choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched, scatter));

@@ -328,7 +328,8 @@ def test_gemm_dynamic_schedule_matches_fixed_stride(mnk, gemm_mode, monkeypatch)
     check_gemm(fixed[rows].float(), a[rows].float() @ b.float().t())
 
 
-@pytest.mark.parametrize("mnk", [(2048, 1024, 384), (4096 + 40, 2048 + 24, 1024 + 16), (1024, 512, 128 * 3)])
+@pytest.mark.parametrize("mnk", [(2048, 1024, 384), (4096 + 40, 2048 + 24, 1024 + 16), (1024, 512, 128 * 3),
+                                 (8192, 4096, 128 * 6), (8192, 8192, 128 * 8), (4096, 4096, 128 * 9 + 16), (512, 256, 128)])
 def test_gemm_split_drain_matches_whole_drain(mnk, monkeypatch):
     """The 512x256 pair kernel starts the next tile on the accumulator half its epilogue has already
     drained; with F8B200_GEMM_SPLIT_DRAIN=0 it waits for the whole accumulator.  Every output element
@@ -342,10 +343,10 @@ def test_gemm_split_drain_matches_whole_drain(mnk, monkeypatch):
     monkeypatch.setenv("F8B200_GEMM_MODE", "2cta")
     want = gemm(a, b, sa, sb)
     monkeypatch.setenv("F8B200_GEMM_MODE", "pw")
-    for split in ("0", "1", "1"):
+    for split in ("0", "head", "1", "1"):  # none / start of the next tile only / both ends (the default)
         monkeypatch.setenv("F8B200_GEMM_SPLIT_DRAIN", split)
         assert torch.equal(gemm(a, b, sa, sb).view(torch.int16), want.view(torch.int16)), split
-    rows = torch.tensor([0, 127, 128, 255, 256, 511, 512, m - 1], device="cuda")
+    rows = torch.tensor(sorted({min(r, m - 1) for r in (0, 127, 128, 255, 256, 511, 512, m - 1)}), device="cuda")
     check_gemm(want[rows].float(), a[rows].float() @ b.float().t())
 
 
