@@ -47,10 +47,10 @@ GEMM_DRAM_TRAFFIC = {
     "wide": {"wo.fwd": (0.43e9, 0.24e9), "wo.wgrad": (0.88e9, 0.12e9), "w13.fwd": (2.45e9, 1.86e9),
              "w13.dgrad": (6.54e9, 0.26e9), "w13.wgrad": (5.46e9, 0.93e9), "w2.fwd": (2.93e9, 0.26e9),
              "w2.dgrad": (1.34e9, 0.91e9)},
-    "pw": {"wqkv.fwd": (0.61e9, 0.31e9), "wqkv.dgrad": (0.87e9, 0.25e9), "wqkv.wgrad": (1.05e9, 0.16e9),
-           "wo.fwd": (0.48e9, 0.25e9), "wo.dgrad": (0.47e9, 0.25e9), "wo.wgrad": (0.82e9, 0.12e9),
-           "w13.fwd": (2.22e9, 1.86e9), "w13.dgrad": (7.74e9, 0.26e9), "w13.wgrad": (7.10e9, 0.93e9),
-           "w2.fwd": (3.42e9, 0.26e9), "w2.dgrad": (1.26e9, 0.92e9), "w2.wgrad": (3.01e9, 0.46e9)},
+    "pw": {"wqkv.fwd": (0.61e9, 0.32e9), "wqkv.dgrad": (0.81e9, 0.26e9), "wqkv.wgrad": (1.05e9, 0.16e9),
+           "wo.fwd": (0.46e9, 0.25e9), "wo.dgrad": (0.45e9, 0.25e9), "wo.wgrad": (0.82e9, 0.13e9),
+           "w13.fwd": (2.56e9, 1.90e9), "w13.dgrad": (8.31e9, 0.27e9), "w13.wgrad": (6.38e9, 0.96e9),
+           "w2.fwd": (3.69e9, 0.27e9), "w2.dgrad": (1.35e9, 0.94e9), "w2.wgrad": (2.87e9, 0.48e9)},
 }
 # amax launch read + cast launch read + cast launch write on one 16384 x 8192 bf16 tensor
 CAST_DRAM_TRAFFIC = {"plain": (268.4e6, 268.5e6, 78.2e6), "transposed": (268.4e6, 268.5e6, 211.9e6)}
