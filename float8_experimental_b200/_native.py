@@ -44,10 +44,12 @@ EXPORTS = (
     "f8b200_rmsnorm_amax",
     "f8b200_rmsnorm_cast",
     "f8b200_swiglu_amax",
+    "f8b200_swiglu_amax_approx",
     "f8b200_swiglu_cast",
     "f8b200_rmsnorm_bwd_workspace_bytes",
     "f8b200_rmsnorm_bwd",
     "f8b200_swiglu_bwd",
+    "f8b200_swiglu_bwd_approx",
     "f8b200_read_device_error",
     "f8b200_check_device_error",
 )
@@ -95,11 +97,13 @@ def load() -> ctypes.CDLL:
     lib.f8b200_rmsnorm_amax.argtypes = [vp, i32, i64, i64, i64, vp, ctypes.c_float, vp, vp, vp]
     lib.f8b200_rmsnorm_cast.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.f8b200_swiglu_amax.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
+    lib.f8b200_swiglu_amax_approx.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
     lib.f8b200_swiglu_cast.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i32, vp, vp, i64, vp]
     lib.f8b200_rmsnorm_bwd_workspace_bytes.argtypes = [i64]
     lib.f8b200_rmsnorm_bwd_workspace_bytes.restype = i64
     lib.f8b200_rmsnorm_bwd.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, vp, vp, i64, vp, vp, i64, vp]
     lib.f8b200_swiglu_bwd.argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, vp, vp, i64, vp]
+    lib.f8b200_swiglu_bwd_approx.argtypes = [vp, vp, vp, i32, i64, i64, i64, i64, i64, vp, vp, i64, vp]
     lib.f8b200_read_device_error.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     lib.f8b200_check_device_error.argtypes = []
     lib.f8b200_gemm_kernel_choice.argtypes = [i64, i64, i64]
@@ -497,14 +501,15 @@ def rmsnorm_cast(x: torch.Tensor, rows: int, cols: int, ld: int, weight: torch.T
 
 
 def swiglu_amax(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int,
-                y_out: Optional[torch.Tensor], ld_y: int, amax_out: torch.Tensor) -> None:
+                y_out: Optional[torch.Tensor], ld_y: int, amax_out: torch.Tensor, approx: bool = False) -> None:
     _require_cuda(a, b, y_out, amax_out)
+    args = (a.data_ptr(), b.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b, _ptr(y_out), ld_y,
+            amax_out.data_ptr(), _stream(a))
     with _Launch("glu_amax", a.device):
-        _check(
-            load().f8b200_swiglu_amax(a.data_ptr(), b.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b,
-                                      _ptr(y_out), ld_y, amax_out.data_ptr(), _stream(a)),
-            "f8b200_swiglu_amax",
-        )
+        if approx:
+            _check(load().f8b200_swiglu_amax_approx(*args), "f8b200_swiglu_amax_approx")
+        else:
+            _check(load().f8b200_swiglu_amax(*args), "f8b200_swiglu_amax")
 
 
 def swiglu_cast(a: torch.Tensor, b: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int, amax: torch.Tensor,
@@ -548,14 +553,15 @@ def rmsnorm_bwd(x: torch.Tensor, g: torch.Tensor, rows: int, cols: int, ld_x: in
 
 
 def swiglu_bwd(a: torch.Tensor, b: torch.Tensor, g: torch.Tensor, rows: int, cols: int, ld_a: int, ld_b: int,
-               ld_g: int, da: torch.Tensor, db: torch.Tensor) -> None:
+               ld_g: int, da: torch.Tensor, db: torch.Tensor, approx: bool = False) -> None:
     _require_cuda(a, b, g, da, db)
+    args = (a.data_ptr(), b.data_ptr(), g.data_ptr(), hp_code(a.dtype), rows, cols, ld_a, ld_b, ld_g, da.data_ptr(),
+            db.data_ptr(), cols, _stream(a))
     with _Launch("glu_bwd", a.device):
-        _check(
-            load().f8b200_swiglu_bwd(a.data_ptr(), b.data_ptr(), g.data_ptr(), hp_code(a.dtype), rows, cols, ld_a,
-                                     ld_b, ld_g, da.data_ptr(), db.data_ptr(), cols, _stream(a)),
-            "f8b200_swiglu_bwd",
-        )
+        if approx:
+            _check(load().f8b200_swiglu_bwd_approx(*args), "f8b200_swiglu_bwd_approx")
+        else:
+            _check(load().f8b200_swiglu_bwd(*args), "f8b200_swiglu_bwd")
 
 
 def check_device_error() -> None:

@@ -18,7 +18,7 @@ Ops (namespace `f8b200`):
   scaled_mm(a, b_t, scale_a, scale_b, bias, out_dtype, use_fast_accum) -> out
   rmsnorm_amax(x, weight, eps) -> (rstd fp32 [rows], amax fp32 0-dim)      f8b200_rmsnorm_amax
   rmsnorm_cast(x, weight, rstd, amax, kind) -> (data, scale)               f8b200_rmsnorm_cast
-  swiglu_amax(a, b, write_y) -> (amax fp32 0-dim, y or empty)              f8b200_swiglu_amax
+  swiglu_amax(a, b, write_y, approx) -> (amax fp32 0-dim, y or empty)      f8b200_swiglu_amax[_approx]
   swiglu_cast(a, b, amax, kind) -> (data, scale)                           f8b200_swiglu_cast
 """
 from __future__ import annotations
@@ -52,9 +52,9 @@ _lib.define(
 )
 _lib.define("rmsnorm_amax(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _lib.define("rmsnorm_cast(Tensor x, Tensor weight, Tensor rstd, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
-_lib.define("swiglu_amax(Tensor a, Tensor b, bool write_y) -> (Tensor, Tensor)")
+_lib.define("swiglu_amax(Tensor a, Tensor b, bool write_y, bool approx=False) -> (Tensor, Tensor)")
 _lib.define("rmsnorm_bwd(Tensor x, Tensor grad_y, Tensor weight, Tensor rstd) -> (Tensor, Tensor)")
-_lib.define("swiglu_bwd(Tensor a, Tensor b, Tensor grad_y) -> (Tensor, Tensor)")
+_lib.define("swiglu_bwd(Tensor a, Tensor b, Tensor grad_y, bool approx=False) -> (Tensor, Tensor)")
 _lib.define("swiglu_cast(Tensor a, Tensor b, Tensor amax, int fp8_kind) -> (Tensor, Tensor)")
 
 
@@ -232,11 +232,11 @@ def _glu_operands(a, b):
     return am, bm, rows, cols, lda, ldb
 
 
-def _swiglu_amax_cuda(a, b, write_y: bool):
+def _swiglu_amax_cuda(a, b, write_y: bool, approx: bool = False):
     am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
     amax = torch.empty((), dtype=torch.float32, device=a.device)
     y = _empty_like_shape(a, a.dtype) if write_y else a.new_empty((0,))
-    N.swiglu_amax(am, bm, rows, cols, lda, ldb, y if write_y else None, cols, amax)
+    N.swiglu_amax(am, bm, rows, cols, lda, ldb, y if write_y else None, cols, amax, approx)
     return amax, y
 
 
@@ -257,12 +257,12 @@ def _rmsnorm_bwd_cuda(x, grad_y, weight, rstd):
     return dx.view(x.shape), dw
 
 
-def _swiglu_bwd_cuda(a, b, grad_y):
+def _swiglu_bwd_cuda(a, b, grad_y, approx: bool = False):
     am, bm, rows, cols, lda, ldb = _glu_operands(a, b)
     gm, _, _, ldg = _as_matrix(grad_y.reshape(a.shape).contiguous())
     da = torch.empty(a.shape, dtype=a.dtype, device=a.device)
     db = torch.empty(a.shape, dtype=a.dtype, device=a.device)
-    N.swiglu_bwd(am, bm, gm, rows, cols, lda, ldb, ldg, da, db)
+    N.swiglu_bwd(am, bm, gm, rows, cols, lda, ldb, ldg, da, db, approx)
     return da, db
 
 
@@ -294,12 +294,12 @@ def _rmsnorm_bwd_fake(x, grad_y, weight, rstd):
 
 
 @torch.library.register_fake("f8b200::swiglu_bwd")
-def _swiglu_bwd_fake(a, b, grad_y):
+def _swiglu_bwd_fake(a, b, grad_y, approx=False):
     return torch.empty_like(a), torch.empty_like(a)
 
 
 @torch.library.register_fake("f8b200::swiglu_amax")
-def _swiglu_amax_fake(a, b, write_y):
+def _swiglu_amax_fake(a, b, write_y, approx=False):
     return a.new_empty((), dtype=torch.float32), a.new_empty(a.shape if write_y else (0,))
 
 

@@ -147,6 +147,7 @@ def measure_fused_norm(torch, dev, x):
     a, b = h[:, :28672], h[:, 28672:]
     glu_ms = timed(lambda: swiglu_to_float8_dynamic(a, b))
     glu_recompute_ms = timed(lambda: swiglu_to_float8_dynamic(a, b, recompute=True))
+    glu_approx_ms = timed(lambda: swiglu_to_float8_dynamic(a, b, approx_gate=True))
     glu_unfused_ms = timed(lambda: hp_tensor_to_float8_dynamic(torch.nn.functional.silu(a) * b, torch.float8_e4m3fn, cfg))
     # backward of the two producers (CUDA kernels) against eager autograd of the same formulas
     from float8_experimental_b200._ops import ops
@@ -164,6 +165,7 @@ def measure_fused_norm(torch, dev, x):
     norm_bwd_eager_ms = timed(eager_norm_bwd)
     gg = torch.randn(a.shape, device=dev, dtype=x.dtype)
     glu_bwd_ms = timed(lambda: ops.swiglu_bwd(a, b, gg))
+    glu_bwd_approx_ms = timed(lambda: ops.swiglu_bwd(a, b, gg, True))
 
     def eager_glu_bwd():
         ar, br = a.detach().requires_grad_(True), b.detach().requires_grad_(True)
@@ -173,6 +175,7 @@ def measure_fused_norm(torch, dev, x):
     backward = {"rmsnorm_bwd_ms": norm_bwd_ms, "rmsnorm_bwd_gbs": 6.0 * x.numel() / (norm_bwd_ms * 1e-3) / 1e9,
                 "rmsnorm_eager_fwd_bwd_ms": norm_bwd_eager_ms,
                 "swiglu_bwd_ms": glu_bwd_ms, "swiglu_bwd_gbs": 10.0 * a.numel() / (glu_bwd_ms * 1e-3) / 1e9,
+                "swiglu_bwd_approx_gate_ms": glu_bwd_approx_ms,
                 "swiglu_eager_fwd_bwd_ms": glu_bwd_eager_ms}
     return {"shape": list(x.shape), "backward": backward,
             "fused_ms": fused_ms, "fused_gbs": 5.0 * x.numel() / (fused_ms * 1e-3) / 1e9,
@@ -182,6 +185,7 @@ def measure_fused_norm(torch, dev, x):
                        "fused_bytes": "9 B per element: a and b read, gate output written (4 + 2); read back and cast "
                                       "(2 + 1)",
                        "fused_recompute_ms": glu_recompute_ms,
+                       "fused_approx_gate_ms": glu_approx_ms,
                        "unfused_eager_silu_mul_then_cast_ms": glu_unfused_ms}}
 
 

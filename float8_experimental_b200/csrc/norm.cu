@@ -448,10 +448,17 @@ namespace {
 
 __device__ __forceinline__ float silu_f32(float a) { return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a))); }
 
-template <int HP>
+// Opt-in approximate gate (the `_approx` entry points): sigmoid from ex2.approx and rcp.approx (about 2^-21
+// relative error in fp32 instead of correctly rounded division and a 1-ulp exp), then the same roundings to T.
+// The error is far below half an ulp of a 16-bit T, so silu(a) rounds to the same T value except where the
+// exact result lies within ~2^-12 of an ulp of a rounding boundary; there it is the neighbouring T value.
+__device__ __forceinline__ float sigmoid_approx(float a) { return __fdividef(1.0f, 1.0f + __expf(-a)); }
+
+template <int HP, bool APPROX = false>
 __device__ __forceinline__ uint32_t swiglu_pair(uint32_t a2, uint32_t b2) {
   float a0, a1;
   unpack_pair<HP>(a2, a0, a1);
+  if constexpr (APPROX) return mul2<HP>(pack_round2<HP>(a0 * sigmoid_approx(a0), a1 * sigmoid_approx(a1)), b2);
   return mul2<HP>(pack_round2<HP>(silu_f32(a0), silu_f32(a1)), b2);
 }
 
@@ -464,7 +471,7 @@ constexpr int kGluThreads = 256;
 
 // 16-bit dtypes, 8 elements per thread and step; rows x cols with separate row pitches for a and b
 // (the two halves of one fused w1|w3 output are the usual case).
-template <int HP, bool WRITE_Y>
+template <int HP, bool WRITE_Y, bool APPROX = false>
 __global__ void __launch_bounds__(kGluThreads)
 swiglu_amax_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, int64_t lda_bytes, int64_t ldb_bytes,
                         int64_t rows, int64_t chunks_per_row, uint32_t* __restrict__ amax_bits,
@@ -477,10 +484,10 @@ swiglu_amax_fast_kernel(const char* __restrict__ a, const char* __restrict__ b, 
     const uint4 qa = __ldcs(reinterpret_cast<const uint4*>(a + r * lda_bytes) + c);
     const uint4 qb = __ldcs(reinterpret_cast<const uint4*>(b + r * ldb_bytes) + c);
     uint4 y;
-    y.x = swiglu_pair<HP>(qa.x, qb.x);
-    y.y = swiglu_pair<HP>(qa.y, qb.y);
-    y.z = swiglu_pair<HP>(qa.z, qb.z);
-    y.w = swiglu_pair<HP>(qa.w, qb.w);
+    y.x = swiglu_pair<HP, APPROX>(qa.x, qb.x);
+    y.y = swiglu_pair<HP, APPROX>(qa.y, qb.y);
+    y.z = swiglu_pair<HP, APPROX>(qa.z, qb.z);
+    y.w = swiglu_pair<HP, APPROX>(qa.w, qb.w);
     amax2 = __vmaxu2(amax2, y.x & 0x7FFF7FFFu);
     amax2 = __vmaxu2(amax2, y.y & 0x7FFF7FFFu);
     amax2 = __vmaxu2(amax2, y.z & 0x7FFF7FFFu);
@@ -587,8 +594,9 @@ bool glu_vec_ok(int hp_dtype, int64_t cols, int64_t lda, int64_t ldb, const void
 }  // namespace
 }  // namespace f8b200
 
-extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
-                                  int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out, void* stream) {
+static int swiglu_amax_impl(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
+                            int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out, void* stream, bool approx) {
+  using namespace f8b200;
   if (a == nullptr || b == nullptr || amax_out == nullptr) return F8B200_ERR_BAD_ARG;
   if (hp_dtype < 0 || hp_dtype > 2 || rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols) return F8B200_ERR_BAD_ARG;
   if (y_out != nullptr && ld_y < cols) return F8B200_ERR_BAD_ARG;
@@ -602,16 +610,20 @@ extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, in
   char* yp = static_cast<char*>(y_out);
   uint32_t* ab = reinterpret_cast<uint32_t*>(amax_out);
   const bool y_vec = y_out == nullptr || (ld_y % 8 == 0 && reinterpret_cast<uintptr_t>(y_out) % 16 == 0);
-  if (glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b) && y_vec) {
+  const bool vec = glu_vec_ok(hp_dtype, cols, ld_a, ld_b, a, b) && y_vec;
+  if (approx && !vec) return F8B200_ERR_UNSUPPORTED;  // only the vectorised 16-bit kernels have the approximate gate
+  if (vec) {
     const int64_t cpr = cols / 8;
     const int grid = glu_grid(rows * cpr);
-#define F8_GLU_A(HP, WY) \
-  swiglu_amax_fast_kernel<HP, WY><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab, yp, ld_y * 2)
+#define F8_GLU_A(HP, WY, AX) \
+  swiglu_amax_fast_kernel<HP, WY, AX><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a * 2, ld_b * 2, rows, cpr, ab, yp, ld_y * 2)
+#define F8_GLU_A2(HP, WY) do { if (approx) F8_GLU_A(HP, WY, true); else F8_GLU_A(HP, WY, false); } while (0)
     if (hp_dtype == F8B200_BF16) {
-      if (y_out != nullptr) F8_GLU_A(F8B200_BF16, true); else F8_GLU_A(F8B200_BF16, false);
+      if (y_out != nullptr) F8_GLU_A2(F8B200_BF16, true); else F8_GLU_A2(F8B200_BF16, false);
     } else {
-      if (y_out != nullptr) F8_GLU_A(F8B200_FP16, true); else F8_GLU_A(F8B200_FP16, false);
+      if (y_out != nullptr) F8_GLU_A2(F8B200_FP16, true); else F8_GLU_A2(F8B200_FP16, false);
     }
+#undef F8_GLU_A2
 #undef F8_GLU_A
     return check_launch();
   }
@@ -623,6 +635,17 @@ extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, in
   else
     swiglu_amax_generic_kernel<F8B200_FP32><<<grid, kGluThreads, 0, st>>>(ap, bp, ld_a, ld_b, rows, cols, ab, yp, ld_y);
   return check_launch();
+}
+
+extern "C" int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
+                                  int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out, void* stream) {
+  return swiglu_amax_impl(a, b, hp_dtype, rows, cols, ld_a, ld_b, y_out, ld_y, amax_out, stream, false);
+}
+
+extern "C" int f8b200_swiglu_amax_approx(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
+                                         int64_t ld_a, int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out,
+                                         void* stream) {
+  return swiglu_amax_impl(a, b, hp_dtype, rows, cols, ld_a, ld_b, y_out, ld_y, amax_out, stream, true);
 }
 
 extern "C" int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols, int64_t ld_a,
@@ -777,7 +800,7 @@ rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int parts, int64_t c
   }
 }
 
-template <int HP>
+template <int HP, bool APPROX = false>
 __global__ void __launch_bounds__(kGluThreads)
 swiglu_bwd_kernel(const char* __restrict__ a, const char* __restrict__ b, const char* __restrict__ g, int64_t lda_bytes,
                   int64_t ldb_bytes, int64_t ldg_bytes, int64_t rows, int64_t chunks_per_row, char* __restrict__ da,
@@ -791,10 +814,10 @@ swiglu_bwd_kernel(const char* __restrict__ a, const char* __restrict__ b, const 
     widen8<HP>(__ldcs(reinterpret_cast<const uint4*>(g + r * ldg_bytes) + c), gv);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-av[j])));
+      const float sig = APPROX ? sigmoid_approx(av[j]) : __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-av[j])));
       const float ds = round_hp<HP>(gv[j] * bv[j]);
       dav[j] = ds * (sig * (1.0f + av[j] * (1.0f - sig)));
-      dbv[j] = gv[j] * round_hp<HP>(silu_f32(av[j]));
+      dbv[j] = gv[j] * round_hp<HP>(APPROX ? av[j] * sig : silu_f32(av[j]));
     }
     uint4 oa, ob;
     oa.x = pack_round2<HP>(dav[0], dav[1]); oa.y = pack_round2<HP>(dav[2], dav[3]);
@@ -930,9 +953,10 @@ extern "C" int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtyp
   return check_launch();
 }
 
-extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
-                                 int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
-                                 int64_t ld_out, void* stream) {
+static int swiglu_bwd_impl(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows, int64_t cols,
+                           int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db, int64_t ld_out, void* stream,
+                           bool approx) {
+  using namespace f8b200;
   if (a == nullptr || b == nullptr || grad_y == nullptr || da == nullptr || db == nullptr) return F8B200_ERR_BAD_ARG;
   if (rows <= 0 || cols <= 0 || ld_a < cols || ld_b < cols || ld_g < cols || ld_out < cols) return F8B200_ERR_BAD_ARG;
   if (hp_dtype < 0 || hp_dtype > 2) return F8B200_ERR_BAD_ARG;
@@ -942,6 +966,7 @@ extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_
   int rc = f8b200_device_check();
   if (rc != F8B200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (approx && !fast) return F8B200_ERR_UNSUPPORTED;  // only the vectorised 16-bit kernel has the approximate gate
   if (!fast) {
     const int ggrid = glu_grid(rows * cols);
 #define F8_GLU_BWD_GEN(HP)                                                                                             \
@@ -956,13 +981,27 @@ extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_
   }
   const int64_t cpr = cols / 8;
   const int grid = glu_grid(rows * cpr);
-  if (hp_dtype == F8B200_BF16)
-    swiglu_bwd_kernel<F8B200_BF16><<<grid, kGluThreads, 0, st>>>(
-        static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a * 2, ld_b * 2,
-        ld_g * 2, rows, cpr, static_cast<char*>(da), static_cast<char*>(db), ld_out * 2);
-  else
-    swiglu_bwd_kernel<F8B200_FP16><<<grid, kGluThreads, 0, st>>>(
-        static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a * 2, ld_b * 2,
-        ld_g * 2, rows, cpr, static_cast<char*>(da), static_cast<char*>(db), ld_out * 2);
+#define F8_GLU_BWD(HP, AX)                                                                                             \
+  swiglu_bwd_kernel<HP, AX><<<grid, kGluThreads, 0, st>>>(                                                             \
+      static_cast<const char*>(a), static_cast<const char*>(b), static_cast<const char*>(grad_y), ld_a * 2, ld_b * 2, \
+      ld_g * 2, rows, cpr, static_cast<char*>(da), static_cast<char*>(db), ld_out * 2)
+  if (hp_dtype == F8B200_BF16) {
+    if (approx) F8_GLU_BWD(F8B200_BF16, true); else F8_GLU_BWD(F8B200_BF16, false);
+  } else {
+    if (approx) F8_GLU_BWD(F8B200_FP16, true); else F8_GLU_BWD(F8B200_FP16, false);
+  }
+#undef F8_GLU_BWD
   return check_launch();
+}
+
+extern "C" int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
+                                 int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
+                                 int64_t ld_out, void* stream) {
+  return swiglu_bwd_impl(a, b, grad_y, hp_dtype, rows, cols, ld_a, ld_b, ld_g, da, db, ld_out, stream, false);
+}
+
+extern "C" int f8b200_swiglu_bwd_approx(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
+                                        int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
+                                        int64_t ld_out, void* stream) {
+  return swiglu_bwd_impl(a, b, grad_y, hp_dtype, rows, cols, ld_a, ld_b, ld_g, da, db, ld_out, stream, true);
 }

@@ -88,8 +88,8 @@ class Float8RMSNorm(torch.nn.Module):
 
 class _SwiGLUToFloat8(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, b, float8_dtype, linear_mm_config, gemm_input_role, reduce_amax, recompute):
-        amax, y = ops.swiglu_amax(a, b, not recompute)
+    def forward(ctx, a, b, float8_dtype, linear_mm_config, gemm_input_role, reduce_amax, recompute, approx_gate):
+        amax, y = ops.swiglu_amax(a, b, not recompute, approx_gate)
         if reduce_amax and dist.is_initialized():
             dist.all_reduce(amax, op=dist.ReduceOp.MAX)
         if recompute:
@@ -98,14 +98,15 @@ class _SwiGLUToFloat8(torch.autograd.Function):
             data, _, scale = ops.cast_from_amax(y, amax, _kind(float8_dtype), False)
             del y  # a temporary: nothing keeps it for backward
         ctx.save_for_backward(a, b)
+        ctx.approx_gate = approx_gate
         return Float8Tensor(data, scale, a.dtype, linear_mm_config, gemm_input_role)
 
     @staticmethod
     def backward(ctx, g):
         # y = silu(a) * b:  dy/db = silu(a),  dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))
         a, b = ctx.saved_tensors
-        da, db = ops.swiglu_bwd(a, b, g if g.dtype == a.dtype else g.to(a.dtype))
-        return da, db, None, None, None, None, None
+        da, db = ops.swiglu_bwd(a, b, g if g.dtype == a.dtype else g.to(a.dtype), ctx.approx_gate)
+        return da, db, None, None, None, None, None, None
 
 
 def swiglu_to_float8_dynamic(
@@ -116,15 +117,24 @@ def swiglu_to_float8_dynamic(
     gemm_input_role: GemmInputRole = GemmInputRole.INPUT,
     reduce_amax: bool = False,
     recompute: bool = False,
+    approx_gate: bool = False,
 ) -> Float8Tensor:
     """fp8(silu(a) * b) with a dynamic per-tensor scale in two launches and 9 bytes of traffic
     per element (17 unfused).  `a` and `b` share shape and dtype; they may be column slices of one
     fused w1|w3 output.  By default the first launch writes the gate output once (a temporary in
     the input dtype, freed on return) while it takes the amax, and the second is the plain cast;
     `recompute=True` never writes it and evaluates the gate in both launches instead (no
-    temporary, same bytes moved, more arithmetic: slower).  Both give the same bytes."""
+    temporary, same bytes moved, more arithmetic: slower).  Both give the same bytes.
+
+    `approx_gate=True` (opt-in; 16-bit inputs whose last dimension is a multiple of 8, not with
+    `recompute`) evaluates the sigmoid with the hardware's approximate exp2 and reciprocal in forward and
+    backward: the gate output, its amax and the gradients are within one ulp of the input dtype of the exact
+    path's, hence every fp8 byte within one fp8 step; shapes the approximate kernels do not cover raise."""
     if a.numel() == 0:
         raise RuntimeError("swiglu_to_float8_dynamic: empty input (amax of an empty tensor is undefined)")
+    if approx_gate and recompute:
+        raise RuntimeError("swiglu_to_float8_dynamic: approx_gate needs the gate output written once (recompute=False)")
     return _SwiGLUToFloat8.apply(
-        a, b, float8_dtype, linear_mm_config or LinearMMConfig(), gemm_input_role, reduce_amax, recompute
+        a, b, float8_dtype, linear_mm_config or LinearMMConfig(), gemm_input_role, reduce_amax, recompute,
+        approx_gate
     )

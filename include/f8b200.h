@@ -351,6 +351,20 @@ int f8b200_swiglu_amax(const void* a, const void* b, int hp_dtype, int64_t rows,
 int f8b200_swiglu_cast(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
                        int64_t ld_a, int64_t ld_b, const float* amax, int fp8_kind,
                        float* scale_out, void* out, int64_t ld_out, void* stream);
+/*
+ * Opt-in approximate gate: f8b200_swiglu_amax with sigmoid(a) = rcp.approx(1 + ex2.approx(-a * log2 e))
+ * (about 2^-21 relative error in fp32) in place of the correctly rounded division and expf; the
+ * roundings to T are the same.  RN_T(silu(a)) is then the exact path's value except where that lies
+ * within ~2^-12 ulp of a rounding boundary of T, where it is the neighbouring T value: y, and the
+ * amax, are within one ulp of T of the exact path's, so every fp8 byte of the cast that follows is
+ * within one fp8 step.  Issue-bound like the exact kernel, with about a third fewer instructions per
+ * element.  16-bit dtypes with cols a multiple of 8 and 16-byte aligned rows only
+ * (F8B200_ERR_UNSUPPORTED otherwise).  No reference counterpart (the reference evaluates the gate
+ * with the framework's exact ops).
+ */
+int f8b200_swiglu_amax_approx(const void* a, const void* b, int hp_dtype, int64_t rows, int64_t cols,
+                              int64_t ld_a, int64_t ld_b, void* y_out, int64_t ld_y, float* amax_out,
+                              void* stream);
 
 /*
  * Backward of the two fused producers (the casts are transparent to autograd:
@@ -378,6 +392,11 @@ int f8b200_rmsnorm_bwd(const void* x, const void* grad_y, int hp_dtype, int64_t 
 int f8b200_swiglu_bwd(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
                       int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
                       int64_t ld_out, void* stream);
+/* f8b200_swiglu_bwd with the approximate sigmoid of f8b200_swiglu_amax_approx (same restrictions):
+ * da and db within one ulp of T of the exact path's. */
+int f8b200_swiglu_bwd_approx(const void* a, const void* b, const void* grad_y, int hp_dtype, int64_t rows,
+                             int64_t cols, int64_t ld_a, int64_t ld_b, int64_t ld_g, void* da, void* db,
+                             int64_t ld_out, void* stream);
 
 /*
  * Reads and clears the device error word of the current device (synchronises the

@@ -145,7 +145,7 @@ def _rmsnorm_bwd(x, grad_y, weight, rstd):
     return dx.to(x.dtype).reshape(x.shape), dw.to(weight.dtype)
 
 
-def _swiglu_bwd(a, b, grad_y):
+def _swiglu_bwd(a, b, grad_y, approx=False):
     """Gradient of `silu(a) * b` (profile_linear_float8.py:117-118):
     dy/db = silu(a), dy/da = b * sigmoid(a) * (1 + a * (1 - sigmoid(a)))."""
     a32, g32 = a.float(), grad_y.reshape(a.shape).float()
@@ -155,7 +155,7 @@ def _swiglu_bwd(a, b, grad_y):
     return da.to(a.dtype), db.to(b.dtype)
 
 
-def _swiglu_amax(a, b, write_y):
+def _swiglu_amax(a, b, write_y, approx=False):
     name = _HP[a.dtype]
     y = O.swiglu(to_np(a), to_np(b), name)
     amax = np.float32(np.nan) if np.isnan(y).any() else np.float32(np.abs(y).max())

@@ -123,6 +123,56 @@ def test_fused_swiglu_full_size_against_unfused_composition_on_gpu():
         _close_fp8(fused._data, ref._data, 1e-4)
 
 
+def _fp8_code_steps(x, y):
+    """Distance in fp8 codes along the real line (sign-magnitude bytes made monotonic)."""
+    def key(t):
+        u = t.view(torch.uint8).to(torch.int16)
+        return torch.where(u >= 128, 127 - u, u)  # -0 -> -1, negative codes descend
+    return (key(x) - key(y)).abs()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2048, 4096), (3, 40, 264), (512, 28672)])
+def test_fused_swiglu_approximate_gate_is_within_one_step_of_the_exact_one(dtype, shape):
+    """`approx_gate=True`: sigmoid from the approximate exp2 and reciprocal.  The stated bound: the amax (and
+    with it the scale) within one ulp of the input dtype of the exact path's, every fp8 byte within one
+    fp8 step, gradients within one ulp of the input dtype.  Most bytes are identical."""
+    torch.manual_seed(shape[-1] + 7)
+    h = (torch.randn(*shape[:-1], 2 * shape[-1], device="cuda") * 3).to(dtype)
+    a = h[..., : shape[-1]].detach().requires_grad_(True)
+    b = h[..., shape[-1]:].detach().requires_grad_(True)
+    a2, b2 = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    g = torch.randn(shape, device="cuda").to(dtype)
+    exact = swiglu_to_float8_dynamic(a, b)
+    fast = swiglu_to_float8_dynamic(a2, b2, approx_gate=True)
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    rel = abs(fast._scale.item() / exact._scale.item() - 1.0)
+    assert rel <= 2.0 * ulp, rel
+    steps = _fp8_code_steps(fast._data, exact._data)
+    assert steps.max().item() <= 1
+    if fast._scale.item() == exact._scale.item():
+        assert (steps != 0).float().mean().item() <= 2e-3
+    exact.backward(g)
+    fast.backward(g)
+    for got, ref in ((a2.grad, a.grad), (b2.grad, b.grad)):
+        assert got.dtype == dtype
+        err = (got.float() - ref.float()).abs()
+        assert bool((err <= 2.0 * ulp * ref.float().abs() + 1e-5).all())  # (1 + a (1 - sig)) cancels near a = -1.28
+        assert (got != ref).float().mean().item() <= 2e-3
+
+
+def test_fused_swiglu_approximate_gate_refuses_what_it_does_not_cover():
+    a = torch.randn(8, 40, device="cuda", dtype=torch.float32)
+    with pytest.raises(RuntimeError):
+        swiglu_to_float8_dynamic(a, a, approx_gate=True)          # fp32
+    h = torch.randn(8, 36, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        swiglu_to_float8_dynamic(h, h, approx_gate=True)          # columns not a multiple of 8
+    c = torch.randn(8, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        swiglu_to_float8_dynamic(c, c, approx_gate=True, recompute=True)
+
+
 def _sqnr(ref, got):
     ref, got = ref.double(), got.double()
     return 20 * torch.log10(ref.norm() / (ref - got).norm()).item()
