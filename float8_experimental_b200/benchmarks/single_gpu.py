@@ -9,6 +9,7 @@ profile_linear_float8.py (the norm -> linear fragments)."""
 from __future__ import annotations
 
 import os
+import statistics
 import time
 
 M_TOKENS = 16384
@@ -237,9 +238,34 @@ def measure_ffn_fragment(torch, f8, dev):
 
 
 
-def _sustained_ms(torch, fn, seconds: float = 0.6) -> float:
+_NVML_HANDLES = {}
+
+
+def _sm_clock_mhz(torch):
+    """Current SM clock of torch's current device read through NVML (a query; nothing is set), or None."""
+    dev = torch.cuda.current_device()
+    if dev not in _NVML_HANDLES:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+            _NVML_HANDLES[dev] = (pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid))
+        except Exception:  # noqa: BLE001
+            _NVML_HANDLES[dev] = None
+    entry = _NVML_HANDLES[dev]
+    if entry is None:
+        return None
+    try:
+        return float(entry[0].nvmlDeviceGetClockInfo(entry[1], entry[0].NVML_CLOCK_SM))
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def _sustained_ms(torch, fn, seconds: float = 0.6, clock_samples=None) -> float:
     """Mean time of `fn` repeated back to back for about `seconds` (power-capped parts settle at
-    their sustained clock within a fraction of a second), CUDA events on the current stream."""
+    their sustained clock within a fraction of a second), CUDA events on the current stream.
+    With `clock_samples` (a list) the SM clock is read every 20 ms while the queued work runs."""
     fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -252,6 +278,13 @@ def _sustained_ms(torch, fn, seconds: float = 0.6) -> float:
     for _ in range(iters):
         fn()
     e1.record()
+    if clock_samples is not None:
+        while not e1.query():
+            mhz = _sm_clock_mhz(torch)
+            if mhz is None:
+                break
+            clock_samples.append(mhz)
+            time.sleep(0.02)
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
 
@@ -275,7 +308,8 @@ def gemm_sweep(variants, shapes=None, seconds: float = 0.6, emit=None):
     mc41 (the single-GPU multicast library), auto (the default choice), cublaslt (torch._scaled_mm);
     suffix -static = fixed tile stride, -direct = per-thread store epilogue, -tma / -smem = TMA-store epilogue /
     warp-written whole lines after staging in shared memory (default: TMA stores).  Returns (rows,
-    totals_ms); `emit(row)` is called per GEMM."""
+    totals_ms); `emit(row)` is called per GEMM.  Every entry also carries the median SM clock read while
+    it ran ("sm_mhz"), so that time x clock (cycles) can be compared where the power limit moves the clock."""
     import torch
 
     from .. import _native as N
@@ -303,9 +337,12 @@ def gemm_sweep(variants, shapes=None, seconds: float = 0.6, emit=None):
                     if base == "auto":
                         os.environ.pop("F8B200_GEMM_MC", None)
                     fn = lambda: N.gemm_fp8(a, k, b, k, one, one, None, out, n, m, n, k, False)  # noqa: E731
-                ms = _sustained_ms(torch, fn, seconds)
+                clocks = []
+                ms = _sustained_ms(torch, fn, seconds, clocks)
                 totals[v] += ms
                 row[v] = {"ms": round(ms, 4), "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}
+                if clocks:
+                    row[v]["sm_mhz"] = statistics.median(clocks)
             rows.append(row)
             if emit is not None:
                 emit(row)
@@ -324,7 +361,17 @@ def measure_gemm_vs_cublaslt(seconds: float = 0.35):
     (`torch._scaled_mm`, the kernel the reference calls: float8_python_api.py:43-63), sustained,
     same process, same operands."""
     rows, totals = gemm_sweep(["auto", "cublaslt"], seconds=seconds)
+    clocked = all("sm_mhz" in r[v] for r in rows for v in ("auto", "cublaslt"))
+
+    def mcycles(v):  # sum over the GEMMs of time x median SM clock while it ran, in millions of SM cycles
+        return round(sum(r[v]["ms"] * r[v]["sm_mhz"] for r in rows) / 1e3, 2) if clocked else None
+
+    def mean_mhz(v):  # time-weighted
+        return round(sum(r[v]["ms"] * r[v]["sm_mhz"] for r in rows) / sum(r[v]["ms"] for r in rows), 1) if clocked else None
+
     return {"ours_ms": totals["auto"], "cublaslt_ms": totals["cublaslt"],
+            "ours_sm_mhz": mean_mhz("auto"), "cublaslt_sm_mhz": mean_mhz("cublaslt"),
+            "ours_mcycles": mcycles("auto"), "cublaslt_mcycles": mcycles("cublaslt"),
             "per_shape_tflops": {r["gemm"]: [r["auto"]["tflops"], r["cublaslt"]["tflops"]] for r in rows},
             "how": f"each GEMM back to back for {seconds} s per variant, CUDA events, bf16 output, K-major operands"}
 
