@@ -340,6 +340,62 @@ def case_cast_all_gather_over_peer_memory(rank, world, port):
     dist.destroy_process_group()
 
 
+def case_fsdp1_composition(rank, world, port, weight_dynamic):
+    """Float8Linear under the first-generation FSDP wrapper (flat parameters, `use_orig_params=True`), the
+    procedure of the reference's test/test_fsdp.py:68-184: a two-layer model, once in the base dtype and
+    once converted to float8 (input and grad_output delayed, weight delayed or dynamic), both wrapped,
+    two SGD iterations on per-rank slices of one global batch with `sync_float8_amax_and_scale_history`
+    after each float8 backward; the gathered outputs and the full parameters of the two models must agree
+    to more than 15 dB."""
+    _init(rank, world, port)
+    import float8_experimental_b200 as f8
+    from float8_experimental_b200.float8_utils import compute_error
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+
+    batch, seq, k, n = 8, 8, 32, 32
+    dtype = torch.bfloat16 if DEVICE == "cuda" else torch.float32
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(k, n, dtype=dtype), nn.ReLU(), nn.Linear(n, n, dtype=dtype)).to(DEVICE)
+    model_f8 = copy.deepcopy(base)
+    delayed = f8.CastConfig(scaling_type=f8.ScalingType.DELAYED)
+    config = f8.Float8LinearConfig(
+        cast_config_input=delayed, cast_config_grad_output=delayed,
+        cast_config_weight=f8.CastConfig(scaling_type=f8.ScalingType.DYNAMIC) if weight_dynamic else delayed)
+    f8.convert_to_float8_training(model_f8, config=config)
+    device_id = torch.device("cuda", rank) if DEVICE == "cuda" else torch.device("cpu")
+    base = FSDP(base, use_orig_params=True, device_id=device_id)
+    model_f8 = FSDP(model_f8, use_orig_params=True, device_id=device_id)
+    opt = torch.optim.SGD(base.parameters(), lr=0.01)
+    opt_f8 = torch.optim.SGD(model_f8.parameters(), lr=0.01)
+    lo, hi = rank * batch // world, (rank + 1) * batch // world
+    xs = [torch.randn(batch, seq, k, device=DEVICE).to(dtype)[lo:hi] for _ in range(2)]
+    gs = [torch.randn(batch, seq, n, device=DEVICE).to(dtype)[lo:hi] for _ in range(2)]
+    y = y_f8 = None
+    for i in range(2):  # the second iteration is the first that casts with scales from the history
+        opt.zero_grad()
+        y = base(xs[i])
+        y.backward(gs[i])
+        opt.step()
+        opt_f8.zero_grad()
+        y_f8 = model_f8(xs[i])
+        y_f8.backward(gs[i])
+        assert f8.linear_requires_sync(config)
+        f8.sync_float8_amax_and_scale_history(model_f8)
+        opt_f8.step()
+    whole = torch.cat(_all_gather_list(y.detach(), world))
+    whole_f8 = torch.cat(_all_gather_list(y_f8.detach(), world))
+    assert compute_error(whole, whole_f8).item() > 15.0
+    # the reference compares full state dicts; gathering the full parameters compares the same tensors
+    with FSDP.summon_full_params(base), FSDP.summon_full_params(model_f8):
+        full = dict(base.named_parameters())
+        full_f8 = dict(model_f8.named_parameters())
+        assert len(full) == 4 and full.keys() == full_f8.keys()
+        for name, v in full.items():
+            assert compute_error(v.detach().float(), full_f8[name].detach().float()).item() > 15.0, name
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def case_package_parity(rank, world, port, name):
     """The parity checks the benchmark runs before it times anything on several GPUs
     (`float8_experimental_b200.benchmarks.multi_gpu`), one by one.  GPU only."""

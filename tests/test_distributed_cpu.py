@@ -59,3 +59,8 @@ def test_sequence_parallel_with_fused_reduce_scatter_route():
     """The row-parallel layer's fused GEMM + reduce-scatter route (host side; the peer-memory GEMM is
     replaced by a stand-in on CPU ranks) still equals the unsharded model."""
     _run("case_tensor_parallel", True, True)
+
+
+@pytest.mark.parametrize("weight_dynamic", [False, True])
+def test_fsdp1_flat_parameter_wrapper_composes_with_float8_linear(weight_dynamic):
+    _run("case_fsdp1_composition", weight_dynamic)

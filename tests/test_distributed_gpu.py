@@ -68,3 +68,8 @@ def test_cast_all_gather_over_peer_memory():
 def test_benchmark_parity_checks(name):
     """Each check of the block that `bench.py --gpus N` runs before timing (N > 1), here on two ranks."""
     _run("case_package_parity", name)
+
+
+@pytest.mark.parametrize("weight_dynamic", [False, True])
+def test_fsdp1_flat_parameter_wrapper_composes_with_float8_linear(weight_dynamic):
+    _run("case_fsdp1_composition", weight_dynamic)
