@@ -513,9 +513,49 @@ def measure_llama3_8b_linears(torch, dev, steps: int = 3, n_blocks: int = 32, se
         ms = e0.elapsed_time(e1) / steps
         return {"ms_per_step": ms, "tflops": flops / ms / 1e9, "host_enqueue_ms_per_step": host_ms}
 
+    def timed_graph(model):
+        """The same step captured once into a CUDA graph and replayed: no host work per layer."""
+        def step():
+            model(x).backward(go)
+
+        def clear():
+            x.grad = None
+            for p in model.parameters():
+                p.grad = None
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                clear()
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        clear()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        del graph
+        clear()
+        return {"ms_per_step": ms, "tflops": flops / ms / 1e9}
+
     model = build()
     f8.convert_to_float8_training(model, config=f8.Float8LinearConfig())
     out["ours"] = timed(model)
+    try:
+        out["ours_cuda_graph"] = timed_graph(model)
+    except Exception as exc:  # noqa: BLE001
+        torch.cuda.synchronize()
+        out["ours_cuda_graph"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     os.environ["F8B200_LINEAR_SINGLE_NODE"] = "0"
     try:
         out["ours_general_route"] = timed(model)
