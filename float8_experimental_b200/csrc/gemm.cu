@@ -25,6 +25,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -1994,15 +1995,23 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
 
 // Kernel choice: 0 = one CTA per 128x256 tile, 1 = CTA pairs on 256x256 tiles (cta_group::2, two accumulators),
 // 2 = one CTA per 256x256 tile, 3 = CTA pairs on 512x256 tiles (cta_group::2, one 256x256 accumulator per CTA).
-// Default: kernel 3 whenever the problem has more than 256 rows.  It moves 25 % fewer operand bytes from L2 per
-// flop than the others (48 KB per k-block for 256x256 of output against 64 KB), which on a power-capped part is
-// worth more than the fully hidden epilogue of kernel 1, and its split accumulator drain hides half of its own:
-// sustained over the twelve GEMMs of the LLaMa-2-70B step it measured 33.6 ms against 35.1 ms for kernel 1 alone
-// and 34.1 ms for the earlier rule (kernel 1 for K < 16384, kernel 2 above), ahead on every shape.  With at most
-// 256 rows a 512-row tile would be half empty: kernel 1.
-// F8B200_GEMM_MODE ("1cta" / "2cta" / "wide" / "pw") forces one kernel; F8B200_GEMM_WIDE_K=<k> restores the earlier
-// rule with that threshold.  Both are read at every call so that tests can exercise every kernel in one process.
-static int gemm_mode(int64_t m, int64_t k) {
+// Kernel 3 moves 25 % fewer operand bytes from L2 per flop than the others (48 KB per k-block for 256x256 of
+// output against 64 KB), which on a power-capped part is worth more than the fully hidden epilogue of kernel 1:
+// sustained over the twelve GEMMs of the LLaMa-2-70B step (M = 16384, K >= 8192) it measured 33.6 ms against
+// 35.1 ms for kernel 1, ahead or level on every shape.  Kernel 1 is the better one where kernel 3's price shows:
+// (a) its accumulator drain is only partly overlapped (about 2500 cycles per tile stay exposed, which is 7 %
+// of a K = 4096 tile), and (b) its tiles are twice as large, so a product of a few hundred tiles fills the
+// last wave worse (256 tiles on 74 pairs: 4 waves for the work of 3.46).  The rule below scores both kernels,
+// score = (tiles / (waves x pairs)) x (share of a tile's time that is MMA work, with kernel 1's larger operand
+// traffic as a penalty that grows with K), and takes kernel 1 only when it scores 4 % better, which keeps
+// kernel 3 on every product of the 70B step.  Measured on the LLaMa-3-8B products (M = 8192; K, N in 1024 /
+// 4096 / 14336) the rule's choices are 2-4 % faster than kernel 3 alone (and 1.5x on the 1024 x 4096 x 8192
+// weight gradient, whose 32 large tiles leave most pairs idle).  With at most 256 rows a 512-row tile would be
+// half empty: kernel 1.
+// F8B200_GEMM_MODE ("1cta" / "2cta" / "wide" / "pw") forces one kernel; F8B200_GEMM_WIDE_K=<k> restores an earlier
+// rule (kernel 1 below that K, kernel 2 above).  Both are read at every call so that tests can exercise every
+// kernel in one process.
+static int gemm_mode(int64_t m, int64_t n, int64_t k) {
   const char* e = getenv("F8B200_GEMM_MODE");
   if (e != nullptr && e[0] == '1') return 0;
   if (e != nullptr && e[0] == '2') return 1;
@@ -2010,7 +2019,18 @@ static int gemm_mode(int64_t m, int64_t k) {
   if (e != nullptr && e[0] == 'p') return 3;
   const char* t = getenv("F8B200_GEMM_WIDE_K");
   if (t != nullptr && t[0] != 0) return k >= atoll(t) ? 2 : 1;
-  return m > 256 ? 3 : 1;
+  if (m <= 256) return 1;
+  const double pairs = (double)(persistent_ctas() / 2 > 0 ? persistent_ctas() / 2 : 1);
+  auto fill = [&](int64_t tile_m) {  // share of the pair-waves' capacity that the product's tiles use
+    const double tiles = (double)((m + tile_m - 1) / tile_m) * (double)((n + 255) / 256);
+    const double waves = (double)(int64_t)((tiles + pairs - 1) / pairs);
+    return tiles / (waves * pairs);
+  };
+  const double kb = (double)((k + 127) / 128);
+  const double busy_wide = kb * 1024.0 / (kb * 1024.0 + 2500.0);
+  double busy_pair = 0.963;
+  if (k > 8192) busy_pair -= 0.02 * log2((double)k / 8192.0);
+  return fill(256) * busy_pair > 1.04 * fill(512) * busy_wide ? 1 : 3;
 }
 
 }  // namespace gemm
@@ -2100,7 +2120,7 @@ static int gemm_fp8_impl(const void* a, int a_kind, int a_layout, int64_t lda, c
     return b_layout ? gemm::encode_operand_map_mn(&mb, b, n, k, ldb)
                     : gemm::encode_operand_map(&mb, b, n, k, ldb, box_rows_b > 0 ? box_rows_b : box_rows);
   };
-  int mode = gemm::gemm_mode(m, k);
+  int mode = gemm::gemm_mode(m, n, k);
   if (mode == 3) {
     // CTA pairs on 512x256 tiles: each CTA fetches a 256-row box of A and a 128-row box of B
     rc = encode_operands(256, 128);
@@ -2296,8 +2316,7 @@ extern "C" int f8b200_gemm_fp8_scatter_rows(const void* a, int a_kind, int a_lay
 }
 
 extern "C" int f8b200_gemm_kernel_choice(int64_t m, int64_t n, int64_t k) {
-  (void)n;
-  return gemm::gemm_mode(m, k);
+  return gemm::gemm_mode(m, n, k);
 }
 
 extern "C" int f8b200_check_device_error(void) {

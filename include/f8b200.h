@@ -260,9 +260,10 @@ int f8b200_sum_slots(const void* slots, int n_slots, int64_t slot_stride, int hp
 /*
  * Which kernel f8b200_gemm_fp8 / _ws would run for an m x n x k product with the current
  * environment: 0 = one CTA per 128x256 tile, 1 = CTA pair per 256x256 tile, 2 = one CTA per
- * 256x256 tile, 3 = CTA pair per 512x256 tile (the default above 256 rows).  All four return
- * the same bits; the choice is a matter of speed.  Reporting aid for benchmarks; host only, no
- * CUDA call.  (cuBLASLt's heuristic behind torch._scaled_mm, float8_python_api.py:43-63, is the
+ * 256x256 tile, 3 = CTA pair per 512x256 tile.  Default: 3 for large products with K >= 8192, 1 where
+ * the larger tiles would fill the last wave of CTA pairs badly or K is short (and for at most 256
+ * rows).  All four return the same bits; the choice is a matter of speed.  Reporting aid for benchmarks; host only (it reads
+ * the SM count of the current device and assumes 148 without one).  (cuBLASLt's heuristic behind torch._scaled_mm, float8_python_api.py:43-63, is the
  * reference-side counterpart.)
  */
 int f8b200_gemm_kernel_choice(int64_t m, int64_t n, int64_t k);

@@ -95,3 +95,24 @@ def test_bindings_are_well_formed():
         status, name = call.args
         assert isinstance(name, ast.Constant) and name.value in _native.EXPORTS, call.lineno
         assert isinstance(status, ast.Call) and status.func.attr == name.value, call.lineno
+
+
+def test_default_gemm_kernel_choice(monkeypatch):
+    """Host-side rule behind f8b200_gemm_fp8: CTA pairs on 512x256 tiles for the large long-K products (every
+    GEMM of the LLaMa-2-70B step), CTA pairs on 256x256 tiles where the large tiles would fill the last wave
+    badly, K is short, or there are at most 256 rows; the environment can force any kernel."""
+    for var in ("F8B200_GEMM_MODE", "F8B200_GEMM_WIDE_K", "F8B200_GEMM_SM_MARGIN"):
+        monkeypatch.delenv(var, raising=False)
+    choice = _native.gemm_kernel_choice
+    m = 16384
+    for k, n in ((8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192)):
+        assert [choice(m, n, k), choice(m, k, n), choice(n, k, m)] == [3, 3, 3], (k, n)
+    assert choice(8192, 4096, 4096) == 1      # K = 4096: the exposed part of the drain weighs 7 %
+    assert choice(1024, 4096, 8192) == 1      # 32 large tiles would leave most CTA pairs idle
+    assert choice(8192, 4096, 14336) == 1     # 256 large tiles: 4 waves for the work of 3.46
+    assert choice(4096, 4096, 8192) == 3
+    assert choice(256, 8192, 8192) == 1 and choice(257, 8192, 8192) in (1, 3)
+    monkeypatch.setenv("F8B200_GEMM_MODE", "wide")
+    assert choice(m, 8192, 8192) == 2
+    monkeypatch.setenv("F8B200_GEMM_MODE", "pw")
+    assert choice(8192, 4096, 4096) == 3
