@@ -28,7 +28,13 @@ def _entry(rank, case, world, port, extra):
 
 
 def _run(case, *extra):
-    mp.spawn(_entry, args=(case, WORLD, _free_port(), extra), nprocs=WORLD, join=True)
+    for attempt in range(3):  # the probed port can be taken again before rank 0 listens on it
+        try:
+            mp.spawn(_entry, args=(case, WORLD, _free_port(), extra), nprocs=WORLD, join=True)
+            return
+        except Exception as exc:  # noqa: BLE001
+            if "EADDRINUSE" not in str(exc) or attempt == 2:
+                raise
 
 
 def test_sync_all_reduces_amaxes_once():
