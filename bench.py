@@ -508,7 +508,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             fused_norm = side(single_gpu.measure_fused_norm, torch, dev, xs[0].detach())
             if full and "error" not in fused_norm:
                 fused_norm["ffn_fragment"] = side(single_gpu.measure_ffn_fragment, torch, f8, dev)
-    if world > 1 and full:
+    if world > 1 and args.layers is None:
         # where the N > 1 step spends its device time (all ranks run the steps, rank 0 profiles)
         if rank == 0:
             comm_split = side(multi_gpu.profile_step_split, step, dev)

@@ -477,4 +477,79 @@ def profile_step_split(step, dev, steps: int = 2):
             kinds["memcpy_memset"] += us
         else:
             kinds["other_kernels"] += us
-    return {k: round(v / steps / 1e3, 3) for k, v in kinds.items()} | {"unit": "ms of device time per step", "steps": steps}
+    out = {k: round(v / steps / 1e3, 3) for k, v in kinds.items()} | {"unit": "ms of device time per step", "steps": steps}
+    try:
+        out["timeline"] = _timeline_of(prof, steps)
+    except Exception as exc:  # noqa: BLE001
+        out["timeline"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    return out
+
+
+def _timeline_of(prof, steps):
+    """Where the step's wall time goes on the stream that runs the GEMMs, from the profiler's kernel
+    timeline: time that stream is busy, time it idles while an NCCL kernel runs on another stream (the
+    exposed communication), and time it idles with nothing running anywhere (host-side gaps)."""
+    import json
+    import tempfile
+
+    with tempfile.NamedTemporaryFile(suffix=".json") as f:
+        prof.export_chrome_trace(f.name)
+        trace = json.load(open(f.name))
+    kernels = [e for e in trace.get("traceEvents", []) if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")
+               and "dur" in e and "ts" in e]
+    if not kernels:
+        return {"error": "no kernel events in the trace"}
+    stream_of = lambda e: e.get("args", {}).get("stream")  # noqa: E731
+    gemm_streams = {}
+    for e in kernels:
+        if "gemm_fp8" in e["name"]:
+            gemm_streams[stream_of(e)] = gemm_streams.get(stream_of(e), 0.0) + e["dur"]
+    if not gemm_streams:
+        return {"error": "no GEMM kernels in the trace"}
+    main = max(gemm_streams, key=gemm_streams.get)
+    t0 = min(e["ts"] for e in kernels)
+    t1 = max(e["ts"] + e["dur"] for e in kernels)
+
+    def merged(events):
+        spans = sorted((e["ts"], e["ts"] + e["dur"]) for e in events)
+        out_spans = []
+        for a, b in spans:
+            if out_spans and a <= out_spans[-1][1]:
+                out_spans[-1][1] = max(out_spans[-1][1], b)
+            else:
+                out_spans.append([a, b])
+        return out_spans
+
+    def overlap(spans_a, spans_b):
+        i = j = 0
+        tot = 0.0
+        while i < len(spans_a) and j < len(spans_b):
+            lo, hi = max(spans_a[i][0], spans_b[j][0]), min(spans_a[i][1], spans_b[j][1])
+            if hi > lo:
+                tot += hi - lo
+            if spans_a[i][1] < spans_b[j][1]:
+                i += 1
+            else:
+                j += 1
+        return tot
+
+    busy = merged([e for e in kernels if stream_of(e) == main])
+    idle, prev = [], t0
+    for a, b in busy:
+        if a > prev:
+            idle.append([prev, a])
+        prev = max(prev, b)
+    if t1 > prev:
+        idle.append([prev, t1])
+    nccl = merged([e for e in kernels if "nccl" in e["name"].lower() and stream_of(e) != main])
+    others = merged([e for e in kernels if stream_of(e) != main])
+    busy_ms = sum(b - a for a, b in busy) / 1e3 / steps
+    idle_ms = sum(b - a for a, b in idle) / 1e3 / steps
+    idle_nccl = overlap(idle, nccl) / 1e3 / steps
+    idle_other = overlap(idle, others) / 1e3 / steps
+    gaps = sorted(((b - a) / 1e3 for a, b in idle), reverse=True)[:6]
+    return {"span_ms_per_step": round((t1 - t0) / 1e3 / steps, 3), "gemm_stream_busy_ms": round(busy_ms, 3),
+            "gemm_stream_idle_ms": round(idle_ms, 3), "idle_while_nccl_runs_ms": round(idle_nccl, 3),
+            "idle_while_any_other_stream_runs_ms": round(idle_other, 3),
+            "idle_with_nothing_running_ms": round(idle_ms - idle_other, 3),
+            "largest_idle_gaps_ms": [round(g, 3) for g in gaps]}
