@@ -1819,7 +1819,9 @@ static int choose_raster(int64_t m, int64_t n, int64_t k, int tile_m, int tile_n
   const double cost_m = a_bytes + b_bytes * (double)((tiles_m + gm - 1) / gm);
   const double cost_n = b_bytes + a_bytes * (double)((tiles_n + gn - 1) / gn);
   // L2 hints (bit 0: output stores evict-first, bit 1: streaming operand evict-first,
-  // bit 2: panel operand evict-last); F8B200_GEMM_L2HINT overrides the default.
+  // bit 2: panel operand evict-last); F8B200_GEMM_L2HINT overrides the default.  An operand without a
+  // hint bit is loaded with no cache-hint operand at all (see l2_policy: that is what lets the L2 request
+  // coalescer merge its loads), so the default asks for none.
   int hints = 1;
   if (const char* e = getenv("F8B200_GEMM_L2HINT")) hints = atoi(e) & 7;
   return (cost_n < cost_m ? (int)(gn | (1 << 16)) : (int)gm) | (hints << 20);
