@@ -3,7 +3,7 @@ benchmark's reference arm and the tests can import `float8_experimental` itself 
 the reference checkout is not mounted.  TEST / BENCHMARK INFRASTRUCTURE ONLY: nothing in the
 product package imports it.
 
-    python oracle/make_ref.py [path-to-reference-checkout]        (default: /root/reference)
+    python oracle/make_ref.py [path-to-reference-checkout]        (default: REFERENCE_ROOT below)
 
 The reference is pure Python (no native code to compile) and declares `hatchling` as its build
 backend, which an offline `pip install --no-index` cannot satisfy; the recipe therefore copies the
@@ -20,9 +20,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 PACKAGE = "float8_experimental"
+REFERENCE_ROOT = os.environ.get("F8_REFERENCE_ROOT", "/root/reference")  # where the build machine mounts the checkout
 
 
-def make_ref(reference_root: str = "/root/reference"):
+def make_ref(reference_root: str = REFERENCE_ROOT):
     src = os.path.join(reference_root, PACKAGE)
     if not os.path.isdir(src):
         return None
