@@ -86,6 +86,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same probe with a suspend-time hint: the hardware may keep the thread suspended for up to about
+// `hint_ns` while the phase is incomplete and wakes it when the phase completes, so a long wait costs a few
+// probes instead of a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t WAIT_BY_HINT = 0x80000000u;  // flag in a `backoff_ns` argument: the rest is a suspend-time hint
+
 // Bounded wait.  Returns false when the budget ran out or another role already gave up.
 // `backoff_ns` > 0 puts the polling thread to sleep between probes: waits that are long
 // and off the critical path (ring slots coming free, a whole tile being accumulated)
@@ -1118,6 +1134,17 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -1181,12 +1208,17 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int a_kind, int b_kind, i
 template <bool CLUSTER_ACQUIRE = false, typename Bars = PairBarriers>
 __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, Bars* bars, uint32_t peer_rank,
                                           uint32_t who, uint32_t backoff_ns = 0) {
-  auto probe = [&]() { return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  const bool by_hint = (backoff_ns & WAIT_BY_HINT) != 0u;
+  const uint32_t hint = backoff_ns & ~WAIT_BY_HINT;
+  auto probe = [&]() {
+    if (by_hint) return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster_hint(bar, parity, hint) : mbar_try_wait_hint(bar, parity, hint);
+    return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity);
+  };
   if (probe()) return true;
   const long long t0 = clock64();
   for (uint32_t it = 0; it < 0x7FFFFFFFu; ++it) {
     if (probe()) return true;
-    if (backoff_ns != 0u) __nanosleep(backoff_ns);
+    if (backoff_ns != 0u && !by_hint) __nanosleep(backoff_ns);
     if ((it & 63u) == 63u) {
       if (bars->abort_flag != 0u) return false;
       if (clock64() - t0 > WAIT_BUDGET_CYCLES) break;
@@ -1445,6 +1477,7 @@ constexpr int QSTAGE_BYTES = QA_BYTES + QB_BYTES;
 constexpr int QTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int SPLIT_DRAIN_BIT = 26;  // bit of the packed `raster` word: overlap the epilogue by halves
 constexpr int SPLIT_TAIL_BIT = 27;   // and finish accumulator half 0 ahead of half 1 at the end of a tile
+constexpr int WAIT_SLEEP_BIT = 28;   // waits sleep between probes (or spin) instead of passing a suspend-time hint
 
 struct __align__(8) QBarriers {
   uint64_t full[QSTAGES];
@@ -1482,6 +1515,11 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
   const bool split_drain = (raster >> SPLIT_DRAIN_BIT) & 1;
   const bool split_tail = (raster >> SPLIT_TAIL_BIT) & 1;
+  // Waits pass a suspend-time hint to mbarrier.try_wait (the hardware parks the thread and wakes it when the
+  // phase completes) instead of sleeping between probes or spinning: 12-17 % fewer executed instructions and
+  // 0.4-0.5 % less time over the twelve GEMMs of the 70B step.  F8B200_GEMM_WAIT=sleep restores the loops.
+  const bool hw_wait = ((raster >> WAIT_SLEEP_BIT) & 1) == 0;
+  auto bo = [&](uint32_t ns) { return hw_wait ? (WAIT_BY_HINT | (ns == 0u ? 2000u : ns * 32u)) : ns; };
   const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
 
   if (threadIdx.x == 0) {
@@ -1530,7 +1568,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         int64_t next = t + num_clusters;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (sched != nullptr && leader && kb == claim_kb) next = num_clusters + (int64_t)atomicAdd(sched, 1u);
-          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
+          if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, bo(64u))) { ok = false; break; }
           uint8_t* sa = tiles + stage * QSTAGE_BYTES;
           if (leader) mbar_expect_tx(&bars->full[stage], 2 * QSTAGE_BYTES);
           const uint32_t full_in_leader = mapa_u32(smem_u32(&bars->full[stage]), 0u);
@@ -1553,7 +1591,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             st_cluster_u32(mapa_u32(smem_u32(&bars->ring.tile[slot]), 1u), (uint32_t)v);
             mbar_arrive_release_cluster(mapa_u32(smem_u32(&bars->ring.full[slot]), 1u));
           } else {
-            const int32_t v = pair_ring_read(bars, entry, peer, 64u, 32u);
+            const int32_t v = pair_ring_read(bars, entry, peer, 64u, bo(32u));
             if (v == -2) { ok = false; break; }
             next = v < 0 ? num_tiles : (int64_t)v;
           }
@@ -1563,7 +1601,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
       // tail: every release the leader multicast to this CTA's empty barriers has landed
       for (int s = 0; ok && s < QSTAGES; ++s) {
-        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, 64u)) { ok = false; break; }
+        if (!pair_wait(&bars->empty[stage], phase ^ 1u, bars, peer, 1u, bo(64u))) { ok = false; break; }
         if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
       }
       if (!ok) {
@@ -1592,7 +1630,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       };
       for (; ok && t < num_tiles; ++local) {
         const uint32_t free_parity = (uint32_t)(local & 1) ^ 1u;
-        if (!pair_wait(&bars->tmem_empty[0], free_parity, bars, peer, 2u)) { ok = false; break; }
+        if (!pair_wait(&bars->tmem_empty[0], free_parity, bars, peer, 2u, bo(0u))) { ok = false; break; }
         tc_fence_after();
         // head of the tile on accumulator half 0 alone, while the epilogue still drains half 1
         const int head = split_drain ? (num_kb < QSTAGES ? num_kb : QSTAGES) : 0;
@@ -1600,14 +1638,14 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           int st = stage;
           uint32_t ph = phase;
           for (int kb = 0; kb < head; ++kb) {
-            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u)) { ok = false; break; }
+            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u, bo(0u))) { ok = false; break; }
             tc_fence_after();
             issue_half(st, kb, 0);
             if (++st == QSTAGES) { st = 0; ph ^= 1u; }
           }
         }
         if (!ok) break;
-        if (!pair_wait(&bars->tmem_empty[1], free_parity, bars, peer, 2u)) { ok = false; break; }
+        if (!pair_wait(&bars->tmem_empty[1], free_parity, bars, peer, 2u, bo(0u))) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < head; ++kb) {  // these stages are known to be full
           issue_half(stage, kb, 1);
@@ -1619,7 +1657,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         int tail = split_tail ? (num_kb - head < QSTAGES ? num_kb - head : QSTAGES) : 0;
         if (tail < 0) tail = 0;
         for (int kb = head; kb < num_kb - tail; ++kb) {
-          if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u)) { ok = false; break; }
+          if (!pair_wait(&bars->full[stage], phase, bars, peer, 4u, bo(0u))) { ok = false; break; }
           tc_fence_after();
           issue_half(stage, kb, 0);
           issue_half(stage, kb, 1);
@@ -1631,7 +1669,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           int st = stage;
           uint32_t ph = phase;
           for (int kb = num_kb - tail; kb < num_kb; ++kb) {
-            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u)) { ok = false; break; }
+            if (!pair_wait(&bars->full[st], ph, bars, peer, 4u, bo(0u))) { ok = false; break; }
             tc_fence_after();
             issue_half(st, kb, 0);
             if (++st == QSTAGES) { st = 0; ph ^= 1u; }
@@ -1646,7 +1684,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
         tc_commit_pair(&bars->tmem_full[1]);
         if (sched != nullptr) {
-          const int32_t v = pair_ring_read(bars, (uint32_t)local, peer, 16u, 0u);
+          const int32_t v = pair_ring_read(bars, (uint32_t)local, peer, 16u, bo(0u));
           if (v == -2) { ok = false; break; }
           t = v < 0 ? num_tiles : (int64_t)v;
         } else {
@@ -1678,7 +1716,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
         int got = 1;
-        if (lane == 0) got = pair_wait(&bars->tmem_full[h], (uint32_t)(local & 1), bars, peer, 8u, 256u) ? 1 : 0;
+        if (lane == 0) got = pair_wait(&bars->tmem_full[h], (uint32_t)(local & 1), bars, peer, 8u, bo(256u)) ? 1 : 0;
         if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 256 + part * 128);
@@ -1691,7 +1729,7 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!ok) break;
       if (sched != nullptr) {
         int v = 0;
-        if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, 64u);
+        if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, bo(64u));
         v = __shfl_sync(0xFFFFFFFFu, v, 0);
         if (v == -2) { ok = false; break; }
         t = v < 0 ? num_tiles : (int64_t)v;
@@ -1990,6 +2028,8 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
     if (e[0] == '0') split = 0;
     if (e[0] == 'h') split = 1 << pairwide::SPLIT_DRAIN_BIT;
   }
+  if (const char* e = getenv("F8B200_GEMM_WAIT"))
+    if (e[0] == 's') split |= 1 << pairwide::WAIT_SLEEP_BIT;
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
                          choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched, scatter));
