@@ -221,6 +221,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32
 // (storage [rows, K], K contiguous), 1 = MN-major (storage [K, rows], rows contiguous).
 constexpr int LAYOUT_A_MN_BIT = 24;
 constexpr int LAYOUT_B_MN_BIT = 25;
+constexpr int WAIT_SLEEP_BIT = 28;  // 512x256 pair kernel: waits sleep between probes (or spin) instead of passing a suspend-time hint
 // Encoded-address step between consecutive K = 32 MMAs inside one 128-wide k-block.
 __device__ __forceinline__ uint64_t desc_k_step(bool mn_major) {
   return mn_major ? (uint64_t)((UMMA_K * 128) >> 4) : (uint64_t)(UMMA_K >> 4);
@@ -1477,7 +1478,6 @@ constexpr int QSTAGE_BYTES = QA_BYTES + QB_BYTES;
 constexpr int QTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int SPLIT_DRAIN_BIT = 26;  // bit of the packed `raster` word: overlap the epilogue by halves
 constexpr int SPLIT_TAIL_BIT = 27;   // and finish accumulator half 0 ahead of half 1 at the end of a tile
-constexpr int WAIT_SLEEP_BIT = 28;   // waits sleep between probes (or spin) instead of passing a suspend-time hint
 
 struct __align__(8) QBarriers {
   uint64_t full[QSTAGES];
@@ -1518,6 +1518,8 @@ gemm_fp8_pairwide_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   // Waits pass a suspend-time hint to mbarrier.try_wait (the hardware parks the thread and wakes it when the
   // phase completes) instead of sleeping between probes or spinning: 12-17 % fewer executed instructions and
   // 0.4-0.5 % less time over the twelve GEMMs of the 70B step.  F8B200_GEMM_WAIT=sleep restores the loops.
+  // (The 256x256 pair kernel keeps the loops: with hints its twelve LLaMa-3-8B products took 2.85-2.88 ms
+  // against 2.80 ms.)
   const bool hw_wait = ((raster >> WAIT_SLEEP_BIT) & 1) == 0;
   auto bo = [&](uint32_t ns) { return hw_wait ? (WAIT_BY_HINT | (ns == 0u ? 2000u : ns * 32u)) : ns; };
   const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
@@ -1907,6 +1909,12 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   return check_launch();
 }
 
+// F8B200_GEMM_WAIT=sleep (read at every call): the 512x256 pair kernel's waits sleep between probes
+static int wait_bits() {
+  const char* e = getenv("F8B200_GEMM_WAIT");
+  return (e != nullptr && e[0] == 's') ? (1 << WAIT_SLEEP_BIT) : 0;
+}
+
 template <typename OutT>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int use_tma,
                        const float* sa, const float* sb, const void* bias, void* out, int64_t ldo, int m, int n, int k,
@@ -2028,8 +2036,7 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
     if (e[0] == '0') split = 0;
     if (e[0] == 'h') split = 1 << pairwide::SPLIT_DRAIN_BIT;
   }
-  if (const char* e = getenv("F8B200_GEMM_WAIT"))
-    if (e[0] == 's') split |= 1 << pairwide::WAIT_SLEEP_BIT;
+  split |= wait_bits();
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
                          choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched, scatter));
