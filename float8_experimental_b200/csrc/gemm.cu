@@ -1,9 +1,11 @@
 // Scaled fp8 GEMM for sm_100a:  out[M,N] = (A[M,K] . B[N,K]^T) / (sa * sb) (+ bias).
 //
 // Four persistent, warp-specialised kernels share the device code of this file:
-//   pair-wide kernel (namespace pairwide, the default) two CTAs per 512x256 tile, two
-//                 tcgen05.mma.cta_group::2 per k-step, one 256x256 accumulator per CTA drained by halves;
-//   pair kernel   (namespace pair, default for at most 256 rows) two CTAs per 256x256 tile,
+//   pair-wide kernel (namespace pairwide, the default for large products with K >= 8192) two CTAs per
+//                 512x256 tile, two tcgen05.mma.cta_group::2 per k-step, one 256x256 accumulator per CTA
+//                 drained by halves;
+//   pair kernel   (namespace pair, the default for short K, for products whose 512x256 tiles would fill
+//                 the last wave badly and for at most 256 rows: see gemm_mode) two CTAs per 256x256 tile,
 //                 tcgen05.mma.cta_group::2, accumulators double buffered in tensor memory;
 //   wide kernel   (namespace wide) one CTA per 256x256 tile, two M128 N256 MMAs per k-step, the
 //                 accumulator fills tensor memory;
