@@ -223,6 +223,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32
 // (storage [rows, K], K contiguous), 1 = MN-major (storage [K, rows], rows contiguous).
 constexpr int LAYOUT_A_MN_BIT = 24;
 constexpr int LAYOUT_B_MN_BIT = 25;
+constexpr int EPI_ALL_POLL_BIT = 29;  // pair kernels: every epilogue warp polls the accumulator barrier itself (the earlier scheme)
 constexpr int WAIT_SLEEP_BIT = 28;  // 512x256 pair kernel: waits sleep between probes (or spin) instead of passing a suspend-time hint
 // Encoded-address step between consecutive K = 32 MMAs inside one 128-wide k-block.
 __device__ __forceinline__ uint64_t desc_k_step(bool mn_major) {
@@ -1263,6 +1264,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
   const int num_kb = (k + BK - 1) / BK;
   const int64_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const bool a_mn = (raster >> LAYOUT_A_MN_BIT) & 1, b_mn = (raster >> LAYOUT_B_MN_BIT) & 1;
+  const bool one_poller = ((raster >> EPI_ALL_POLL_BIT) & 1) == 0;
   const uint64_t step_a = desc_k_step(a_mn), step_b = desc_k_step(b_mn);
 
   if (threadIdx.x == 0) {
@@ -1410,8 +1412,19 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       int got = 1;
-      if (lane == 0) got = pair_wait(&bars->tmem_full[acc], acc_phase, bars, peer, 8u, 256u) ? 1 : 0;
-      if (__shfl_sync(0xFFFFFFFFu, got, 0) == 0) { ok = false; break; }
+      if (!one_poller || warp == 2) {
+        if (lane == 0) got = pair_wait(&bars->tmem_full[acc], acc_phase, bars, peer, 8u, 256u) ? 1 : 0;
+        got = __shfl_sync(0xFFFFFFFFu, got, 0);
+      }
+      if (one_poller) {  // one warp polls, the other three wait in named barrier 1 (see the 512x256 kernel): -0.6 to -0.9 %
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (lane == 0) {
+          (void)mbar_try_wait(&bars->tmem_full[acc], acc_phase);
+          got = bars->abort_flag != 0u ? 0 : 1;
+        }
+        got = __shfl_sync(0xFFFFFFFFu, got, 0);
+      }
+      if (got == 0) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PBN);
       drain_accumulator<OutT>(ea, taddr, tc.m * PBM + (int)rank * 128 + quarter * 32, tc.n * PBN, PBN, boxes);
@@ -1422,7 +1435,11 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
         int v = 0;
         if (lane == 0) v = pair_ring_read(bars, (uint32_t)local, peer, 32u, 64u);
         v = __shfl_sync(0xFFFFFFFFu, v, 0);
-        if (v == -2) { ok = false; break; }
+        if (v == -2) {
+          if (one_poller) asm volatile("bar.arrive 1, 128;" ::: "memory");
+          ok = false;
+          break;
+        }
         t = v < 0 ? num_tiles : (int64_t)v;
       } else {
         t += num_clusters;
@@ -1480,7 +1497,6 @@ constexpr int QSTAGE_BYTES = QA_BYTES + QB_BYTES;
 constexpr int QTHREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int SPLIT_DRAIN_BIT = 26;  // bit of the packed `raster` word: overlap the epilogue by halves
 constexpr int SPLIT_TAIL_BIT = 27;   // and finish accumulator half 0 ahead of half 1 at the end of a tile
-constexpr int EPI_ALL_POLL_BIT = 29; // every epilogue warp polls the accumulator barrier itself (the earlier scheme)
 
 struct __align__(8) QBarriers {
   uint64_t full[QSTAGES];
@@ -1934,6 +1950,11 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   return check_launch();
 }
 
+// F8B200_GEMM_EPIWAIT=all (read at every call): every epilogue warp of the pair kernels polls for its accumulator
+static int epi_wait_bits() {
+  const char* e = getenv("F8B200_GEMM_EPIWAIT");
+  return (e != nullptr && e[0] == 'a') ? (1 << EPI_ALL_POLL_BIT) : 0;
+}
 // F8B200_GEMM_WAIT=sleep (read at every call): the 512x256 pair kernel's waits sleep between probes
 static int wait_bits() {
   const char* e = getenv("F8B200_GEMM_WAIT");
@@ -1984,7 +2005,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   }
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
-                         choose_raster(m, n, k, pair::PBM, pair::PBN) | layouts, sched));
+                         choose_raster(m, n, k, pair::PBM, pair::PBN) | layouts | epi_wait_bits(), sched));
 }
 
 template <typename OutT>
@@ -2062,8 +2083,7 @@ static int launch_pairwide(const CUtensorMap& ma, const CUtensorMap& mb, const C
     if (e[0] == 'h') split = 1 << pairwide::SPLIT_DRAIN_BIT;
   }
   split |= wait_bits();
-  if (const char* e = getenv("F8B200_GEMM_EPIWAIT"))
-    if (e[0] == 'a') split |= 1 << pairwide::EPI_ALL_POLL_BIT;
+  split |= epi_wait_bits();
   return record_cuda_error(
       cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, sa, sb, bias_t, out_t, ldo, m, n, k, idesc, vec_ok, use_tma,
                          choose_raster(m, n, k, pairwide::QBM, pairwide::QBN) | layouts | split, sched, scatter));
