@@ -509,3 +509,38 @@ def test_single_node_route_matches_general_route(monkeypatch):
     odd = Float8Linear.from_float(nn.Linear(72, 48, bias=False).to(torch.bfloat16), f8.Float8LinearConfig())
     with pytest.raises(RuntimeError, match="multiple of 16"):
         odd(torch.randn(16, 72).to(torch.bfloat16))
+
+
+def test_step_timeline_from_a_profiler_trace(tmp_path):
+    """`benchmarks.multi_gpu._timeline_of`: busy / idle time of the stream that runs the GEMMs and the idle
+    time spent under NCCL kernels of other streams, from a chrome trace (here a hand-made one)."""
+    import json
+
+    from float8_experimental_b200.benchmarks import multi_gpu
+
+    def k(name, ts, dur, stream, cat="kernel"):
+        return {"name": name, "cat": cat, "ts": ts, "dur": dur, "args": {"stream": stream}}
+
+    events = [
+        k("gemm_fp8_pairwide_kernel", 0, 1000, 7), k("cast_tile8_kernel", 1000, 100, 7),
+        # 400 us gap on stream 7: an all-gather runs on stream 20 during 300 us of it
+        k("ncclDevKernel_AllGather", 1050, 350, 20),
+        k("gemm_fp8_pairwide_kernel", 1500, 2000, 7),
+        k("ncclDevKernel_ReduceScatter", 2000, 1800, 21),      # overlaps the GEMM, then 300 us exposed
+        k("Memset", 3900, 10, 7, cat="gpu_memset"),
+        {"name": "cudaLaunchKernel", "cat": "cuda_runtime", "ts": 0, "dur": 5},
+    ]
+
+    class FakeProf:
+        def export_chrome_trace(self, path):
+            with open(path, "w") as f:
+                json.dump({"traceEvents": events}, f)
+
+    t = multi_gpu._timeline_of(FakeProf(), steps=2)
+    assert t["span_ms_per_step"] == pytest.approx(3.91 / 2)
+    assert t["gemm_stream_busy_ms"] == pytest.approx(3.11 / 2)
+    assert t["gemm_stream_idle_ms"] == pytest.approx(0.8 / 2)
+    # idle [1100, 1500) under the all-gather until 1400; idle [3500, 3900) under the reduce-scatter until 3800
+    assert t["idle_while_nccl_runs_ms"] == pytest.approx(0.6 / 2)
+    assert t["idle_with_nothing_running_ms"] == pytest.approx(0.2 / 2)
+    assert t["largest_idle_gaps_ms"][:2] == [0.4, 0.4]
