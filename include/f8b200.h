@@ -116,7 +116,7 @@ int f8b200_cast(const void* x, int hp_dtype, int64_t rows, int64_t cols, int64_t
  * then f8b200_cast(scale_src = 1, reverse = 1) from that amax (scale stored to scale_out when not
  * NULL).  Two kernels and a 4-byte memset on `stream`, one host call: hp_tensor_to_float8_dynamic of
  * float8_experimental/float8_scaling_utils.py:33-62 (about ten operator launches in the reference).
- * With hundreds of small layers per step the host calls, not the kernels, bound the step time.
+ * One host call per tensor keeps the host ahead of the GPU in models of many small layers.
  */
 int f8b200_cast_dynamic(const void* x, int hp_dtype, int64_t rows, int64_t cols, int fp8_kind,
                         float* amax_out, float* scale_out, void* out, void* stream);
